@@ -1,0 +1,240 @@
+/*
+ * mac_b200.h -- C ABI of the B200-native MAC-Attention fused decode path.
+ *
+ * Plain C: raw device pointers, int32/int64 sizes and scalars, no torch types.
+ * Every entry point returns 0 on success or a negative MAC_B200_E* code; the
+ * text of the last error on the calling thread is at mac_b200_last_error().
+ * Nothing here synchronises the host with the device; work is queued on the
+ * stream that is passed in (a cudaStream_t carried as void*; NULL = legacy
+ * default stream) on the device that is current on the calling thread.
+ *
+ * Each entry point replaces one operator of the reference's PyTorch extension
+ * modules (paths relative to the reference project,
+ * attention/src/mac_attention/integrations/sglang/csrc/):
+ *
+ *   mac_b200_persistent_decode_bf16       mac_decode_persistent.cu:4962-5524
+ *   mac_b200_prefill_update_cache         mac_prefill_update_cache.cu:324-372
+ *   mac_b200_mark_persistent_ready        mac_prefill_update_cache.cu:374-409
+ *   mac_b200_invalidate_persistent_ready  mac_prefill_update_cache.cu:411-446
+ *   mac_b200_update_request_state         mac_prefill_update_cache.cu:448-495
+ *
+ * Notation: N batch rows, Hq query heads, Hkv KV heads, G = Hq/Hkv (1..8),
+ * D = 128, M ring capacity, R ring rows, P = past_lens[n] (tokens already in
+ * the KV pool, excluding the current one), S = semantic_pos_ahead,
+ * F = front_sink_tokens.
+ */
+#ifndef MAC_B200_H_
+#define MAC_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MAC_B200_ABI_VERSION 1
+
+/* Error codes (negative). */
+#define MAC_B200_OK 0
+#define MAC_B200_EINVAL (-1)      /* bad argument: shape, dtype flag, null pointer          */
+#define MAC_B200_EUNSUPPORTED (-2)/* valid for the reference API but outside this build      */
+#define MAC_B200_ECUDA (-3)       /* a CUDA runtime call failed (text has the CUDA error)    */
+#define MAC_B200_ECAPTURE (-4)    /* scratch must grow but the stream is being captured      */
+#define MAC_B200_ESIZE (-5)       /* request exceeds a stated fixed capacity                 */
+
+/* Bits of the device status word (see mac_b200_query_status). */
+#define MAC_B200_STATUS_BARRIER_TIMEOUT 0x1u /* a bounded grid-barrier wait ran out         */
+#define MAC_B200_STATUS_BAD_REQUEST 0x2u     /* req id / length outside the tables; row zeroed */
+#define MAC_B200_STATUS_SCHED_OVERFLOW 0x4u  /* internal schedule exceeded its arena         */
+
+/*
+ * Arguments of one fused MAC decode step.
+ * Replaces the 68 positional arguments of the reference operator
+ * mac_persistent_decode_bf16 (mac_decode_persistent.cu:4962-5030).  All
+ * pointers are device pointers unless stated otherwise; "bf16" buffers are
+ * passed as void*.  Tensors are contiguous, row-major, with the shapes given.
+ *
+ * The reference's task-list and partial-result workspaces (its arguments
+ * complete_task_go .. partial_tail_lse) are private scratch of the old
+ * kernel's scheduler; the host shim validates them for signature
+ * compatibility and this kernel does not need them.
+ */
+typedef struct MacB200DecodeArgs {
+  /* ---- sizes ---- */
+  int32_t N;                   /* decode rows in this step                                  */
+  int32_t Hq;                  /* query heads                                               */
+  int32_t Hkv;                 /* KV heads                                                  */
+  int32_t D;                   /* head dim, must be 128                                     */
+  int32_t M;                   /* ring capacity (slots per request)                         */
+  int32_t R;                   /* ring rows = query_cache.size(0)                           */
+  int32_t req_to_token_rows;   /* rows of req_to_token                                      */
+  int32_t req_to_token_stride; /* columns of req_to_token                                   */
+  int64_t kv_tokens;           /* rows of k_buffer / v_buffer                               */
+  int32_t ws_batch;            /* N' >= N: leading dim of the decision workspaces           */
+  int32_t max_match_tiles;     /* Tm = match_dist.size(2) >= ceil(M / match_tile_slots)     */
+
+  /* ---- scalars, same meaning as the reference operator's ---- */
+  int32_t max_context;
+  int32_t tile_tokens;         /* accepted; only used for reported counters                 */
+  int32_t match_tile_slots;
+  int32_t semantic_pos_ahead;  /* S */
+  int32_t front_sink_tokens;   /* F (negative is treated as 0)                              */
+  int32_t gen_min_limit;
+  int32_t lookback_right;
+  int32_t candidate_mode;
+  float threshold;             /* hit iff dist < 2*D*(1-threshold)^2 (strict)               */
+  float sm_scale;
+  int32_t debug_enabled;       /* >= 2: write timestamps into phase_cycles                  */
+  int32_t bench_mode;          /* 0 off, 1 synthetic per head, 2 synthetic per KV group     */
+  float bench_hit_rate;
+  float bench_hit_rate_std;
+  float bench_skip_ratio;
+  float bench_skip_ratio_std;
+  float bench_match_lag_mean;
+  float bench_match_lag_std;
+  int32_t bench_seed;
+  int32_t bench_miss_mask;     /* < 0 off */
+  int32_t bench_layer_id;
+  /* Result-affecting launcher knobs the reference reads from the environment
+   * (mac_decode_persistent.cu:5229, 5337). */
+  int32_t mixed_group_fallback; /* MAC_PERSISTENT_MIXED_GROUP_FALLBACK, default 1           */
+  int32_t bench_exact_quota;    /* MAC_BENCH_EXACT_QUOTA, default 1                         */
+  int32_t out_cache_loc_is_i64; /* 0: int32, 1: int64                                       */
+  int32_t phase_cycles_count;   /* elements of phase_cycles (>= 6)                          */
+  int32_t grid_cap;             /* > 0 caps the persistent grid (MAC_PERSISTENT_COOP_CTAS)  */
+
+  /* ---- inputs ---- */
+  const void* q_post;          /* [N,Hq,D] bf16, post-RoPE query (attention)                */
+  const void* q_pre;           /* [N,Hq,D] bf16, pre-RoPE query (matching, ring write)      */
+  const void* k_buffer;        /* [kv_tokens,Hkv,D] bf16                                    */
+  const void* v_buffer;        /* [kv_tokens,Hkv,D] bf16                                    */
+  const int32_t* req_to_token; /* [rows,stride] logical position -> KV pool row             */
+  const int32_t* req_ids;      /* [>=N]                                                     */
+  const int32_t* past_lens;    /* [>=N]                                                     */
+  const void* out_cache_loc;   /* [>=N] int32 or int64: pool row of the current token       */
+  /* ---- MAC ring (read and written) ---- */
+  void* query_cache;           /* [R,M,Hq,D] bf16                                           */
+  void* attn_cache;            /* [R,M,Hq,D] bf16                                           */
+  float* lse_cache;            /* [R,M,Hq] f32, natural log                                 */
+  /* ---- outputs ---- */
+  void* out;                   /* [N,Hq,D] bf16                                             */
+  float* optional_lse;         /* [N,Hq] f32 natural log, or NULL                           */
+  /* ---- observable workspace outputs (all int32 unless noted) ---- */
+  float* match_dist;           /* [N',Hq,Tm] f32 */
+  int32_t* match_pos;          /* [N',Hq,Tm] */
+  int32_t* match_slot;         /* [N',Hq,Tm] */
+  int32_t* head_hit;           /* [N',Hq] */
+  int32_t* head_match_slot;
+  int32_t* head_match_pos;
+  int32_t* head_prefix_end;
+  int32_t* head_rect_start;
+  int32_t* head_new_end;
+  int32_t* group_rect_begin;   /* [N',Hkv] */
+  int32_t* group_rect_end;
+  int32_t* group_rect_tiles;
+  int32_t* group_tail_begin;
+  int32_t* group_tail_end;
+  int32_t* group_tail_tiles;
+  int32_t* group_mode;         /* 0 all heads reuse, 1 full attention, 2 mixed              */
+  int32_t* task_counts;        /* [>=9] */
+  int64_t* phase_cycles;       /* [phase_cycles_count] int64 */
+  /* ---- readiness gate: NULL cache_ready = every request ready ---- */
+  const uint8_t* cache_ready;  /* [R] bool/u8 */
+  const int64_t* cache_epoch;  /* [R] or NULL */
+  const int64_t* request_epoch;/* [R] or NULL */
+} MacB200DecodeArgs;
+
+/*
+ * One fused MAC decode step: ring match scan, hit/miss/demoted scheduling,
+ * partial attention, LSE merge, ring update and output, one persistent launch.
+ * Replaces mac_persistent_decode_bf16 (mac_decode_persistent.cu:4962-5524).
+ *
+ * Scratch: a small per-device arena owned by the library holds split-KV
+ * partials and scheduler words.  It is allocated (or grown) on the first call
+ * that needs it, which therefore must not happen while `stream` is being
+ * captured into a CUDA graph: make one eager call first.  Later calls allocate
+ * nothing.  Launches of this entry point that overlap on one device race on
+ * that arena; keep them on one stream or order them with events.
+ */
+int mac_b200_persistent_decode_bf16(const MacB200DecodeArgs* args, void* stream);
+
+/*
+ * Arguments of the prefill-side ring build.
+ * Replaces the 14 arguments of mac_prefill_update_cache
+ * (mac_prefill_update_cache.cu:324-337).
+ */
+typedef struct MacB200PrefillArgs {
+  int32_t R, M, H, D;            /* ring geometry: q_cache is [R,M,H,D]                       */
+  int32_t B;                     /* batch rows = req_ids.size(0)                              */
+  int32_t src_rows;              /* rows of src_q / src_attn / src_lse                        */
+  int32_t request_length_by_batch; /* 1: request_length is [B] (read only); 0: [R], bumped    */
+  void* q_cache;                 /* [R,M,H,D] bf16 */
+  void* attn_cache;              /* [R,M,H,D] bf16 */
+  float* lse_cache;              /* [R,M,H] f32    */
+  void* q_post_cache;            /* [R,M,H,D] bf16 or NULL: rows get the bf16 NaN 0x7fc0      */
+  int32_t* request_length;       /* [R] or [B] */
+  const int32_t* req_ids;        /* [B] */
+  const void* src_q;             /* [src_rows,H,D] bf16 */
+  const void* src_attn;          /* [src_rows,H,D] bf16 */
+  const float* src_lse;          /* [src_rows,H] f32 */
+  const int32_t* offsets;        /* [B+1] row offsets into src_* */
+  const int32_t* lens;           /* [B] */
+} MacB200PrefillArgs;
+
+/* Replaces mac_prefill_update_cache (mac_prefill_update_cache.cu:324-372). */
+int mac_b200_prefill_update_cache(const MacB200PrefillArgs* args, void* stream);
+
+/* Replaces mac_mark_persistent_ready (mac_prefill_update_cache.cu:374-409):
+ * for each valid req: cache_epoch[req] = request_epoch[req]; ready[req] = 1. */
+int mac_b200_mark_persistent_ready(uint8_t* ready, int64_t* cache_epoch,
+                                   const int64_t* request_epoch, const int32_t* req_ids,
+                                   int32_t B, int32_t R, void* stream);
+
+/* Replaces mac_invalidate_persistent_ready (mac_prefill_update_cache.cu:411-446):
+ * ready[req] = 0; cache_epoch[req] = -1; request_epoch[req] += 1. */
+int mac_b200_invalidate_persistent_ready(uint8_t* ready, int64_t* cache_epoch,
+                                         int64_t* request_epoch, const int32_t* req_ids,
+                                         int32_t B, int32_t R, void* stream);
+
+/* Replaces mac_update_request_state (mac_prefill_update_cache.cu:448-495). */
+int mac_b200_update_request_state(int32_t* req_len, int32_t* match_req_len,
+                                  int32_t* cache_lens, const int32_t* req_ids,
+                                  const int32_t* seq_lens, const int32_t* cur_lens,
+                                  int32_t B, int32_t R, void* stream);
+
+/* Text of the last error raised on the calling thread ("" if none).
+ * Stands in for the c10::Error text of the reference's TORCH_CHECKs. */
+const char* mac_b200_last_error(void);
+
+/* MAC_B200_ABI_VERSION the library was built with. */
+int mac_b200_abi_version(void);
+
+/*
+ * Reads (and clears) the sticky device status word of the current device:
+ * synchronises `stream`, copies the word back, resets barrier state if a
+ * bounded wait ran out.  Not on the hot path; tests and health checks poll it.
+ * No counterpart in the reference (its kernel has no bounded waits).
+ */
+int mac_b200_query_status(uint32_t* status_out, void* stream);
+
+/*
+ * Static launch facts of the decode kernel on the current device, for logs
+ * and benchmarks (the reference prints the same under
+ * MAC_PERSISTENT_DEBUG_LAUNCH, mac_decode_persistent.cu:5406-5419).
+ */
+typedef struct MacB200LaunchInfo {
+  int32_t sm_count;
+  int32_t ctas_per_sm;
+  int32_t block_threads;
+  int32_t dynamic_smem_bytes;
+  int32_t regs_per_thread;
+  int32_t last_grid;            /* grid of the most recent decode launch on this device      */
+  int64_t arena_bytes;          /* current size of the per-device scratch arena              */
+  int64_t kernel_launches;      /* decode + prefill + gate kernels launched by this process  */
+} MacB200LaunchInfo;
+int mac_b200_launch_info(MacB200LaunchInfo* info);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MAC_B200_H_ */

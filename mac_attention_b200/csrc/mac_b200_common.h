@@ -1,0 +1,41 @@
+// Shared host-side helpers of the C-ABI library: thread-local error text,
+// CUDA error mapping, launch counting.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/mac_b200.h"
+
+namespace mac_b200 {
+
+// Text behind mac_b200_last_error(); one buffer per host thread.
+char* error_buffer();
+constexpr int kErrorBufferBytes = 512;
+
+int fail(int code, const char* fmt, ...);
+
+inline int cuda_fail(cudaError_t err, const char* what) {
+  return fail(MAC_B200_ECUDA, "%s: %s (%s)", what, cudaGetErrorString(err),
+              cudaGetErrorName(err));
+}
+
+// Kernels launched by this process through the library (all entry points).
+extern std::atomic<int64_t> g_kernel_launches;
+
+#define MAC_REQUIRE(cond, ...)                        \
+  do {                                                \
+    if (!(cond)) return ::mac_b200::fail(MAC_B200_EINVAL, __VA_ARGS__); \
+  } while (0)
+
+#define MAC_CUDA(call)                                              \
+  do {                                                              \
+    cudaError_t _e = (call);                                        \
+    if (_e != cudaSuccess) return ::mac_b200::cuda_fail(_e, #call); \
+  } while (0)
+
+}  // namespace mac_b200

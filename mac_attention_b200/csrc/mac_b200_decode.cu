@@ -1,0 +1,1386 @@
+// Fused MAC decode step for B200 (sm_100a): one persistent, CUDA-graph-safe launch.
+//
+// What one launch does, for every decode row n and query head:
+//   A. match scan    squared-L2 distance between the pre-RoPE query and every
+//                    candidate row of the request's recent-query ring; per
+//                    match tile argmin with (distance, then older position)
+//                    ordering.
+//   B. classify      per head hit test / synthetic benchmark override /
+//                    front-sink demotion; per KV group mode (all heads reuse,
+//                    full attention, mixed); per group token rows
+//                    sink | band | tail and their cost.
+//   C. attend+merge  the rows of all groups are laid end to end in a "cost
+//                    space" ordered demoted -> miss -> hit queue and cut into
+//                    equal pieces, a whole multiple of the grid (wave-quantised);
+//                    CTAs pull pieces by ticket.  Each (piece x row) segment is
+//                    streamed through a per-warp cp.async ring of 16-token bf16
+//                    K/V blocks and contracted with mma.sync m16n8k16 (the GQA
+//                    group's query rows padded to 16).  The CTA that retires a
+//                    group's last segment LSE-merges prefix state + partials,
+//                    writes the ring row and the output.
+// Phases are separated by two grid barriers (bounded spins, cooperative launch
+// guarantees co-residency); nothing else waits on another CTA.
+//
+// Semantics follow the reference kernel
+// attention/src/mac_attention/integrations/sglang/csrc/mac_decode_persistent.cu
+// (cited as DEC.cu below); structure, scheduling and data flow are new.
+#include <cuda_bf16.h>
+
+#include <climits>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "mac_b200_common.h"
+
+namespace mac_b200 {
+namespace {
+
+// ----------------------------------------------------------------- constants
+constexpr int kD = 128;                    // head dim (fixed, as in the reference)
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kStages = 3;                 // per-warp cp.async ring depth
+constexpr int kBlkTok = 16;                // tokens per warp block (one mma K step of P.V)
+constexpr int kRowBytes = kD * 2;          // one bf16 K or V row
+constexpr int kStageBytes = 2 * kBlkTok * kRowBytes;     // K block + V block = 8 KB
+constexpr int kWarpRingBytes = kStages * kStageBytes;    // 24 KB
+constexpr int kRingBytes = kWarps * kWarpRingBytes;      // 192 KB
+constexpr int kMaxGroups = 4096;           // N * Hkv upper bound of one launch
+constexpr int kMaxHq = 128;
+constexpr int kOvhTok = 256;               // cost of opening a segment, in token equivalents
+constexpr int kMinPieceTok = 2048;
+constexpr int kCombineRow = kD + 8;        // padded fp32 row of the cross-warp combine buffer
+constexpr int kSmemPerm = kMaxGroups * 2;              // u16 gperm[]
+constexpr int kSmemPrefix = (kMaxGroups + 1) * 4;      // u32 cost prefix
+constexpr int kSmemMisc = 1024;
+constexpr int kSmemBytes = kRingBytes + kSmemPerm + kSmemPrefix + 12 + kSmemMisc;
+constexpr unsigned kSpinLimit = 1u << 22;  // polls (each >= ~100 ns) before a wait gives up
+constexpr float kLog2e = 1.4426950408889634074f;
+constexpr float kLn2 = 0.6931471805599453094f;
+
+// Cross-launch state: the grid barrier words and the sticky status word.  Zero
+// at module load; the barrier leaves its counter at zero after every use.
+__device__ unsigned g_bar_count = 0;
+__device__ unsigned g_bar_gen = 0;
+__device__ unsigned g_status = 0;
+
+struct GroupPlan {
+  int32_t sink_hi;   // sink row  [0, sink_hi)
+  int32_t band_lo;   // band row  [band_lo, new_end)
+  int32_t new_end;   // tail row  [new_end, kv_len)
+  int32_t kv_len;
+  int32_t cls;       // 0 demoted queue, 1 miss queue, 2 hit queue
+  int32_t cost;      // token equivalents, sum over non-empty rows of (len + kOvhTok)
+  int32_t mode;
+  int32_t bad;
+};
+
+struct Arena {
+  uint32_t* ticket;      // [1] piece ticket of phase C
+  int32_t* garrive;      // [NG] segments retired per group
+  GroupPlan* plan;       // [NG]
+  float* part_o;         // [slots][G][kD]
+  float* part_lse;       // [slots][8]
+  int32_t slots;
+};
+
+struct DecodeParams {
+  MacB200DecodeArgs a;
+  Arena ar;
+  float thr_dist;
+  float scale_log2;      // sm_scale * log2(e)
+  int32_t G;
+  int32_t NG;
+  int32_t F;             // front_sink_tokens clamped at 0
+  int32_t tm_used;       // ceil(M / match_tile_slots)
+  int32_t max_pieces;
+};
+
+// ------------------------------------------------------------- small helpers
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t bits16) {
+  return __uint_as_float(bits16 << 16);
+}
+__device__ __forceinline__ float bf16_lo(uint32_t packed) { return __uint_as_float(packed << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t packed) {
+  return __uint_as_float(packed & 0xffff0000u);
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float lg2(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src),
+               "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1,
+                                            uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1,
+                                                  uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+// D(16x8,f32) += A(16x16,bf16,row) * B(16x8,bf16,col).  Rows 8..15 of A are
+// always zero here (at most 8 query heads share a KV head), so a1 = a3 = 0.
+__device__ __forceinline__ void mma_bf16_rows8(float (&c)[4], uint32_t a0, uint32_t a2,
+                                               uint32_t b0, uint32_t b1) {
+  const uint32_t z = 0u;
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(z), "r"(a2), "r"(z), "r"(b0), "r"(b1));
+}
+
+// DEC.cu:798-807
+__device__ __forceinline__ int ring_slot_to_pos(int past_len, int M, int slot) {
+  if (past_len < M) return slot;
+  int order = slot - past_len % M;
+  if (order < 0) order += M;
+  return past_len - M + order;
+}
+// DEC.cu:837-848
+__device__ __forceinline__ int pos_to_ring_slot(int past_len, int M, int pos) {
+  if (past_len < M) return pos;
+  int slot = (pos - (past_len - M)) + past_len % M;
+  if (slot >= M) slot -= M;
+  if (slot < 0) slot += M;
+  return slot;
+}
+__device__ __forceinline__ int cache_end_for_pos(int p, int S) {
+  const int e = p + 1 - S;
+  return e > 0 ? e : 0;
+}
+__device__ __forceinline__ bool better_pair(float d, int pos, float bd, int bp) {
+  return (d < bd) || (d == bd && pos < bp);
+}
+// DEC.cu:221-230
+__device__ __forceinline__ bool request_ready(const MacB200DecodeArgs& a, int req) {
+  if (a.cache_ready == nullptr) return true;
+  if (req < 0) return false;
+  if (a.cache_ready[req] == 0) return false;
+  if (a.cache_epoch != nullptr && a.request_epoch != nullptr &&
+      a.cache_epoch[req] != a.request_epoch[req])
+    return false;
+  return true;
+}
+__device__ __forceinline__ bool request_bad(const MacB200DecodeArgs& a, int n) {
+  const int req = a.req_ids[n];
+  const int P = a.past_lens[n];
+  return req < 0 || req >= a.R || req >= a.req_to_token_rows || P < 0 ||
+         P > a.req_to_token_stride;
+}
+__device__ __forceinline__ void candidate_window(const MacB200DecodeArgs& a, int P, int& begin,
+                                                 int& end) {
+  begin = P - a.M > 0 ? P - a.M : 0;
+  end = P;
+  if (a.candidate_mode == 1) {
+    end = P - a.lookback_right;
+    if (end < begin) end = begin;
+  }
+}
+
+// Synthetic-decision hash of the reference's benchmark mode, DEC.cu:817-835.
+__device__ __forceinline__ uint32_t mix_u32(uint32_t x) {
+  x ^= x >> 16;
+  x *= 0x7feb352du;
+  x ^= x >> 15;
+  x *= 0x846ca68bu;
+  x ^= x >> 16;
+  return x;
+}
+__device__ __forceinline__ float uniform01_u32(uint32_t x) {
+  return static_cast<float>(mix_u32(x) & 0x00ffffffu) * (1.0f / 16777216.0f);
+}
+__device__ __forceinline__ float pseudo_normal_u32(uint32_t x) {
+  float s = uniform01_u32(x);
+  s = __fadd_rn(s, uniform01_u32(x ^ 0x9e3779b9u));
+  s = __fadd_rn(s, uniform01_u32(x ^ 0x85ebca6bu));
+  s = __fadd_rn(s, uniform01_u32(x ^ 0xc2b2ae35u));
+  return __fmul_rn(__fadd_rn(s, -2.0f), 1.7320508075688772f);
+}
+__device__ __forceinline__ float clampf(float v, float lo, float hi) {
+  return fminf(fmaxf(v, lo), hi);
+}
+// DEC.cu:375-388 (the a*b+c there is one fused multiply-add on the device)
+__device__ __forceinline__ int bench_target_miss_units(const MacB200DecodeArgs& a, int total) {
+  if (total <= 0) return 0;
+  float miss_rate = clampf(__fadd_rn(1.0f, -a.bench_hit_rate), 0.0f, 1.0f);
+  int miss;
+  if (a.bench_exact_quota != 0 && a.bench_hit_rate_std == 0.0f)
+    miss = static_cast<int>(floorf(__fmaf_rn(miss_rate, static_cast<float>(total), 0.5f)));
+  else
+    miss = static_cast<int>(ceilf(__fmul_rn(miss_rate, static_cast<float>(total))));
+  if (miss < 0) miss = 0;
+  if (miss > total) miss = total;
+  return miss;
+}
+
+// ------------------------------------------------------------- grid barrier
+// Sense-reversing barrier on two static words.  The wait is bounded: when it
+// runs out the CTA records MAC_B200_STATUS_BARRIER_TIMEOUT and the kernel
+// returns (all CTAs observe the same failure through the return value).
+__device__ bool grid_barrier(unsigned nblocks) {
+  __shared__ int sh_ok;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    const unsigned gen = ld_acquire_u32(&g_bar_gen);
+    __threadfence();
+    const unsigned prev = atomicAdd(&g_bar_count, 1u);
+    if (prev == nblocks - 1) {
+      g_bar_count = 0;
+      __threadfence();
+      atomicAdd(&g_bar_gen, 1u);
+    } else {
+      unsigned polls = 0;
+      while (ld_acquire_u32(&g_bar_gen) == gen) {
+        __nanosleep(40);
+        if (++polls > kSpinLimit) {
+          atomicOr(&g_status, MAC_B200_STATUS_BARRIER_TIMEOUT);
+          ok = 0;
+          break;
+        }
+      }
+    }
+    __threadfence();
+    sh_ok = ok;
+  }
+  __syncthreads();
+  return sh_ok != 0;
+}
+
+// ---------------------------------------------------------------- phase A
+// One work item = (match tile, request).  The CTA streams the tile's ring
+// rows for all query heads: a half-warp owns one 256-byte (slot, head) row
+// per load, lane t holding dims [8t, 8t+8); distances are summed in exactly
+// the reference's order (8 sequential FMAs per lane, xor butterfly 8,4,2,1;
+// DEC.cu:1062-1069, 343-349) so thresholds and ties resolve identically.
+__device__ void phase_match_scan(const DecodeParams& p, uint8_t* smem) {
+  const MacB200DecodeArgs& a = p.a;
+  const int tid = threadIdx.x;
+  // control words used after the barriers
+  if (blockIdx.x == 0) {
+    if (tid < 9) a.task_counts[tid] = 0;
+    if (tid == 9) *p.ar.ticket = 0u;
+  }
+  for (int g = blockIdx.x * kThreads + tid; g < p.NG; g += gridDim.x * kThreads)
+    p.ar.garrive[g] = 0;
+
+  uint4* q_sm = reinterpret_cast<uint4*>(smem);                       // [Hq][16] uint4
+  float* best_d_sm = reinterpret_cast<float*>(smem + kMaxHq * kRowBytes);  // [Hq*spar]
+  int* best_p_sm = reinterpret_cast<int*>(best_d_sm + 2 * kMaxHq);
+  int* best_s_sm = best_p_sm + 2 * kMaxHq;
+
+  const int Hq = a.Hq, M = a.M, Tm = a.max_match_tiles;
+  int p2 = 1;
+  while (p2 < Hq && p2 < 16) p2 <<= 1;   // heads scanned side by side
+  const int spar = 16 / p2;              // slots scanned side by side
+  const int hw = tid >> 4, tx = tid & 15;
+  const int hslot = hw % p2, sub = hw / p2;
+  const unsigned sub_mask = (tid & 16) ? 0xffff0000u : 0x0000ffffu;
+  const char* ring = static_cast<const char*>(a.query_cache);
+
+  const int items = a.N * Tm;
+  for (int item = blockIdx.x; item < items; item += gridDim.x) {
+    const int tile = item / a.N;
+    const int n = item - tile * a.N;
+    const int64_t out_base = static_cast<int64_t>(n) * Hq * Tm + tile;
+    const int slot_begin = tile * a.match_tile_slots;
+    int slot_end = slot_begin + a.match_tile_slots;
+    if (slot_end > M) slot_end = M;
+    bool eligible = false;
+    int P = 0, req = 0, cbeg = 0, cend = 0;
+    if (!request_bad(a, n)) {
+      P = a.past_lens[n];
+      req = a.req_ids[n];
+      candidate_window(a, P, cbeg, cend);
+      eligible = P >= a.gen_min_limit && cend > cbeg && request_ready(a, req);
+    }
+    // does this tile hold any candidate slot?
+    bool any = false;
+    if (eligible && slot_begin < slot_end) {
+      if (P < M) {
+        any = slot_begin < cend && slot_end > cbeg;  // slot == pos
+      } else {
+        any = true;  // every slot maps into [P-M, P); lookback may trim a few
+      }
+    }
+    if (!any) {
+      for (int h = tid; h < Hq; h += kThreads) {
+        a.match_dist[out_base + static_cast<int64_t>(h) * Tm] = INFINITY;
+        a.match_pos[out_base + static_cast<int64_t>(h) * Tm] = INT_MAX;
+        a.match_slot[out_base + static_cast<int64_t>(h) * Tm] = -1;
+      }
+      continue;
+    }
+    __syncthreads();  // previous item's smem readers are done
+    {
+      const uint4* qsrc = reinterpret_cast<const uint4*>(
+          static_cast<const char*>(a.q_pre) + static_cast<int64_t>(n) * Hq * kRowBytes);
+      for (int i = tid; i < Hq * 16; i += kThreads) q_sm[i] = qsrc[i];
+    }
+    __syncthreads();
+
+    const int64_t req_base = static_cast<int64_t>(req) * M;
+    for (int h = hslot; h < Hq; h += p2) {
+      float qf[8];
+      {
+        const uint4 qv = q_sm[h * 16 + tx];
+        qf[0] = bf16_lo(qv.x); qf[1] = bf16_hi(qv.x);
+        qf[2] = bf16_lo(qv.y); qf[3] = bf16_hi(qv.y);
+        qf[4] = bf16_lo(qv.z); qf[5] = bf16_hi(qv.z);
+        qf[6] = bf16_lo(qv.w); qf[7] = bf16_hi(qv.w);
+      }
+      float bd = INFINITY;
+      int bp = INT_MAX, bs = -1;
+      constexpr int kU = 8;
+      for (int s0 = slot_begin + sub; s0 < slot_end; s0 += kU * spar) {
+        uint4 raw[kU];
+        int pos[kU];
+        bool val[kU];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          const int s = s0 + u * spar;
+          pos[u] = ring_slot_to_pos(P, M, s);
+          val[u] = s < slot_end && pos[u] >= cbeg && pos[u] < cend;
+          if (val[u])
+            raw[u] = ld_stream16(ring + ((req_base + s) * Hq + h) * kRowBytes + tx * 16);
+        }
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          if (!val[u]) continue;  // uniform across the half-warp
+          float acc = 0.0f, diff;
+          diff = qf[0] - bf16_lo(raw[u].x); acc = __fmaf_rn(diff, diff, acc);
+          diff = qf[1] - bf16_hi(raw[u].x); acc = __fmaf_rn(diff, diff, acc);
+          diff = qf[2] - bf16_lo(raw[u].y); acc = __fmaf_rn(diff, diff, acc);
+          diff = qf[3] - bf16_hi(raw[u].y); acc = __fmaf_rn(diff, diff, acc);
+          diff = qf[4] - bf16_lo(raw[u].z); acc = __fmaf_rn(diff, diff, acc);
+          diff = qf[5] - bf16_hi(raw[u].z); acc = __fmaf_rn(diff, diff, acc);
+          diff = qf[6] - bf16_lo(raw[u].w); acc = __fmaf_rn(diff, diff, acc);
+          diff = qf[7] - bf16_hi(raw[u].w); acc = __fmaf_rn(diff, diff, acc);
+#pragma unroll
+          for (int off = 8; off > 0; off >>= 1)
+            acc = __fadd_rn(acc, __shfl_xor_sync(sub_mask, acc, off, 16));
+          if (better_pair(acc, pos[u], bd, bp)) {
+            bd = acc;
+            bp = pos[u];
+            bs = s0 + u * spar;
+          }
+        }
+      }
+      if (tx == 0) {
+        best_d_sm[h * spar + sub] = bd;
+        best_p_sm[h * spar + sub] = bp;
+        best_s_sm[h * spar + sub] = bs;
+      }
+    }
+    __syncthreads();
+    for (int h = tid; h < Hq; h += kThreads) {
+      float bd = INFINITY;
+      int bp = INT_MAX, bs = -1;
+      for (int s = 0; s < spar; ++s) {
+        const float d = best_d_sm[h * spar + s];
+        const int pp = best_p_sm[h * spar + s];
+        if (better_pair(d, pp, bd, bp)) {
+          bd = d;
+          bp = pp;
+          bs = best_s_sm[h * spar + s];
+        }
+      }
+      a.match_dist[out_base + static_cast<int64_t>(h) * Tm] = bd;
+      a.match_pos[out_base + static_cast<int64_t>(h) * Tm] = bp;
+      a.match_slot[out_base + static_cast<int64_t>(h) * Tm] = bs;
+    }
+  }
+}
+
+// ---------------------------------------------------------------- phase B
+// One warp per KV group: cross-tile argmin per head, hit test, synthetic
+// override, front-sink demotion, group mode, reported arrays, and the group's
+// plan for phase C.  Decision rules: DEC.cu:1142-1402.
+__device__ void phase_classify(const DecodeParams& p) {
+  const MacB200DecodeArgs& a = p.a;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int G = p.G, Hq = a.Hq, Hkv = a.Hkv, M = a.M, Tm = a.max_match_tiles;
+  int gp2 = 1;
+  while (gp2 < G) gp2 <<= 1;
+  const int L = 32 / gp2;        // lanes cooperating on one head
+  const int hl = lane / L;       // head index inside the group
+  const int sub = lane % L;
+  const int S = a.semantic_pos_ahead;
+
+  for (int g = blockIdx.x * kWarps + warp; g < p.NG; g += gridDim.x * kWarps) {
+    const int n = g / Hkv, hkv = g - n * Hkv;
+    const int64_t go = static_cast<int64_t>(n) * Hkv + hkv;
+    GroupPlan plan;
+    if (request_bad(a, n)) {
+      // Malformed row: zero output, no ring access, sticky status bit.
+      __nv_bfloat16* out = static_cast<__nv_bfloat16*>(a.out);
+      for (int i = lane; i < G * kD; i += 32)
+        out[(static_cast<int64_t>(n) * Hq + hkv * G) * kD + i] = __float2bfloat16_rn(0.0f);
+      if (lane < G) {
+        const int64_t ho = static_cast<int64_t>(n) * Hq + hkv * G + lane;
+        if (a.optional_lse) a.optional_lse[ho] = -INFINITY;
+        a.head_hit[ho] = 0; a.head_match_slot[ho] = -1; a.head_match_pos[ho] = -1;
+        a.head_prefix_end[ho] = 0; a.head_rect_start[ho] = 0; a.head_new_end[ho] = 0;
+      }
+      if (lane == 0) {
+        atomicOr(&g_status, MAC_B200_STATUS_BAD_REQUEST);
+        a.group_rect_begin[go] = 0; a.group_rect_end[go] = 0; a.group_rect_tiles[go] = 0;
+        a.group_tail_begin[go] = 0; a.group_tail_end[go] = 0; a.group_tail_tiles[go] = 0;
+        a.group_mode[go] = 1;
+        plan.sink_hi = 0; plan.band_lo = 0; plan.new_end = 0; plan.kv_len = 0;
+        plan.cls = 0; plan.cost = 0; plan.mode = 1; plan.bad = 1;
+        p.ar.plan[g] = plan;
+      }
+      continue;
+    }
+    const int P = a.past_lens[n], req = a.req_ids[n];
+    int cbeg, cend;
+    candidate_window(a, P, cbeg, cend);
+    const bool ready = request_ready(a, req);
+    const bool eligible = P >= a.gen_min_limit && cend > cbeg && ready;
+    const int hq = hkv * G + hl;
+    const bool head_lane = hl < G;
+
+    float bd = INFINITY;
+    int bp = INT_MAX, bs = -1;
+    if (head_lane && eligible) {
+      const int64_t base = (static_cast<int64_t>(n) * Hq + hq) * Tm;
+      for (int t = sub; t < p.tm_used; t += L) {
+        const float d = __ldcg(a.match_dist + base + t);
+        const int pp = __ldcg(a.match_pos + base + t);
+        const int ss = __ldcg(a.match_slot + base + t);
+        if (better_pair(d, pp, bd, bp)) { bd = d; bp = pp; bs = ss; }
+      }
+    }
+    for (int off = L >> 1; off > 0; off >>= 1) {
+      const float od = __shfl_xor_sync(0xffffffffu, bd, off);
+      const int op = __shfl_xor_sync(0xffffffffu, bp, off);
+      const int os = __shfl_xor_sync(0xffffffffu, bs, off);
+      if (better_pair(od, op, bd, bp)) { bd = od; bp = op; bs = os; }
+    }
+    bool hit = eligible && bs >= 0 && bd < p.thr_dist;
+
+    if (a.bench_mode != 0 || a.bench_miss_mask >= 0) {
+      // DEC.cu:1184-1269
+      const uint32_t unit_id = (a.bench_mode == 2) ? static_cast<uint32_t>(hkv)
+                                                   : static_cast<uint32_t>(hq);
+      const uint32_t base_key = static_cast<uint32_t>(a.bench_seed) ^
+                                (static_cast<uint32_t>(a.bench_layer_id) * 0x9e3779b9u) ^
+                                (static_cast<uint32_t>(P) * 0x85ebca6bu);
+      const uint32_t key = base_key ^ (static_cast<uint32_t>(n) * 0xc2b2ae35u) ^
+                           (unit_id * 0x27d4eb2fu);
+      if (a.bench_miss_mask >= 0) {
+        const bool miss = hl >= 0 && hl < 30 && (((a.bench_miss_mask >> hl) & 1) != 0);
+        hit = eligible && P > 0 && M > 0 && !miss;
+      } else if (a.bench_exact_quota != 0 && a.bench_hit_rate_std == 0.0f) {
+        const int total = (a.bench_mode == 2) ? a.N * Hkv : a.N * Hq;
+        const int unit = (a.bench_mode == 2) ? n * Hkv + hkv : n * Hq + hq;
+        const int miss_units = bench_target_miss_units(a, total);
+        const int offset = total > 0 ? static_cast<int>(base_key % static_cast<uint32_t>(total)) : 0;
+        int rotated = unit + offset;
+        if (rotated >= total) rotated -= total;
+        hit = eligible && P > 0 && M > 0 && !(rotated < miss_units);
+      } else {
+        const float rate = clampf(__fmaf_rn(a.bench_hit_rate_std,
+                                            pseudo_normal_u32(key ^ 0x4cf5ad43u),
+                                            a.bench_hit_rate), 0.0f, 1.0f);
+        hit = eligible && P > 0 && M > 0 && uniform01_u32(key ^ 0x165667b1u) < rate;
+      }
+      if (hit) {
+        const int max_lag = M < P ? M : P;
+        const int new_end_tmp = cache_end_for_pos(P, S);
+        float lag_f = __fmaf_rn(a.bench_match_lag_std, pseudo_normal_u32(key ^ 0xd3a2646cu),
+                                a.bench_match_lag_mean);
+        bool requested_skip = false;
+        if (a.bench_skip_ratio >= 0.0f) {
+          requested_skip = true;
+          const float skip = clampf(__fmaf_rn(a.bench_skip_ratio_std,
+                                              pseudo_normal_u32(key ^ 0xfd7046c5u),
+                                              a.bench_skip_ratio), 0.0f, 0.999999f);
+          int target = static_cast<int>(roundf(__fmul_rn(skip, static_cast<float>(P))));
+          if (target > new_end_tmp - 1) target = new_end_tmp - 1;
+          if (target < 0) target = 0;
+          lag_f = static_cast<float>(new_end_tmp - target);
+        }
+        int lag = static_cast<int>(roundf(lag_f));
+        if (lag < 1) lag = 1;
+        if (requested_skip) {
+          if (lag > P) lag = P;
+        } else if (lag > max_lag) {
+          lag = max_lag;
+        }
+        if (max_lag <= 0 || new_end_tmp <= 0) {
+          hit = false; bp = INT_MAX; bs = -1;
+        } else {
+          bp = P - lag;
+          if (bp < 0) bp = 0;
+          bs = pos_to_ring_slot(P, M, bp);
+          bd = 0.0f;
+        }
+      } else {
+        bp = INT_MAX; bs = -1; bd = INFINITY;
+      }
+    }
+
+    int prefix_end = 0, rect_start = 0, mpos = -1, mslot = -1;
+    if (hit) {
+      mpos = bp; mslot = bs;
+      prefix_end = cache_end_for_pos(mpos, S);
+      rect_start = prefix_end;
+    }
+    if (hit && p.F > 0 && prefix_end < p.F) {  // DEC.cu:1285-1291
+      hit = false; mpos = -1; mslot = -1; prefix_end = 0; rect_start = 0;
+    }
+    const int new_end = cache_end_for_pos(P, S);
+    // reusable ("valid") head: DEC.cu:1323-1328
+    bool valid = head_lane && hit && mslot >= 0;
+    if (valid) {
+      const float pl = a.lse_cache[(static_cast<int64_t>(req) * M + mslot) * Hq + hq];
+      const int clen = new_end - rect_start;
+      valid = isfinite(pl) && clen >= 0 && clen <= M;
+    }
+    const bool rep = head_lane && sub == 0;  // one representative lane per head
+    const unsigned vmask = __ballot_sync(0xffffffffu, valid && rep);
+    const int vcount = __popc(vmask);
+    int mode = 1;
+    if (vcount == G) mode = 0;
+    else if (vcount > 0 && a.mixed_group_fallback != 0) mode = 2;
+    int fs = p.F < new_end ? p.F : new_end;
+    if (mode != 0 && !(mode == 2 && valid)) {
+      hit = false; mslot = -1; mpos = -1; prefix_end = 0; rect_start = fs;
+    }
+    // group rows
+    int sink_hi = fs < rect_start ? fs : rect_start;   // DEC.cu:725-731
+    int my_lo = head_lane ? rect_start : INT_MAX;
+    int my_sink = head_lane ? sink_hi : 0;
+    for (int off = 16; off > 0; off >>= 1) {
+      my_lo = min(my_lo, __shfl_xor_sync(0xffffffffu, my_lo, off));
+      my_sink = max(my_sink, __shfl_xor_sync(0xffffffffu, my_sink, off));
+    }
+    int band_lo = my_lo;
+    if (band_lo > new_end) band_lo = new_end;
+    if (band_lo < 0) band_lo = 0;
+    if (rep) {
+      const int64_t ho = static_cast<int64_t>(n) * Hq + hq;
+      a.head_hit[ho] = hit ? 1 : 0;
+      a.head_match_slot[ho] = mslot;
+      a.head_match_pos[ho] = mpos;
+      a.head_prefix_end[ho] = prefix_end;
+      a.head_rect_start[ho] = rect_start;
+      a.head_new_end[ho] = new_end;
+    }
+    if (lane == 0) {
+      const int kv_len = P + 1;
+      const int tile = a.tile_tokens > 0 ? a.tile_tokens : 1;
+      const int band_tok = new_end - band_lo;
+      a.group_rect_begin[go] = band_lo;
+      a.group_rect_end[go] = new_end;
+      a.group_rect_tiles[go] = (band_tok + tile - 1) / tile;
+      a.group_tail_begin[go] = new_end;
+      a.group_tail_end[go] = kv_len;
+      a.group_tail_tiles[go] = (kv_len - new_end + tile - 1) / tile;
+      a.group_mode[go] = mode;
+      if (mode != 0) atomicAdd(&a.task_counts[5], 1);
+      if (mode == 1) atomicAdd(&a.task_counts[6], 1);
+      if (mode != 0 && band_tok > tile) atomicAdd(&a.task_counts[3], 1);
+      if (kv_len > new_end) atomicAdd(&a.task_counts[1], 1);
+      plan.sink_hi = my_sink;
+      plan.band_lo = band_lo;
+      plan.new_end = new_end;
+      plan.kv_len = kv_len;
+      plan.mode = mode;
+      plan.bad = 0;
+      plan.cls = (mode == 0) ? 2 : (eligible ? 1 : 0);
+      int cost = 0;
+      if (my_sink > 0) cost += my_sink + kOvhTok;
+      if (band_tok > 0) cost += band_tok + kOvhTok;
+      if (kv_len > new_end) cost += kv_len - new_end + kOvhTok;
+      plan.cost = cost;
+      p.ar.plan[g] = plan;
+    }
+  }
+}
+
+// ---------------------------------------------------------------- phase C
+struct Schedule {
+  uint16_t* gperm;   // [NG] cost-space order -> group id
+  uint32_t* cpre;    // [NG+1] exclusive prefix of group cost in cost-space order
+  uint32_t W;        // total cost
+  uint32_t ps;       // piece size
+  uint32_t pieces;
+};
+
+// Block-wide exclusive scan of one 64-bit value per thread; returns the
+// thread's prefix and the block total.  `warp_tot` is a [kWarps] smem scratch.
+__device__ __forceinline__ unsigned long long block_scan_excl(unsigned long long v,
+                                                              unsigned long long* warp_tot,
+                                                              unsigned long long& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned long long inc = v;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const unsigned long long o = __shfl_up_sync(0xffffffffu, inc, off);
+    if (lane >= off) inc += o;
+  }
+  __syncthreads();
+  if (lane == 31) warp_tot[warp] = inc;
+  __syncthreads();
+  unsigned long long base = 0, tot = 0;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) {
+    const unsigned long long t = warp_tot[w];
+    if (w < warp) base += t;
+    tot += t;
+  }
+  total = tot;
+  return base + inc - v;
+}
+
+// Every CTA derives the same schedule from the group plans: order groups by
+// queue (demoted, miss, hit), prefix-sum their cost, cut into pieces.
+__device__ void build_schedule(const DecodeParams& p, Schedule& sc, unsigned long long* scan_sm) {
+  const int tid = threadIdx.x;
+  const int NG = p.NG;
+  // pass 1: class totals
+  unsigned long long carry = 0;
+  unsigned long long totals = 0;
+  for (int base = 0; base < NG; base += kThreads) {
+    const int g = base + tid;
+    unsigned long long v = 0;
+    if (g < NG) v = 1ull << (21 * __ldcg(&p.ar.plan[g].cls));
+    unsigned long long t;
+    block_scan_excl(v, scan_sm, t);
+    totals += t;
+  }
+  const unsigned t0 = static_cast<unsigned>(totals & 0x1fffffull);
+  const unsigned t1 = static_cast<unsigned>((totals >> 21) & 0x1fffffull);
+  // pass 2: rank inside class -> permutation
+  for (int base = 0; base < NG; base += kThreads) {
+    const int g = base + tid;
+    int cls = 0;
+    unsigned long long v = 0;
+    if (g < NG) {
+      cls = __ldcg(&p.ar.plan[g].cls);
+      v = 1ull << (21 * cls);
+    }
+    unsigned long long t;
+    const unsigned long long ex = block_scan_excl(v, scan_sm, t) + carry;
+    carry += t;
+    if (g < NG) {
+      const unsigned r = static_cast<unsigned>((ex >> (21 * cls)) & 0x1fffffull);
+      const unsigned v_idx = (cls == 0) ? r : (cls == 1 ? t0 + r : t0 + t1 + r);
+      sc.gperm[v_idx] = static_cast<uint16_t>(g);
+    }
+  }
+  __syncthreads();
+  // pass 3: cost prefix in cost-space order
+  unsigned long long ccarry = 0;
+  for (int base = 0; base < NG; base += kThreads) {
+    const int v_idx = base + tid;
+    unsigned long long c = 0;
+    if (v_idx < NG) c = static_cast<unsigned long long>(__ldcg(&p.ar.plan[sc.gperm[v_idx]].cost));
+    unsigned long long t;
+    const unsigned long long ex = block_scan_excl(c, scan_sm, t) + ccarry;
+    ccarry += t;
+    if (v_idx < NG) sc.cpre[v_idx] = static_cast<uint32_t>(ex);
+  }
+  if (tid == 0) sc.cpre[NG] = static_cast<uint32_t>(ccarry);
+  __syncthreads();
+  sc.W = static_cast<uint32_t>(ccarry);
+  // Wave-quantised piece count: as many pieces as keep a piece above
+  // kMinPieceTok, at most two per CTA, and a whole multiple of the grid once
+  // there is at least one piece per CTA.
+  unsigned pieces = sc.W / kMinPieceTok;
+  if (pieces < 1) pieces = 1;
+  if (pieces > 2u * gridDim.x) pieces = 2u * gridDim.x;
+  if (pieces > gridDim.x) pieces = (pieces / gridDim.x) * gridDim.x;
+  if (pieces > static_cast<unsigned>(p.max_pieces)) pieces = p.max_pieces;
+  sc.pieces = pieces;
+  sc.ps = (sc.W + pieces - 1) / pieces;
+  if (sc.ps < 1) sc.ps = 1;
+}
+
+struct RowGeom {
+  int tok_begin;   // first logical position of the row
+  int len;         // tokens
+  uint32_t a;      // start of the row in cost space
+  uint32_t c;      // cost of the row (0 if empty)
+};
+
+__device__ __forceinline__ void group_rows(const GroupPlan& pl, uint32_t a0, RowGeom (&rows)[3]) {
+  rows[0].tok_begin = 0;          rows[0].len = pl.sink_hi;
+  rows[1].tok_begin = pl.band_lo; rows[1].len = pl.new_end - pl.band_lo;
+  rows[2].tok_begin = pl.new_end; rows[2].len = pl.kv_len - pl.new_end;
+  uint32_t a = a0;
+#pragma unroll
+  for (int r = 0; r < 3; ++r) {
+    if (rows[r].len < 0) rows[r].len = 0;
+    rows[r].a = a;
+    rows[r].c = rows[r].len > 0 ? static_cast<uint32_t>(rows[r].len + kOvhTok) : 0u;
+    a += rows[r].c;
+  }
+}
+
+// Token sub-range of a row that falls into cost interval [x0, x1).  The first
+// kOvhTok cost units of a row stand for the fixed cost of opening it; cut
+// points are rounded down to whole 16-token blocks so neighbours agree.
+__device__ __forceinline__ void segment_tokens(const RowGeom& row, uint32_t x0, uint32_t x1,
+                                               int& lo, int& hi) {
+  const uint32_t end = row.a + row.c;
+  int l = 0, h = row.len;
+  if (x0 > row.a) {
+    const int rel = static_cast<int>(x0 - row.a) - kOvhTok;
+    l = rel > 0 ? (rel & ~(kBlkTok - 1)) : 0;
+  }
+  if (x1 < end) {
+    const int rel = static_cast<int>(x1 - row.a) - kOvhTok;
+    h = rel > 0 ? (rel & ~(kBlkTok - 1)) : 0;
+  }
+  if (h > row.len) h = row.len;
+  if (l > h) l = h;
+  lo = row.tok_begin + l;
+  hi = row.tok_begin + h;
+}
+
+__device__ __forceinline__ void row_piece_span(const RowGeom& row, uint32_t ps, int& p_lo,
+                                               int& p_hi) {
+  p_lo = static_cast<int>(row.a / ps);
+  p_hi = static_cast<int>((row.a + row.c - 1) / ps);
+}
+
+// Streams logical positions [t0, t1) of request n through KV head hkv for the
+// G query heads of the group and leaves the normalised partial (o, natural-log
+// LSE) of every head in arena slot `slot`.  `row_kind`: 0 sink, 1 band, 2 tail
+// (decides each head's own sub-range inside [t0, t1)).
+__device__ void attend_segment(const DecodeParams& p, uint8_t* smem, int n, int hkv, int t0,
+                               int t1, int row_kind, int slot) {
+  const MacB200DecodeArgs& a = p.a;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int G = p.G;
+  const int req = a.req_ids[n], P = a.past_lens[n];
+  const int hrow = lane >> 2, quad = lane & 3;
+  const bool has_head = hrow < G;
+  const int hq = hkv * G + (has_head ? hrow : 0);
+
+  // this head's own range inside the segment
+  int lo = t0, hi = t1;
+  if (has_head) {
+    const int rs = __ldcg(a.head_rect_start + static_cast<int64_t>(n) * a.Hq + hq);
+    if (row_kind == 1) {
+      lo = max(t0, rs);
+    } else if (row_kind == 0) {
+      const int ne = cache_end_for_pos(P, a.semantic_pos_ahead);
+      int sh = p.F < ne ? p.F : ne;
+      if (sh > rs) sh = rs;
+      hi = min(t1, sh);
+    }
+  } else {
+    hi = lo;  // padded rows see nothing
+  }
+
+  // Q fragments: rows = heads of the group, 8 K-steps of 16 dims
+  uint32_t qa0[8], qa2[8];
+  {
+    const uint32_t* qrow = reinterpret_cast<const uint32_t*>(
+        static_cast<const char*>(a.q_post) + (static_cast<int64_t>(n) * a.Hq + hq) * kRowBytes);
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      qa0[kk] = has_head ? __ldg(qrow + kk * 8 + quad) : 0u;
+      qa2[kk] = has_head ? __ldg(qrow + kk * 8 + 4 + quad) : 0u;
+    }
+  }
+
+  float oacc[16][4];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) { oacc[j][0] = oacc[j][1] = oacc[j][2] = oacc[j][3] = 0.0f; }
+  float m_run = -INFINITY, l_run = 0.0f;
+
+  const int nblk = (t1 - t0 + kBlkTok - 1) / kBlkTok;
+  const int mine = warp < nblk ? (nblk - warp + kWarps - 1) / kWarps : 0;
+  uint8_t* ring = smem + warp * kWarpRingBytes;
+  const uint32_t ring_u32 = smem_u32(ring);
+  const char* kbase = static_cast<const char*>(a.k_buffer) + static_cast<int64_t>(hkv) * kRowBytes;
+  const char* vbase = static_cast<const char*>(a.v_buffer) + static_cast<int64_t>(hkv) * kRowBytes;
+  const int64_t tok_stride = static_cast<int64_t>(a.Hkv) * kRowBytes;
+  const int32_t* table = a.req_to_token + static_cast<int64_t>(req) * a.req_to_token_stride;
+
+  // pool row of the lane's token (lanes 0..15) of this warp's j-th block; -1 = past the end
+  auto load_token = [&](int j) -> int64_t {
+    const int pos = t0 + (warp + j * kWarps) * kBlkTok + (lane & 15);
+    if (pos >= t1) return -1;
+    if (pos == P) {
+      return a.out_cache_loc_is_i64
+                 ? static_cast<int64_t>(static_cast<const int64_t*>(a.out_cache_loc)[n])
+                 : static_cast<int64_t>(static_cast<const int32_t*>(a.out_cache_loc)[n]);
+    }
+    return static_cast<int64_t>(__ldg(table + pos));
+  };
+  auto issue_block = [&](int j, int64_t tok_reg) {
+    const uint32_t st = ring_u32 + (j % kStages) * kStageBytes;
+    const int chunk = lane & 15;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = (lane >> 4) + 2 * i;
+      const int64_t tok = __shfl_sync(0xffffffffu, tok_reg, r);
+      const bool ok = tok >= 0;
+      const int64_t off = (ok ? tok : 0) * tok_stride + chunk * 16;
+      const uint32_t dst = st + r * kRowBytes + ((chunk ^ (r & 7)) << 4);
+      cp_async16(dst, kbase + off, ok ? 16 : 0);
+      cp_async16(dst + kBlkTok * kRowBytes, vbase + off, ok ? 16 : 0);
+    }
+  };
+
+  int64_t tok_next = -1;
+#pragma unroll
+  for (int j = 0; j < kStages - 1; ++j) {
+    if (j < mine) issue_block(j, load_token(j));
+    cp_async_commit();
+  }
+  if (kStages - 1 < mine) tok_next = load_token(kStages - 1);
+
+  for (int j = 0; j < mine; ++j) {
+    cp_async_wait<kStages - 2>();
+    __syncwarp();
+    const uint32_t kst = ring_u32 + (j % kStages) * kStageBytes;
+    const uint32_t vst = kst + kBlkTok * kRowBytes;
+    const int tb = t0 + (warp + j * kWarps) * kBlkTok;
+
+    // S = Q K^T for 16 tokens: two n-blocks of 8 tokens
+    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+    {
+      const int mi = lane >> 3;
+      const int r = ((mi >> 1) << 3) + (lane & 7);
+      const uint32_t row_addr = kst + r * kRowBytes;
+      const int rx = r & 7;
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        const int chunk = 2 * kk + (mi & 1);
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(row_addr + ((chunk ^ rx) << 4), b0, b1, b2, b3);
+        mma_bf16_rows8(s0, qa0[kk], qa2[kk], b0, b1);
+        mma_bf16_rows8(s1, qa0[kk], qa2[kk], b2, b3);
+      }
+    }
+    // online softmax in the log2 domain
+    const int pos0 = tb + quad * 2;
+    float sv[4];
+    sv[0] = (pos0 >= lo && pos0 < hi) ? s0[0] * p.scale_log2 : -INFINITY;
+    sv[1] = (pos0 + 1 >= lo && pos0 + 1 < hi) ? s0[1] * p.scale_log2 : -INFINITY;
+    sv[2] = (pos0 + 8 >= lo && pos0 + 8 < hi) ? s1[0] * p.scale_log2 : -INFINITY;
+    sv[3] = (pos0 + 9 >= lo && pos0 + 9 < hi) ? s1[1] * p.scale_log2 : -INFINITY;
+    float mx = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m_run, mx);
+    const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
+    const float alpha = ex2(m_run - m_use);
+    const float p0 = ex2(sv[0] - m_use), p1 = ex2(sv[1] - m_use);
+    const float p2 = ex2(sv[2] - m_use), p3 = ex2(sv[3] - m_use);
+    l_run = l_run * alpha + ((p0 + p1) + (p2 + p3));
+    m_run = m_new;
+#pragma unroll
+    for (int jj = 0; jj < 16; ++jj) { oacc[jj][0] *= alpha; oacc[jj][1] *= alpha; }
+    const uint32_t pa0 = pack_bf16x2(p0, p1);
+    const uint32_t pa2 = pack_bf16x2(p2, p3);
+    // O += P V
+    {
+      const int mi = lane >> 3;
+      const int r = ((mi & 1) << 3) + (lane & 7);
+      const uint32_t row_addr = vst + r * kRowBytes;
+      const int rx = r & 7;
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj) {
+        const int chunk = 2 * jj + (mi >> 1);
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(row_addr + ((chunk ^ rx) << 4), b0, b1, b2, b3);
+        mma_bf16_rows8(oacc[2 * jj], pa0, pa2, b0, b1);
+        mma_bf16_rows8(oacc[2 * jj + 1], pa0, pa2, b2, b3);
+      }
+    }
+    __syncwarp();
+    const int jn = j + kStages - 1;
+    if (jn < mine) issue_block(jn, tok_next);
+    cp_async_commit();
+    if (jn + 1 < mine) tok_next = load_token(jn + 1);
+  }
+  cp_async_wait<0>();
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+
+  // cross-warp combine through shared memory (the K/V ring is idle now)
+  __syncthreads();
+  float* comb_o = reinterpret_cast<float*>(smem);                    // [kWarps][8][kCombineRow]
+  float* comb_m = comb_o + kWarps * 8 * kCombineRow;                 // [kWarps][8]
+  float* comb_l = comb_m + kWarps * 8;
+  {
+    float* dst = comb_o + (warp * 8 + hrow) * kCombineRow + quad * 2;
+#pragma unroll
+    for (int jj = 0; jj < 16; ++jj)
+      *reinterpret_cast<float2*>(dst + jj * 8) = make_float2(oacc[jj][0], oacc[jj][1]);
+    if (quad == 0) {
+      comb_m[warp * 8 + hrow] = m_run;
+      comb_l[warp * 8 + hrow] = l_run;
+    }
+  }
+  __syncthreads();
+  if (warp < G) {
+    const int h = warp;  // warp h finalises head h; lane owns dims [4*lane, 4*lane+4)
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, comb_m[w * 8 + h]);
+    float lsum = 0.0f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (mx != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        const float wgt = ex2(comb_m[w * 8 + h] - mx);
+        lsum += comb_l[w * 8 + h] * wgt;
+        const float4 o = *reinterpret_cast<const float4*>(comb_o + (w * 8 + h) * kCombineRow + lane * 4);
+        acc.x += o.x * wgt; acc.y += o.y * wgt; acc.z += o.z * wgt; acc.w += o.w * wgt;
+      }
+    }
+    float lse = -INFINITY;
+    if (lsum > 0.0f) {
+      const float inv = 1.0f / lsum;
+      acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+      lse = (mx + lg2(lsum)) * kLn2;
+    } else {
+      acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float* po = p.ar.part_o + (static_cast<int64_t>(slot) * G + h) * kD + lane * 4;
+    __stcg(reinterpret_cast<float4*>(po), acc);
+    if (lane == 0) __stcg(p.ar.part_lse + static_cast<int64_t>(slot) * 8 + h, lse);
+  }
+  __syncthreads();  // combine buffer is free again
+}
+
+// LSE merge of (o, lse) with another partial; natural log (DEC.cu:866-890).
+__device__ __forceinline__ void merge_state(float4& o, float& lse, const float4& o2, float lse2) {
+  if (!isfinite(lse2)) return;
+  if (!isfinite(lse)) {
+    o = o2;
+    lse = lse2;
+    return;
+  }
+  const float m = fmaxf(lse, lse2);
+  const float es = expf(lse - m), eo = expf(lse2 - m);
+  const float den = es + eo;
+  const float ws = es / den, wo = eo / den;
+  o.x = ws * o.x + wo * o2.x; o.y = ws * o.y + wo * o2.y;
+  o.z = ws * o.z + wo * o2.z; o.w = ws * o.w + wo * o2.w;
+  lse = m + logf(den);
+}
+
+// Runs in the CTA that retired the group's last segment: prefix state (+) band
+// partials -> ring row; (+) sink (+) tail partials -> output.  Warp h owns
+// head h, lane owns 4 dims.  Order of operations: DEC.cu:4346-4365, 4485-4520.
+__device__ void merge_group(const DecodeParams& p, const Schedule& sc, int v_idx, int g,
+                            const GroupPlan& pl) {
+  const MacB200DecodeArgs& a = p.a;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (warp >= p.G) return;
+  const int G = p.G, Hq = a.Hq, M = a.M;
+  const int n = g / a.Hkv, hkv = g - n * a.Hkv;
+  const int hq = hkv * G + warp;
+  const int64_t ho = static_cast<int64_t>(n) * Hq + hq;
+  const int req = a.req_ids[n], P = a.past_lens[n];
+  RowGeom rows[3];
+  group_rows(pl, sc.cpre[v_idx], rows);
+
+  float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+  float lse = -INFINITY;
+  const int hit = __ldcg(a.head_hit + ho);
+  const int mslot = __ldcg(a.head_match_slot + ho);
+  if (hit != 0 && mslot >= 0) {
+    const int64_t row = (static_cast<int64_t>(req) * M + mslot) * Hq + hq;
+    const float pl_lse = a.lse_cache[row];
+    if (isfinite(pl_lse)) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(
+          static_cast<const char*>(a.attn_cache) + row * kRowBytes + lane * 8);
+      o = make_float4(bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y));
+      lse = pl_lse;
+    }
+  }
+  auto merge_row = [&](int r) {
+    if (rows[r].c == 0) return;
+    int p_lo, p_hi;
+    row_piece_span(rows[r], sc.ps, p_lo, p_hi);
+    for (int pc = p_lo; pc <= p_hi; ++pc) {
+      const int64_t slot = static_cast<int64_t>(pc) + 3 * v_idx + r;
+      const float l2 = __ldcg(p.ar.part_lse + slot * 8 + warp);
+      if (!isfinite(l2)) continue;
+      const float4 o2 = __ldcg(reinterpret_cast<const float4*>(
+          p.ar.part_o + (slot * G + warp) * kD + lane * 4));
+      merge_state(o, lse, o2, l2);
+    }
+  };
+  merge_row(1);
+  // ring row of this step, only for requests whose cache is ready
+  if (request_ready(a, req)) {
+    const int dest = P % M;
+    const int64_t row = (static_cast<int64_t>(req) * M + dest) * Hq + hq;
+    const bool ok = isfinite(lse);
+    const uint2 qv = *reinterpret_cast<const uint2*>(static_cast<const char*>(a.q_pre) +
+                                                     ho * kRowBytes + lane * 8);
+    *reinterpret_cast<uint2*>(static_cast<char*>(a.query_cache) + row * kRowBytes + lane * 8) = qv;
+    uint2 ov = make_uint2(0u, 0u);
+    if (ok) {
+      ov.x = pack_bf16x2(o.x, o.y);
+      ov.y = pack_bf16x2(o.z, o.w);
+    }
+    *reinterpret_cast<uint2*>(static_cast<char*>(a.attn_cache) + row * kRowBytes + lane * 8) = ov;
+    if (lane == 0) a.lse_cache[row] = ok ? lse : -INFINITY;
+  }
+  merge_row(0);
+  merge_row(2);
+  {
+    const bool ok = isfinite(lse);
+    uint2 ov = make_uint2(0u, 0u);
+    if (ok) {
+      ov.x = pack_bf16x2(o.x, o.y);
+      ov.y = pack_bf16x2(o.z, o.w);
+    }
+    *reinterpret_cast<uint2*>(static_cast<char*>(a.out) + ho * kRowBytes + lane * 8) = ov;
+    if (lane == 0 && a.optional_lse) a.optional_lse[ho] = ok ? lse : -INFINITY;
+  }
+}
+
+__device__ void phase_attend(const DecodeParams& p, uint8_t* smem) {
+  __shared__ unsigned long long scan_sm[kWarps];
+  __shared__ int sh_piece;
+  __shared__ int sh_last;
+  Schedule sc;
+  sc.gperm = reinterpret_cast<uint16_t*>(smem + kRingBytes);
+  sc.cpre = reinterpret_cast<uint32_t*>(smem + kRingBytes + kSmemPerm);
+  build_schedule(p, sc, scan_sm);
+  const int tid = threadIdx.x;
+  const int NG = p.NG;
+  if (blockIdx.x == 0 && tid == 0) {
+    p.a.task_counts[4] = static_cast<int32_t>(sc.ps);
+    p.a.task_counts[0] = static_cast<int32_t>(sc.pieces);
+  }
+  if (sc.W == 0) return;
+
+  for (;;) {
+    __syncthreads();
+    if (tid == 0) sh_piece = static_cast<int>(atomicAdd(p.ar.ticket, 1u));
+    __syncthreads();
+    const int piece = sh_piece;
+    if (piece >= static_cast<int>(sc.pieces)) break;
+    const uint32_t x0 = static_cast<uint32_t>(piece) * sc.ps;
+    uint32_t x1 = x0 + sc.ps;
+    if (x1 > sc.W) x1 = sc.W;
+    if (x0 >= x1) continue;
+    // first group whose cost range ends after x0
+    int lo = 0, hi = NG;  // find smallest v with cpre[v+1] > x0
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (sc.cpre[mid + 1] > x0) hi = mid; else lo = mid + 1;
+    }
+    for (int v = lo; v < NG && sc.cpre[v] < x1; ++v) {
+      if (sc.cpre[v + 1] == sc.cpre[v]) continue;  // empty group (malformed row)
+      const int g = sc.gperm[v];
+      GroupPlan pl;
+      {
+        const int4* src = reinterpret_cast<const int4*>(&p.ar.plan[g]);
+        const int4 w0 = __ldcg(src), w1 = __ldcg(src + 1);
+        pl.sink_hi = w0.x; pl.band_lo = w0.y; pl.new_end = w0.z; pl.kv_len = w0.w;
+        pl.cls = w1.x; pl.cost = w1.y; pl.mode = w1.z; pl.bad = w1.w;
+      }
+      const int n = g / p.a.Hkv, hkv = g - n * p.a.Hkv;
+      RowGeom rows[3];
+      group_rows(pl, sc.cpre[v], rows);
+      int expected = 0, done_here = 0;
+#pragma unroll 1
+      for (int r = 0; r < 3; ++r) {
+        if (rows[r].c == 0) continue;
+        int p_lo, p_hi;
+        row_piece_span(rows[r], sc.ps, p_lo, p_hi);
+        expected += p_hi - p_lo + 1;
+        if (piece < p_lo || piece > p_hi) continue;
+        int t0, t1;
+        segment_tokens(rows[r], x0, x1, t0, t1);
+        const int slot = piece + 3 * v + r;
+        if (slot < p.ar.slots) {
+          attend_segment(p, smem, n, hkv, t0, t1, r, slot);
+        } else if (tid == 0) {
+          atomicOr(&g_status, MAC_B200_STATUS_SCHED_OVERFLOW);
+        }
+        done_here += 1;
+      }
+      if (done_here == 0) continue;
+      // publish partials, then count this CTA's segments against the group
+      __threadfence();
+      __syncthreads();
+      if (tid == 0) {
+        const int prev = atomicAdd(&p.ar.garrive[g], done_here);
+        sh_last = (prev + done_here == expected) ? 1 : 0;
+      }
+      __syncthreads();
+      if (sh_last) {
+        __threadfence();
+        merge_group(p, sc, v, g, pl);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------- kernel
+__device__ __forceinline__ long long global_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+mac_decode_persistent_kernel(const DecodeParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const bool stamp = p.a.debug_enabled >= 2 && blockIdx.x == 0 && threadIdx.x == 0;
+  if (stamp) p.a.phase_cycles[0] = global_ns();
+  phase_match_scan(p, smem);
+  if (!grid_barrier(gridDim.x)) return;
+  if (stamp) p.a.phase_cycles[1] = global_ns();
+  phase_classify(p);
+  if (!grid_barrier(gridDim.x)) return;
+  if (stamp) p.a.phase_cycles[2] = global_ns();
+  phase_attend(p, smem);
+  if (stamp) {
+    const long long t = global_ns();
+    for (int i = 3; i < p.a.phase_cycles_count; ++i) p.a.phase_cycles[i] = t;
+  }
+}
+
+// --------------------------------------------------------------- host state
+struct DeviceState {
+  bool ready = false;
+  int sm_count = 0;
+  int ctas_per_sm = 0;
+  int regs = 0;
+  int last_grid = 0;
+  void* arena = nullptr;
+  size_t arena_bytes = 0;
+};
+std::mutex g_mu;
+DeviceState g_dev[64];
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct ArenaLayout {
+  size_t ticket, garrive, plan, part_lse, part_o, total;
+  int slots;
+};
+ArenaLayout arena_layout(int NG, int G, int max_pieces) {
+  ArenaLayout L;
+  L.slots = max_pieces + 3 * NG;
+  size_t off = 0;
+  L.ticket = off; off = align_up(off + 64, 256);
+  L.garrive = off; off = align_up(off + sizeof(int32_t) * NG, 256);
+  L.plan = off; off = align_up(off + sizeof(GroupPlan) * NG, 256);
+  L.part_lse = off; off = align_up(off + sizeof(float) * 8 * L.slots, 256);
+  L.part_o = off; off = align_up(off + sizeof(float) * static_cast<size_t>(L.slots) * G * kD, 256);
+  L.total = off;
+  return L;
+}
+
+}  // namespace
+}  // namespace mac_b200
+
+using namespace mac_b200;
+
+extern "C" int mac_b200_persistent_decode_bf16(const MacB200DecodeArgs* args, void* stream_v) {
+  MAC_REQUIRE(args != nullptr, "decode args must not be null");
+  const MacB200DecodeArgs& a = *args;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  // Shape rules of the reference launcher (mac_decode_persistent.cu:5080-5153).
+  MAC_REQUIRE(a.D == kD, "persistent decode supports D=128 only");
+  MAC_REQUIRE(a.Hkv > 0 && a.Hq > 0 && a.Hq % a.Hkv == 0, "Hq must be divisible by Hkv");
+  const int G = a.Hq / a.Hkv;
+  MAC_REQUIRE(G > 0 && G <= 8, "unsupported GQA group size");
+  MAC_REQUIRE(a.N >= 0, "negative batch");
+  MAC_REQUIRE(a.M > 0 && a.R > 0, "ring tensors must not be empty");
+  MAC_REQUIRE(a.match_tile_slots > 0, "match_tile_slots must be positive");
+  MAC_REQUIRE(a.max_match_tiles >= (a.M + a.match_tile_slots - 1) / a.match_tile_slots,
+              "match workspace too small");
+  MAC_REQUIRE(a.ws_batch >= a.N, "decision workspaces are smaller than the batch");
+  MAC_REQUIRE(a.bench_mode == 0 || a.bench_mode == 1 || a.bench_mode == 2,
+              "unsupported synthetic MAC bench mode");
+  MAC_REQUIRE(a.phase_cycles_count >= 6 && a.phase_cycles, "phase_cycles must have at least 6 elements");
+  MAC_REQUIRE(a.q_post && a.q_pre && a.k_buffer && a.v_buffer && a.req_to_token && a.req_ids &&
+                  a.past_lens && a.out_cache_loc && a.query_cache && a.attn_cache && a.lse_cache &&
+                  a.out,
+              "input/output tensors must not be null");
+  MAC_REQUIRE(a.match_dist && a.match_pos && a.match_slot && a.head_hit && a.head_match_slot &&
+                  a.head_match_pos && a.head_prefix_end && a.head_rect_start && a.head_new_end &&
+                  a.group_rect_begin && a.group_rect_end && a.group_rect_tiles &&
+                  a.group_tail_begin && a.group_tail_end && a.group_tail_tiles && a.group_mode &&
+                  a.task_counts,
+              "workspace tensors must not be null");
+  if (a.N == 0) return MAC_B200_OK;
+  if (a.Hq > kMaxHq)
+    return fail(MAC_B200_EUNSUPPORTED, "Hq=%d exceeds this build's limit of %d", a.Hq, kMaxHq);
+  const long long NGll = static_cast<long long>(a.N) * a.Hkv;
+  if (NGll > kMaxGroups)
+    return fail(MAC_B200_EUNSUPPORTED, "N*Hkv=%lld exceeds this build's limit of %d", NGll,
+                kMaxGroups);
+
+  int device = 0;
+  MAC_CUDA(cudaGetDevice(&device));
+  MAC_REQUIRE(device >= 0 && device < 64, "device index out of range");
+  DeviceState st;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    DeviceState& ds = g_dev[device];
+    if (!ds.ready) {
+      int coop = 0;
+      MAC_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device));
+      if (!coop) return fail(MAC_B200_EUNSUPPORTED, "device does not support cooperative launch");
+      MAC_CUDA(cudaFuncSetAttribute(mac_decode_persistent_kernel,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+      MAC_CUDA(cudaDeviceGetAttribute(&ds.sm_count, cudaDevAttrMultiProcessorCount, device));
+      MAC_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+          &ds.ctas_per_sm, mac_decode_persistent_kernel, kThreads, kSmemBytes));
+      if (ds.ctas_per_sm < 1) return fail(MAC_B200_ECUDA, "decode kernel has zero occupancy");
+      cudaFuncAttributes fa{};
+      MAC_CUDA(cudaFuncGetAttributes(&fa, mac_decode_persistent_kernel));
+      ds.regs = fa.numRegs;
+      ds.ready = true;
+    }
+    int grid = ds.sm_count * ds.ctas_per_sm;
+    if (a.grid_cap > 0 && a.grid_cap < grid) grid = a.grid_cap;
+    const int max_pieces = 2 * grid;
+    const ArenaLayout L = arena_layout(static_cast<int>(NGll), G, max_pieces);
+    if (L.total > ds.arena_bytes) {
+      cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+      MAC_CUDA(cudaStreamIsCapturing(stream, &cs));
+      if (cs != cudaStreamCaptureStatusNone)
+        return fail(MAC_B200_ECAPTURE,
+                    "scratch arena must grow to %zu bytes but the stream is being captured; "
+                    "run one eager call with this shape first", L.total);
+      // Launches still in flight may be using the old arena.
+      MAC_CUDA(cudaDeviceSynchronize());
+      if (ds.arena) MAC_CUDA(cudaFree(ds.arena));
+      ds.arena = nullptr;
+      ds.arena_bytes = 0;
+      const size_t want = align_up(L.total + L.total / 4, 1 << 20);
+      MAC_CUDA(cudaMalloc(&ds.arena, want));
+      ds.arena_bytes = want;
+    }
+    ds.last_grid = grid;
+    st = ds;
+  }
+
+  DecodeParams p;
+  p.a = a;
+  p.G = G;
+  p.NG = static_cast<int>(NGll);
+  p.F = a.front_sink_tokens > 0 ? a.front_sink_tokens : 0;
+  p.tm_used = (a.M + a.match_tile_slots - 1) / a.match_tile_slots;
+  p.max_pieces = 2 * st.last_grid;
+  {
+    float t = 2.0f * static_cast<float>(a.D);   // mac_decode_persistent.cu:5342, in float
+    t = t * (1.0f - a.threshold);
+    t = t * (1.0f - a.threshold);
+    p.thr_dist = t;
+  }
+  p.scale_log2 = a.sm_scale * kLog2e;
+  const ArenaLayout L = arena_layout(p.NG, G, p.max_pieces);
+  char* base = static_cast<char*>(st.arena);
+  p.ar.ticket = reinterpret_cast<uint32_t*>(base + L.ticket);
+  p.ar.garrive = reinterpret_cast<int32_t*>(base + L.garrive);
+  p.ar.plan = reinterpret_cast<GroupPlan*>(base + L.plan);
+  p.ar.part_lse = reinterpret_cast<float*>(base + L.part_lse);
+  p.ar.part_o = reinterpret_cast<float*>(base + L.part_o);
+  p.ar.slots = L.slots;
+
+  void* kargs[] = {&p};
+  static const bool plain = [] {
+    const char* e = std::getenv("MAC_B200_PLAIN_LAUNCH");
+    return e && std::atoi(e) != 0;
+  }();
+  if (plain) {
+    mac_decode_persistent_kernel<<<st.last_grid, kThreads, kSmemBytes, stream>>>(p);
+    MAC_CUDA(cudaGetLastError());
+  } else {
+    MAC_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(mac_decode_persistent_kernel),
+                                         dim3(st.last_grid), dim3(kThreads), kargs, kSmemBytes,
+                                         stream));
+  }
+  g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+  return MAC_B200_OK;
+}
+
+extern "C" int mac_b200_query_status(uint32_t* status_out, void* stream_v) {
+  MAC_REQUIRE(status_out != nullptr, "status_out must not be null");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  MAC_CUDA(cudaStreamSynchronize(stream));
+  unsigned v = 0;
+  MAC_CUDA(cudaMemcpyFromSymbol(&v, g_status, sizeof(v)));
+  *status_out = v;
+  if (v != 0) {
+    const unsigned zero = 0;
+    MAC_CUDA(cudaDeviceSynchronize());
+    MAC_CUDA(cudaMemcpyToSymbol(g_status, &zero, sizeof(zero)));
+    if (v & MAC_B200_STATUS_BARRIER_TIMEOUT) {
+      MAC_CUDA(cudaMemcpyToSymbol(g_bar_count, &zero, sizeof(zero)));
+    }
+  }
+  return MAC_B200_OK;
+}
+
+extern "C" int mac_b200_launch_info(MacB200LaunchInfo* info) {
+  MAC_REQUIRE(info != nullptr, "info must not be null");
+  int device = 0;
+  MAC_CUDA(cudaGetDevice(&device));
+  MAC_REQUIRE(device >= 0 && device < 64, "device index out of range");
+  std::lock_guard<std::mutex> lock(g_mu);
+  const DeviceState& ds = g_dev[device];
+  info->sm_count = ds.sm_count;
+  info->ctas_per_sm = ds.ctas_per_sm;
+  info->block_threads = kThreads;
+  info->dynamic_smem_bytes = kSmemBytes;
+  info->regs_per_thread = ds.regs;
+  info->last_grid = ds.last_grid;
+  info->arena_bytes = static_cast<int64_t>(ds.arena_bytes);
+  info->kernel_launches = g_kernel_launches.load(std::memory_order_relaxed);
+  return MAC_B200_OK;
+}
