@@ -1,0 +1,524 @@
+#!/usr/bin/env python3
+"""Benchmark of the fused MAC decode step (one JSON line on stdout).
+
+Metric: microseconds per decode step under CUDA-graph replay, with the
+algorithmic HBM GB/s it corresponds to, on the reference's headline workload:
+GQA-4 (Hq 32 / Hkv 8 / D 128), bf16 paged KV (page 16), batch 64, context
+126976, ring capacity 2048, semantic_pos_ahead 256, per-query-head hit fraction
+0.9 chosen by the reference's own synthetic decision hash (its published curves
+were measured the same way), match lag 64.  Inputs are seeded synthetic tensors
+of those shapes (``mac_attention_b200/synth.py``).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W]           this library
+    python bench.py --impl reference ...                           CPU baseline arm
+    python bench.py --sweep ...                                    hit/batch/context table
+
+With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank
+owns its own requests, KV pool and ring (the path shards by request with no
+collective inside attention); the step time is the max over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+HQ, HKV, DIM = 32, 8, 128
+CAPACITY, SEM, TILE, MTS, MAX_CONTEXT = 2048, 256, 32, 32, 131072
+LAG = 64
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--ctx", type=int, default=126976)
+    ap.add_argument("--hit", type=float, default=0.9)
+    ap.add_argument("--hq", type=int, default=HQ)
+    ap.add_argument("--hkv", type=int, default=HKV)
+    ap.add_argument("--front-sink", type=int, default=0)
+    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--capacity", type=int, default=CAPACITY)
+    ap.add_argument("--bench-mode", type=int, default=1)
+    ap.add_argument("--sweep", action="store_true", help="write the hit/batch/context table")
+    ap.add_argument("--sweep-out", default=str(ROOT / "gpurun_out" / "sweep.json"))
+    ap.add_argument("--baselines", default="", help="comma list for --sweep: flashinfer,refkernel")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-sample-requests", type=int, default=4)
+    ap.add_argument("--shard", default="request", choices=["request", "kv_head"])
+    return ap.parse_args()
+
+
+# --------------------------------------------------------------------------- workload
+def alg_bytes(ws, batch, hq, hkv, F, capacity, past_lens, eligible=True):
+    """Algorithmic bytes of one step from the decision arrays the kernel reports:
+    K/V rows actually needed (512 B per token and KV head), the ring scan (full
+    256 B rows of every candidate slot), reused prefix states, ring write,
+    output, queries and the page-table entries."""
+    import torch
+
+    from mac_attention_b200 import workspace as W
+
+    head_hit = ws[W.HEAD_HIT][:batch].cpu()
+    head_rect = ws[W.HEAD_RECT_START][:batch].cpu()
+    new_end = ws[W.HEAD_NEW_END][:batch].cpu()
+    mode = ws[W.GROUP_MODE][:batch].cpu()
+    G = hq // hkv
+    kv = 0
+    pt = 0
+    for n in range(batch):
+        P = int(past_lens[n])
+        kv_len = P + 1
+        ne = int(new_end[n, 0])
+        distinct = 0
+        for g in range(hkv):
+            if int(mode[n, g]) != 0:
+                t = kv_len
+            else:
+                lo = int(head_rect[n, g * G:(g + 1) * G].min())
+                t = min(F, lo) + (ne - lo) + (kv_len - ne)
+            kv += t * 512
+            distinct = max(distinct, t)
+        pt += 4 * distinct
+    scan = sum(min(capacity, int(p)) for p in past_lens) * hq * 256 if eligible else 0
+    hits = int(head_hit.sum())
+    heads = batch * hq
+    total = kv + scan + hits * 260 + heads * 516 + heads * 256 + heads * 512 + pt
+    return dict(total=total, kv=kv, scan=scan, hit_heads=hits,
+                non_hit_groups=int((mode != 0).sum()), full_groups=int((mode == 1).sum()))
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle samples of one GPU while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.path = None
+
+    def __enter__(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms",
+                 "100", "-i", str(self.index)], stdout=f, stderr=subprocess.DEVNULL)
+        except Exception:  # noqa: BLE001
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:  # noqa: BLE001
+                self.proc.kill()
+
+    def summary(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if not self.path or not os.path.exists(self.path):
+            return out
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            sm.sort()
+            out.update(sm_mhz=sm[len(sm) // 2], sm_max_mhz=max(mx), samples=len(sm))
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def build_case(args, device, seed, batch, ctx, hq, hkv):
+    from mac_attention_b200 import synth
+
+    case = synth.make_decode_case(batch=batch, ctx=ctx, hq=hq, hkv=hkv, capacity=args.capacity,
+                                  page_size=args.page_size, seed=seed, device=device,
+                                  sink_boost=64 if args.front_sink > 0 else 0)
+    return case
+
+
+def make_launch(ext, case, ws, scal, out, lse):
+    import torch
+
+    e = torch.empty(0)
+
+    def launch():
+        ext.mac_persistent_decode_bf16(
+            case.q_post, case.q_pre, case.k, case.v, case.req_to_token, case.req_ids,
+            case.past_lens, case.out_cache_loc, case.query_cache, case.attn_cache, case.lse_cache,
+            out, lse, *ws, *scal, case.query_cache, e, e, e)
+    return launch
+
+
+def scalars(args, hit):
+    """The operator's 21 scalars in positional order (reference benchmark defaults)."""
+    return (MAX_CONTEXT, TILE, MTS, SEM, args.front_sink, 0, 0, 0, 0.45, 1.0 / math.sqrt(DIM),
+            0, args.bench_mode, hit, 0.0, -1.0, 0.0, float(LAG), 0.0, 1, -1, 0)
+
+
+def time_graph(launch, steps, warmup, barrier=None):
+    """Mean ms per replay of a CUDA graph holding one step, CUDA events on the
+    capturing stream's replay stream."""
+    import torch
+
+    for _ in range(3):
+        launch()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        launch()
+    for _ in range(max(warmup, 3)):
+        graph.replay()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        graph.replay()
+    t1.record()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    return t0.elapsed_time(t1) / steps, graph
+
+
+def run_ours(args):
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+
+    from mac_attention_b200 import load_mac_persistent_decode_extension, make_decode_workspace
+    from mac_attention_b200 import ops, sharding
+
+    ext = load_mac_persistent_decode_extension()
+    hq, hkv, batch = args.hq, args.hkv, args.batch
+    if args.shard == "kv_head" and world > 1:
+        q_sl, kv_sl = sharding.head_slices(hq, hkv, world, rank)
+        hq, hkv = q_sl.stop - q_sl.start, kv_sl.stop - kv_sl.start
+        seed = 1000
+    else:
+        seed = 1000 + rank
+    case = build_case(args, dev, seed, batch, args.ctx, hq, hkv)
+    ws = make_decode_workspace(batch, hq, hkv, args.capacity, MAX_CONTEXT, TILE, MTS, SEM,
+                               args.front_sink, device=dev, partial_dtype=torch.bfloat16)
+    out = torch.empty_like(case.q_post)
+    lse = torch.empty(batch, hq, device=dev)
+    scal = scalars(args, args.hit)
+    launch = make_launch(ext, case, ws, scal, out, lse)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    with ClockSampler(local_rank) as clk:
+        ms, graph = time_graph(launch, args.steps, args.warmup, barrier)
+    clocks = clk.summary()
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t)
+    ab = alg_bytes(ws, batch, hq, hkv, args.front_sink, args.capacity,
+                   case.past_lens.cpu().tolist())
+    bytes_all = torch.tensor([float(ab["total"])], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(bytes_all, op=dist.ReduceOp.SUM)
+    status = ops.query_status(dev)
+
+    # end to end through the operator with host buffers: H2D of the step's
+    # inputs from pinned memory, eager operator call, D2H of the output.
+    host = {k: getattr(case, k).cpu().pin_memory() for k in
+            ("q_post", "q_pre", "req_ids", "past_lens", "out_cache_loc")}
+    out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    h2d = sum(v.numel() * v.element_size() for v in host.values())
+    d2h = out_host.numel() * out_host.element_size()
+
+    def e2e_step():
+        for k, v in host.items():
+            getattr(case, k).copy_(v, non_blocking=True)
+        launch()
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    n_e2e = max(5, min(args.steps, 50))
+    launches_before = ops.launch_info(dev)["kernel_launches"]
+    w0 = time.perf_counter()
+    for _ in range(n_e2e):
+        e2e_step()
+    e2e_ms = (time.perf_counter() - w0) * 1e3 / n_e2e
+    launches_e2e = ops.launch_info(dev)["kernel_launches"] - launches_before
+    te = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_ms = float(te)
+
+    info = ops.launch_info(dev)
+    peaks = {}
+    pk = ROOT / "MEASURED_PEAKS.json"
+    if pk.exists():
+        peaks = json.loads(pk.read_text())
+    peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
+    achieved = ab["total"] / (ms * 1e-3) / 1e9
+    line = {
+        "metric": "us_per_decode_step_cuda_graph_replay",
+        "value": ms_max * 1e3,
+        "unit": "us",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_max,
+        "higher_is_better": False,
+        "scaling": "weak" if args.shard == "request" else "strong",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic",
+        "config": {
+            "workload": f"GQA-{args.hq // args.hkv} MAC decode step, Hq{args.hq}/Hkv{args.hkv}/D128, "
+                        f"batch {batch} per GPU, context {args.ctx}, per-head hit fraction {args.hit} "
+                        f"(reference synthetic_head decisions, lag {LAG}), ring M={args.capacity}, "
+                        f"S={SEM}, F={args.front_sink}, paged KV page {args.page_size}",
+            "batch": batch, "context": args.ctx, "hit_fraction": args.hit,
+            "sharding": f"{args.shard} x{world}, no collective in attention",
+            "l2": "inputs larger than L2 (K/V + ring streamed per step >> 126 MB)",
+            "non_hit_groups": ab["non_hit_groups"], "full_attention_groups": ab["full_groups"],
+            "grid": info["last_grid"], "regs": info["regs_per_thread"],
+        },
+        "hbm_gbs": bytes_all.item() / (ms_max * 1e-3) / 1e9,
+        "request_steps_per_s": world * batch / (ms_max * 1e-3),
+        "e2e": {"value": e2e_ms * 1e3, "unit": "us", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": args.steps,
+        "gpu_launches_e2e_region": int(launches_e2e),
+        "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"],
+                   "reasons": clocks["reasons"]},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
+                     "frac": achieved / peak_gbs, "traffic": None,
+                     "kernel": "mac_decode_persistent_kernel",
+                     "alg_bytes_per_launch": ab["total"], "kv_bytes": ab["kv"],
+                     "scan_bytes": ab["scan"],
+                     "peak_source": "MEASURED_PEAKS.json hbm_gbs (of measured)" if peaks
+                     else "6650 GB/s (of fallback)"},
+        "device_status": status,
+    }
+    if rank == 0 and not args.no_cpu_baseline and world == 1:
+        line["cpu_baseline"] = cpu_baseline(args, steps=2, warmup=1)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_baseline(args, steps, warmup):
+    """The CPU restatement of the reference path (oracle port) timed on the host
+    cores on a bounded sample of the workload: the first few requests of the
+    batch, all heads, same context and hit fraction; scaled to the full batch."""
+    import torch
+
+    from mac_attention_b200 import synth
+    from oracle import mac_oracle as O
+
+    ns = max(1, min(args.cpu_sample_requests, args.batch))
+    case = synth.make_decode_case(batch=ns, ctx=args.ctx, hq=args.hq, hkv=args.hkv,
+                                  capacity=args.capacity, page_size=args.page_size, seed=1000,
+                                  device="cpu")
+    cfg = O.DecodeConfig(max_context=MAX_CONTEXT, tile_tokens=TILE, match_tile_slots=MTS,
+                         semantic_pos_ahead=SEM, front_sink_tokens=args.front_sink,
+                         bench_mode=args.bench_mode, bench_hit_rate=args.hit,
+                         bench_match_lag_mean=float(LAG), bench_seed=1)
+    times = []
+    for i in range(warmup + steps):
+        c = case.clone() if i == 0 else case
+        t0 = time.perf_counter()
+        O.decode_step(c.q_post, c.q_pre, c.k, c.v, c.req_to_token, c.req_ids, c.past_lens,
+                      c.out_cache_loc, c.query_cache, c.attn_cache, c.lse_cache, cfg)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    per_sample = sum(times) / len(times)
+    scale = args.batch / ns
+    return {"value": per_sample * scale * 1e6, "unit": "us", "cores": O.lib().mac_oracle_num_threads(),
+            "kind": "port",
+            "sample": f"{ns} of {args.batch} requests (all heads, full context {args.ctx}, hit "
+                      f"{args.hit}), {per_sample:.3f} s per sample step, scaled x{scale:g}"}
+
+
+def run_reference_arm(args):
+    """``--impl reference``: the reference has no CPU implementation of the whole
+    path (its kernel is CUDA only), so this arm times the CPU oracle port on
+    the host cores.  Under torchrun only rank 0 works."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    cb = cpu_baseline(args, steps=max(1, args.steps), warmup=max(0, args.warmup))
+    line = {
+        "impl": "reference",
+        "metric": "us_per_decode_step_cuda_graph_replay",
+        "value": cb["value"], "unit": "us", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": cb["value"] / 1e3, "higher_is_better": False,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": {"workload": f"GQA-{args.hq // args.hkv} MAC decode step, Hq{args.hq}/Hkv{args.hkv}"
+                               f"/D128, batch {args.batch}, context {args.ctx}, hit {args.hit}"},
+        "cpu_baseline": cb,
+        "e2e": {"value": cb["value"], "unit": "us", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------- sweep
+def bench_flashinfer(case, hq, hkv, page_size, steps, warmup):
+    """FlashInfer full decode over the same paged KV (plan once, capture run, time replay)."""
+    import torch
+    import flashinfer
+
+    batch = case.q_post.shape[0]
+    dev = case.q_post.device
+    kv_lens = (case.past_lens + 1).cpu()
+    pages = (kv_lens + page_size - 1) // page_size
+    indptr = torch.zeros(batch + 1, dtype=torch.int32)
+    indptr[1:] = torch.cumsum(pages, 0)
+    idx = []
+    r2t = case.req_to_token.cpu()
+    ocl = case.out_cache_loc.cpu()
+    for n in range(batch):
+        toks = torch.cat([r2t[int(case.req_ids[n]), :int(kv_lens[n]) - 1].long(), ocl[n:n + 1].long()])
+        idx.append((toks[::page_size] // page_size).to(torch.int32))
+    indices = torch.cat(idx).to(dev)
+    last = ((kv_lens - 1) % page_size + 1).to(torch.int32).to(dev)
+    indptr = indptr.to(dev)
+    kc = case.k.view(-1, page_size, hkv, DIM)
+    vc = case.v.view(-1, page_size, hkv, DIM)
+    wsb = torch.empty(256 << 20, device=dev, dtype=torch.uint8)
+    wrapper = flashinfer.decode.BatchDecodeWithPagedKVCacheWrapper(
+        wsb, kv_layout="NHD", use_cuda_graph=True, paged_kv_indptr_buffer=indptr,
+        paged_kv_indices_buffer=indices, paged_kv_last_page_len_buffer=last)
+    wrapper.plan(indptr, indices, last, hq, hkv, DIM, page_size, q_data_type=torch.bfloat16,
+                 kv_data_type=torch.bfloat16, sm_scale=1.0 / math.sqrt(DIM))
+    out = torch.empty_like(case.q_post)
+    lse = torch.empty(batch, hq, device=dev, dtype=torch.float32)
+
+    def launch():
+        wrapper.run(case.q_post, (kc, vc), out=out, lse=lse, return_lse=True)
+
+    ms, _ = time_graph(launch, steps, warmup)
+    return ms, out
+
+
+def run_sweep(args):
+    import torch
+
+    from mac_attention_b200 import load_mac_persistent_decode_extension, make_decode_workspace
+    from mac_attention_b200 import ops
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    ext = load_mac_persistent_decode_extension()
+    baselines = [b for b in args.baselines.split(",") if b]
+    ref_ext = None
+    if "refkernel" in baselines:
+        from oracle import build_ref
+
+        ref_ext = build_ref.load_decode()
+    rows = []
+    hits = [0.0, 0.25, 0.5, 0.75, 0.9, 1.0]
+    shapes = [(b, c) for b in (1, 16, 64) for c in (32768, 65536, 126976)]
+    if os.environ.get("MAC_SWEEP_SHAPES"):
+        shapes = [tuple(int(x) for x in s.split("x")) for s in os.environ["MAC_SWEEP_SHAPES"].split(",")]
+    if os.environ.get("MAC_SWEEP_HITS"):
+        hits = [float(x) for x in os.environ["MAC_SWEEP_HITS"].split(",")]
+    for batch, ctx in shapes:
+        case = build_case(args, dev, 1000, batch, ctx, args.hq, args.hkv)
+        ws = make_decode_workspace(batch, args.hq, args.hkv, args.capacity, MAX_CONTEXT, TILE, MTS,
+                                   SEM, args.front_sink, device=dev, partial_dtype=torch.bfloat16)
+        out = torch.empty_like(case.q_post)
+        lse = torch.empty(batch, args.hq, device=dev)
+        fi_ms = None
+        if "flashinfer" in baselines:
+            try:
+                fi_ms, _ = bench_flashinfer(case, args.hq, args.hkv, args.page_size, args.steps,
+                                            args.warmup)
+            except Exception as exc:  # noqa: BLE001
+                fi_ms = f"unavailable on this box: {type(exc).__name__}: {str(exc)[:200]}"
+        for hit in hits:
+            scal = scalars(args, hit)
+            ms, _ = time_graph(make_launch(ext, case, ws, scal, out, lse), args.steps, args.warmup)
+            ab = alg_bytes(ws, batch, args.hq, args.hkv, args.front_sink, args.capacity,
+                           case.past_lens.cpu().tolist())
+            row = dict(batch=batch, ctx=ctx, hit=hit, mac_us=ms * 1e3,
+                       alg_gbs=ab["total"] / (ms * 1e-3) / 1e9, kv_gb=ab["kv"] / 1e9,
+                       non_hit_groups=ab["non_hit_groups"], full_groups=ab["full_groups"],
+                       flashinfer_us=(fi_ms * 1e3 if isinstance(fi_ms, float) else fi_ms))
+            if ref_ext is not None:
+                try:
+                    rms, _ = time_graph(make_launch(ref_ext, case, ws, scal, out, lse), args.steps,
+                                        args.warmup)
+                    row["refkernel_us"] = rms * 1e3
+                except Exception as exc:  # noqa: BLE001
+                    row["refkernel_us"] = f"failed: {str(exc)[:120]}"
+            rows.append(row)
+            print(json.dumps(row), flush=True)
+        del case, ws
+        torch.cuda.empty_cache()
+    Path(args.sweep_out).parent.mkdir(parents=True, exist_ok=True)
+    Path(args.sweep_out).write_text(json.dumps(dict(rows=rows, status=ops.query_status(dev),
+                                                    hq=args.hq, hkv=args.hkv,
+                                                    front_sink=args.front_sink), indent=1))
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    elif args.sweep:
+        run_sweep(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,58 @@
+"""CPU: the C-ABI library builds for sm_100a, loads, and exports every symbol
+that include/mac_b200.h declares (no compute calls without a GPU)."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+from mac_attention_b200 import _abi, build
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+@pytest.fixture(scope="module")
+def lib():
+    build.build()
+    return _abi.load_library()
+
+
+def _declared_functions():
+    text = (ROOT / "include" / "mac_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(mac_b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_functions_are_exported(lib):
+    names = _declared_functions()
+    assert len(names) == 9
+    for n in names:
+        assert hasattr(lib, n), n
+    assert sorted(_abi.PROTOTYPES) == names
+
+
+def test_abi_version_and_error_text(lib):
+    assert lib.mac_b200_abi_version() == _abi.ABI_VERSION
+    assert lib.mac_b200_last_error() == b""
+    assert lib.mac_b200_persistent_decode_bf16(None, None) == -1
+    assert b"null" in lib.mac_b200_last_error()
+
+
+def test_struct_layout_matches_c():
+    from oracle import mac_oracle as O
+
+    assert O.lib().mac_oracle_abi_struct_size() == ctypes.sizeof(_abi.MacB200DecodeArgs)
+
+
+def test_argument_validation_needs_no_gpu(lib):
+    a = _abi.MacB200DecodeArgs()
+    a.D, a.Hq, a.Hkv = 64, 8, 2
+    assert lib.mac_b200_persistent_decode_bf16(ctypes.byref(a), None) == -1
+    assert b"D=128" in lib.mac_b200_last_error()
+    a.D, a.Hq, a.Hkv = 128, 32, 2
+    assert lib.mac_b200_persistent_decode_bf16(ctypes.byref(a), None) == -1
+    assert b"GQA" in lib.mac_b200_last_error()
+    p = _abi.MacB200PrefillArgs()
+    assert lib.mac_b200_prefill_update_cache(ctypes.byref(p), None) == 0  # capacity 0: no-op
+    p.M, p.B = 4, 1
+    assert lib.mac_b200_prefill_update_cache(ctypes.byref(p), None) == -1
