@@ -63,7 +63,8 @@ def _stream_ptr(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
-def mac_persistent_decode_bf16(
+def _decode_call(
+    entry_name,
     q_post, q_pre, k_buffer, v_buffer, req_to_token, req_ids, past_lens, out_cache_loc,
     query_cache, attn_cache, lse_cache, out, optional_lse,
     match_dist, match_pos, match_slot,
@@ -81,7 +82,7 @@ def mac_persistent_decode_bf16(
     bench_seed, bench_miss_mask, bench_layer_id,
     query_post_cache, mac_cache_ready, mac_cache_epoch, mac_request_epoch,
 ) -> None:
-    """One fused MAC decode step (see ``include/mac_b200.h``).  Returns ``None``."""
+    """Checks and argument marshalling shared by the decode entry points."""
     lib = _abi.load_library()
     _check(q_post, "q_post", _BF16, 3)
     _check(q_pre, "q_pre", _BF16, 3)
@@ -270,7 +271,21 @@ def mac_persistent_decode_bf16(
     a.cache_ready, a.cache_epoch, a.request_epoch = ready_ptr, epoch_ptr, req_epoch_ptr
 
     with torch.cuda.device(q_post.device):
-        _abi.check(lib.mac_b200_persistent_decode_bf16(C.byref(a), _stream_ptr(q_post.device)))
+        _abi.check(getattr(lib, entry_name)(C.byref(a), _stream_ptr(q_post.device)))
+
+
+_DECODE_ARG_COUNT = 68
+
+
+def mac_persistent_decode_bf16(*args) -> None:
+    """One fused MAC decode step; the reference operator's 68 positional arguments
+    (13 tensors, 30 workspace tensors, 21 scalars, ``query_post_cache`` and the
+    three readiness-gate tensors; see ``_decode_call`` for the names and
+    ``include/mac_b200.h`` for the meaning).  Returns ``None``."""
+    if len(args) != _DECODE_ARG_COUNT:
+        raise TypeError(f"mac_persistent_decode_bf16() takes {_DECODE_ARG_COUNT} positional "
+                        f"arguments ({len(args)} given)")
+    _decode_call("mac_b200_persistent_decode_bf16", *args)
 
 
 def mac_prefill_update_cache(
