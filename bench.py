@@ -179,10 +179,10 @@ def make_launch(ext, case, ws, scal, out, lse):
     return launch
 
 
-def scalars(args, hit):
+def scalars(args, hit, debug=0):
     """The operator's 21 scalars in positional order (reference benchmark defaults)."""
     return (MAX_CONTEXT, TILE, MTS, SEM, args.front_sink, 0, 0, 0, 0.45, 1.0 / math.sqrt(DIM),
-            0, args.bench_mode, hit, 0.0, -1.0, 0.0, float(LAG), 0.0, 1, -1, 0)
+            debug, args.bench_mode, hit, 0.0, -1.0, 0.0, float(LAG), 0.0, 1, -1, 0)
 
 
 def time_graph(launch, steps, warmup, barrier=None):
@@ -251,6 +251,9 @@ def run_ours(args):
         if dist is not None:
             dist.barrier()
 
+    profiler_range = os.environ.get("MAC_BENCH_PROFILER_RANGE") == "1"
+    if profiler_range:  # lets a profiler attach to the measured launches only
+        torch.cuda.profiler.start()
     with ClockSampler(local_rank) as clk:
         ms, graph = time_graph(launch, args.steps, args.warmup, barrier)
     clocks = clk.summary()
@@ -294,6 +297,9 @@ def run_ours(args):
     if dist is not None:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_ms = float(te)
+    if profiler_range:
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
 
     info = ops.launch_info(dev)
     peaks = {}
@@ -489,7 +495,13 @@ def run_sweep(args):
             ms, _ = time_graph(make_launch(ext, case, ws, scal, out, lse), args.steps, args.warmup)
             ab = alg_bytes(ws, batch, args.hq, args.hkv, args.front_sink, args.capacity,
                            case.past_lens.cpu().tolist())
+            # one eager launch with phase timestamps (ns) for the breakdown
+            make_launch(ext, case, ws, scalars(args, hit, debug=2), out, lse)()
+            torch.cuda.synchronize()
+            ph = ws[29].cpu().tolist()
             row = dict(batch=batch, ctx=ctx, hit=hit, mac_us=ms * 1e3,
+                       phase_us=dict(scan=(ph[1] - ph[0]) / 1e3, classify=(ph[2] - ph[1]) / 1e3,
+                                     attend_cta0=(ph[3] - ph[2]) / 1e3),
                        alg_gbs=ab["total"] / (ms * 1e-3) / 1e9, kv_gb=ab["kv"] / 1e9,
                        non_hit_groups=ab["non_hit_groups"], full_groups=ab["full_groups"],
                        flashinfer_us=(fi_ms * 1e3 if isinstance(fi_ms, float) else fi_ms))
