@@ -159,6 +159,33 @@ typedef struct MacB200DecodeArgs {
 int mac_b200_persistent_decode_bf16(const MacB200DecodeArgs* args, void* stream);
 
 /*
+ * The same decode step for hosts that cannot allocate device memory.
+ * No counterpart in the reference (its operator takes all scratch from the
+ * caller).
+ *
+ * Who needs it: a process whose own pool allocator owns all of HBM, a plugin
+ * loaded under a sandbox that filters the driver's allocation calls, or code
+ * that is already inside a region where allocating is illegal.  This entry
+ * point never calls cudaMalloc, cudaFree or any allocating library routine:
+ * its scratch (split-KV partials, scheduler words) is one fixed 8 MiB block
+ * of device memory built into the library image, which every GPU that loads
+ * the library keeps until the process exits.
+ *
+ * Limit: a step whose scratch need exceeds the block is refused with
+ * MAC_B200_ESIZE and a message that names the need.  With a grid of 148 CTAs
+ * the need is roughly (296 + 3*N*Hkv) * (Hq/Hkv) * 512 bytes, so e.g. 64
+ * requests x 8 KV heads with 4..8 query heads per KV head fit.
+ *
+ * The first call on a device looks up the block's device address and sets the
+ * kernel's attributes; make that first call outside of any stream capture.
+ * All calls on a device share the block and it keeps the previous call's
+ * contents (the kernel clears the words that must start at zero), so two of
+ * these calls -- or one of these and one mac_b200_persistent_decode_bf16 --
+ * that overlap on the GPU race; keep them on one stream or order them.
+ */
+int mac_b200_persistent_decode_bf16_noalloc(const MacB200DecodeArgs* args, void* stream);
+
+/*
  * Arguments of the prefill-side ring build.
  * Replaces the 14 arguments of mac_prefill_update_cache
  * (mac_prefill_update_cache.cu:324-337).

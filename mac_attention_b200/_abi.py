@@ -64,6 +64,7 @@ class MacB200LaunchInfo(C.Structure):
 # Every symbol include/mac_b200.h declares, with its ctypes prototype.
 PROTOTYPES = {
     "mac_b200_persistent_decode_bf16": (C.c_int, [C.POINTER(MacB200DecodeArgs), ptr]),
+    "mac_b200_persistent_decode_bf16_noalloc": (C.c_int, [C.POINTER(MacB200DecodeArgs), ptr]),
     "mac_b200_prefill_update_cache": (C.c_int, [C.POINTER(MacB200PrefillArgs), ptr]),
     "mac_b200_mark_persistent_ready": (C.c_int, [ptr, ptr, ptr, ptr, i32, i32, ptr]),
     "mac_b200_invalidate_persistent_ready": (C.c_int, [ptr, ptr, ptr, ptr, i32, i32, ptr]),

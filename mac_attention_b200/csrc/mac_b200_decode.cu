@@ -1349,6 +1349,142 @@ extern "C" int mac_b200_persistent_decode_bf16(const MacB200DecodeArgs* args, vo
   return MAC_B200_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Decode entry point that never allocates.
+//
+// Some hosts of this library must not create or free device memory: a serving
+// process that hands all of HBM to its own pool allocator up front, a plugin
+// that runs under a sandbox which filters the driver's allocation calls, or a
+// caller that is already inside a region where allocation is illegal.  For
+// them the split-KV partials and scheduler words live in one fixed block of
+// device memory that is part of the library image itself.
+namespace mac_b200 {
+namespace {
+
+constexpr size_t kNoAllocArenaBytes = size_t(8) << 20;  // 8 MiB, resident on every GPU that loads the library
+static __device__ __align__(256) unsigned char g_noalloc_arena[kNoAllocArenaBytes];
+
+struct NoAllocDeviceState {
+  bool ready = false;
+  int sm_count = 0;
+  int ctas_per_sm = 0;
+  void* arena = nullptr;  // device address of g_noalloc_arena on this device
+};
+std::mutex g_noalloc_mu;
+NoAllocDeviceState g_noalloc_dev[64];
+
+}  // namespace
+}  // namespace mac_b200
+
+extern "C" int mac_b200_persistent_decode_bf16_noalloc(const MacB200DecodeArgs* args,
+                                                       void* stream_v) {
+  MAC_REQUIRE(args != nullptr, "decode args must not be null");
+  const MacB200DecodeArgs& a = *args;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  MAC_REQUIRE(a.D == kD, "persistent decode supports D=128 only");
+  MAC_REQUIRE(a.Hkv > 0 && a.Hq > 0 && a.Hq % a.Hkv == 0, "Hq must be divisible by Hkv");
+  const int G = a.Hq / a.Hkv;
+  MAC_REQUIRE(G > 0 && G <= 8, "unsupported GQA group size");
+  MAC_REQUIRE(a.N >= 0, "negative batch");
+  MAC_REQUIRE(a.M > 0 && a.R > 0, "ring tensors must not be empty");
+  MAC_REQUIRE(a.match_tile_slots > 0, "match_tile_slots must be positive");
+  MAC_REQUIRE(a.max_match_tiles >= (a.M + a.match_tile_slots - 1) / a.match_tile_slots,
+              "match workspace too small");
+  MAC_REQUIRE(a.ws_batch >= a.N, "decision workspaces are smaller than the batch");
+  MAC_REQUIRE(a.bench_mode == 0 || a.bench_mode == 1 || a.bench_mode == 2,
+              "unsupported synthetic MAC bench mode");
+  MAC_REQUIRE(a.phase_cycles_count >= 6 && a.phase_cycles,
+              "phase_cycles must have at least 6 elements");
+  MAC_REQUIRE(a.q_post && a.q_pre && a.k_buffer && a.v_buffer && a.req_to_token && a.req_ids &&
+                  a.past_lens && a.out_cache_loc && a.query_cache && a.attn_cache && a.lse_cache &&
+                  a.out,
+              "input/output tensors must not be null");
+  MAC_REQUIRE(a.match_dist && a.match_pos && a.match_slot && a.head_hit && a.head_match_slot &&
+                  a.head_match_pos && a.head_prefix_end && a.head_rect_start && a.head_new_end &&
+                  a.group_rect_begin && a.group_rect_end && a.group_rect_tiles &&
+                  a.group_tail_begin && a.group_tail_end && a.group_tail_tiles && a.group_mode &&
+                  a.task_counts,
+              "workspace tensors must not be null");
+  if (a.N == 0) return MAC_B200_OK;
+  if (a.Hq > kMaxHq)
+    return fail(MAC_B200_EUNSUPPORTED, "Hq=%d exceeds this build's limit of %d", a.Hq, kMaxHq);
+  const long long NGll = static_cast<long long>(a.N) * a.Hkv;
+  if (NGll > kMaxGroups)
+    return fail(MAC_B200_EUNSUPPORTED, "N*Hkv=%lld exceeds this build's limit of %d", NGll,
+                kMaxGroups);
+
+  int device = 0;
+  MAC_CUDA(cudaGetDevice(&device));
+  MAC_REQUIRE(device >= 0 && device < 64, "device index out of range");
+  NoAllocDeviceState st;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    NoAllocDeviceState& ds = g_noalloc_dev[device];
+    if (!ds.ready) {
+      // One-time set-up for this device (it is the current one): kernel
+      // attributes, occupancy, and the device address of the fixed block.  In
+      // host code the array's name is only a handle for the runtime; the
+      // address a kernel can use comes from cudaGetSymbolAddress.
+      int coop = 0;
+      MAC_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device));
+      if (!coop) return fail(MAC_B200_EUNSUPPORTED, "device does not support cooperative launch");
+      MAC_CUDA(cudaFuncSetAttribute(mac_decode_persistent_kernel,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+      MAC_CUDA(cudaDeviceGetAttribute(&ds.sm_count, cudaDevAttrMultiProcessorCount, device));
+      MAC_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+          &ds.ctas_per_sm, mac_decode_persistent_kernel, kThreads, kSmemBytes));
+      if (ds.ctas_per_sm < 1) return fail(MAC_B200_ECUDA, "decode kernel has zero occupancy");
+      void* sym = nullptr;
+      MAC_CUDA(cudaGetSymbolAddress(&sym, g_noalloc_arena));
+      if (sym == nullptr) return fail(MAC_B200_ECUDA, "fixed scratch block has no device address");
+      ds.arena = sym;
+      ds.ready = true;
+    }
+    st = ds;
+  }
+  int grid = st.sm_count * st.ctas_per_sm;
+  if (a.grid_cap > 0 && a.grid_cap < grid) grid = a.grid_cap;
+  const int max_pieces = 2 * grid;
+  const ArenaLayout L = arena_layout(static_cast<int>(NGll), G, max_pieces);
+  if (L.total > kNoAllocArenaBytes)
+    return fail(MAC_B200_ESIZE,
+                "this step needs %zu bytes of scratch (N*Hkv=%lld groups, %d query heads per "
+                "group) but the fixed block holds %zu; use mac_b200_persistent_decode_bf16 or a "
+                "smaller batch",
+                L.total, NGll, G, kNoAllocArenaBytes);
+
+  DecodeParams p;
+  p.a = a;
+  p.G = G;
+  p.NG = static_cast<int>(NGll);
+  p.F = a.front_sink_tokens > 0 ? a.front_sink_tokens : 0;
+  p.tm_used = (a.M + a.match_tile_slots - 1) / a.match_tile_slots;
+  p.max_pieces = max_pieces;
+  {
+    float t = 2.0f * static_cast<float>(a.D);
+    t = t * (1.0f - a.threshold);
+    t = t * (1.0f - a.threshold);
+    p.thr_dist = t;
+  }
+  p.scale_log2 = a.sm_scale * kLog2e;
+  char* base = static_cast<char*>(st.arena);
+  p.ar.ticket = reinterpret_cast<uint32_t*>(base + L.ticket);
+  p.ar.garrive = reinterpret_cast<int32_t*>(base + L.garrive);
+  p.ar.plan = reinterpret_cast<GroupPlan*>(base + L.plan);
+  p.ar.part_lse = reinterpret_cast<float*>(base + L.part_lse);
+  p.ar.part_o = reinterpret_cast<float*>(base + L.part_o);
+  p.ar.slots = L.slots;
+  // The block keeps whatever the previous call left in it.  The words that
+  // must start at zero (piece ticket, per-group arrival counters) are cleared
+  // by the kernel's first phase before any CTA reads them; everything else is
+  // written before it is read within one launch.
+  void* kargs[] = {&p};
+  MAC_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(mac_decode_persistent_kernel),
+                                       dim3(grid), dim3(kThreads), kargs, kSmemBytes, stream));
+  g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+  return MAC_B200_OK;
+}
+
 extern "C" int mac_b200_query_status(uint32_t* status_out, void* stream_v) {
   MAC_REQUIRE(status_out != nullptr, "status_out must not be null");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);

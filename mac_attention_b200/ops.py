@@ -288,6 +288,19 @@ def mac_persistent_decode_bf16(*args) -> None:
     _decode_call("mac_b200_persistent_decode_bf16", *args)
 
 
+def mac_persistent_decode_bf16_noalloc(*args) -> None:
+    """The decode step through ``mac_b200_persistent_decode_bf16_noalloc``: same 68
+    arguments and results, scratch in the library's fixed 8 MiB block instead of
+    an allocated arena.  For hosts that may not allocate device memory (a
+    serving process whose pool owns all of HBM, a sandboxed plugin); raises
+    ``RuntimeError`` when the step does not fit the block.  Make the first call
+    on a device before any stream capture; overlapping calls on one GPU race."""
+    if len(args) != _DECODE_ARG_COUNT:
+        raise TypeError(f"mac_persistent_decode_bf16_noalloc() takes {_DECODE_ARG_COUNT} "
+                        f"positional arguments ({len(args)} given)")
+    _decode_call("mac_b200_persistent_decode_bf16_noalloc", *args)
+
+
 def mac_prefill_update_cache(
     q_cache, attn_cache, lse_cache, request_length, req_ids, src_q, src_attn, src_lse,
     offsets, lens, capacity, num_heads, head_dim, q_post_cache,
