@@ -288,11 +288,55 @@ __device__ bool grid_barrier(unsigned nblocks) {
 }
 
 // ---------------------------------------------------------------- phase A
-// One work item = (match tile, request).  The CTA streams the tile's ring
-// rows for all query heads: a half-warp owns one 256-byte (slot, head) row
-// per load, lane t holding dims [8t, 8t+8); distances are summed in exactly
-// the reference's order (8 sequential FMAs per lane, xor butterfly 8,4,2,1;
-// DEC.cu:1062-1069, 343-349) so thresholds and ties resolve identically.
+// Match scan.  The CTA owns match tiles blockIdx.x, blockIdx.x + grid, ... of
+// the (tile, request) grid.  A half-warp owns one 256-byte (slot, head) ring
+// row at a time, lane t holding dims [8t, 8t+8); distances are summed in
+// exactly the reference's order (8 sequential FMAs per lane, xor butterfly
+// 8,4,2,1; DEC.cu:1062-1069, 343-349) so thresholds and ties resolve
+// identically.  Rows reach the lanes through a per-thread cp.async ring in
+// shared memory: a batch is 8 ring rows (same head, consecutive slots) plus the
+// matching 16 bytes of the query, kScanDepth-1 batches are in flight per
+// thread, and a lane only ever reads back the bytes it copied itself, so the
+// whole scan runs without a single barrier between warps.
+constexpr int kScanU = 8;
+constexpr int kScanDepth = 5;
+constexpr int kScanStageBytes = (kScanU + 1) * 16 * kThreads;   // 36 KB
+static_assert(kScanDepth * kScanStageBytes <= kRingBytes - 8192, "scan ring must fit");
+constexpr int kScanRoundTiles = 32;   // tiles per round when sub-results are combined in smem
+
+struct ScanCursor {
+  int k, hi, b;                 // tile of the round, head of this half-warp, batch of the tile
+  int n, tile, P, req, cbeg, cend, s_begin, s_end;
+  int tail, off_lo, off_hi;     // logical position of slot s: s + (s < tail ? off_lo : off_hi)
+  bool elig;
+};
+
+// ring_slot_to_pos (DEC.cu:798-807) with the modulo hoisted out of the slot loop.
+__device__ __forceinline__ int scan_slot_pos(const ScanCursor& c, int s) {
+  return s + (s < c.tail ? c.off_lo : c.off_hi);
+}
+
+__device__ __forceinline__ void scan_load_tile(const MacB200DecodeArgs& a, int g, ScanCursor& c) {
+  c.tile = g / a.N;
+  c.n = g - c.tile * a.N;
+  c.s_begin = c.tile * a.match_tile_slots;
+  c.s_end = min(a.M, c.s_begin + a.match_tile_slots);
+  c.elig = false;
+  c.P = 0; c.req = 0; c.cbeg = 0; c.cend = 0;
+  c.tail = 0; c.off_lo = 0; c.off_hi = 0;
+  if (!request_bad(a, c.n)) {
+    c.P = a.past_lens[c.n];
+    c.req = a.req_ids[c.n];
+    candidate_window(a, c.P, c.cbeg, c.cend);
+    c.elig = c.P >= a.gen_min_limit && c.cend > c.cbeg && request_ready(a, c.req);
+    if (c.P >= a.M) {
+      c.tail = c.P % a.M;
+      c.off_lo = c.P - c.tail;          // slots before the write cursor hold the newest positions
+      c.off_hi = c.P - a.M - c.tail;    // slots from the cursor on hold the oldest
+    }
+  }
+}
+
 __device__ void phase_match_scan(const DecodeParams& p, uint8_t* smem) {
   const MacB200DecodeArgs& a = p.a;
   const int tid = threadIdx.x;
@@ -304,130 +348,181 @@ __device__ void phase_match_scan(const DecodeParams& p, uint8_t* smem) {
   for (int g = blockIdx.x * kThreads + tid; g < p.NG; g += gridDim.x * kThreads)
     p.ar.garrive[g] = 0;
 
-  uint4* q_sm = reinterpret_cast<uint4*>(smem);                       // [Hq][16] uint4
-  float* best_d_sm = reinterpret_cast<float*>(smem + kMaxHq * kRowBytes);  // [Hq*spar]
-  int* best_p_sm = reinterpret_cast<int*>(best_d_sm + 2 * kMaxHq);
-  int* best_s_sm = best_p_sm + 2 * kMaxHq;
-
   const int Hq = a.Hq, M = a.M, Tm = a.max_match_tiles;
   int p2 = 1;
   while (p2 < Hq && p2 < 16) p2 <<= 1;   // heads scanned side by side
-  const int spar = 16 / p2;              // slots scanned side by side
+  const int spar = 16 / p2;              // slots scanned side by side (only when Hq < 16)
   const int hw = tid >> 4, tx = tid & 15;
   const int hslot = hw % p2, sub = hw / p2;
   const unsigned sub_mask = (tid & 16) ? 0xffff0000u : 0x0000ffffu;
+  const int nh = hslot < Hq ? (Hq - hslot + p2 - 1) / p2 : 0;          // heads of this half-warp
+  const int nb = (a.match_tile_slots + kScanU * spar - 1) / (kScanU * spar);  // batches per tile
+  const int total_tiles = a.N * Tm;
+  const int my_tiles = static_cast<int>(blockIdx.x) < total_tiles
+                           ? (total_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                                 static_cast<int>(gridDim.x)
+                           : 0;
+  const int round_tiles = spar > 1 ? kScanRoundTiles : (my_tiles > 0 ? my_tiles : 1);
   const char* ring = static_cast<const char*>(a.query_cache);
+  const char* qsrc = static_cast<const char*>(a.q_pre);
+  const uint32_t lane_base = smem_u32(smem) + tid * 16;
+  const uint8_t* lane_ptr = smem + tid * 16;
+  // partial (per sub) results of a round, only used when spar > 1
+  float* part_d = reinterpret_cast<float*>(smem + kScanDepth * kScanStageBytes);
+  int* part_p = reinterpret_cast<int*>(part_d + kScanRoundTiles * 16);
+  int* part_s = part_p + kScanRoundTiles * 16;
 
-  const int items = a.N * Tm;
-  for (int item = blockIdx.x; item < items; item += gridDim.x) {
-    const int tile = item / a.N;
-    const int n = item - tile * a.N;
-    const int64_t out_base = static_cast<int64_t>(n) * Hq * Tm + tile;
-    const int slot_begin = tile * a.match_tile_slots;
-    int slot_end = slot_begin + a.match_tile_slots;
-    if (slot_end > M) slot_end = M;
-    bool eligible = false;
-    int P = 0, req = 0, cbeg = 0, cend = 0;
-    if (!request_bad(a, n)) {
-      P = a.past_lens[n];
-      req = a.req_ids[n];
-      candidate_window(a, P, cbeg, cend);
-      eligible = P >= a.gen_min_limit && cend > cbeg && request_ready(a, req);
+  for (int r0 = 0; r0 < my_tiles; r0 += round_tiles) {
+    const int rt = min(round_tiles, my_tiles - r0);
+    const int nseq = rt * nh * nb;
+    ScanCursor ci, cc;   // issue side, consume side
+    ci.k = ci.hi = ci.b = 0;
+    cc.k = cc.hi = cc.b = 0;
+    if (nseq > 0) {
+      scan_load_tile(a, blockIdx.x + r0 * gridDim.x, ci);
+      cc = ci;
     }
-    // does this tile hold any candidate slot?
-    bool any = false;
-    if (eligible && slot_begin < slot_end) {
-      if (P < M) {
-        any = slot_begin < cend && slot_end > cbeg;  // slot == pos
-      } else {
-        any = true;  // every slot maps into [P-M, P); lookback may trim a few
-      }
-    }
-    if (!any) {
-      for (int h = tid; h < Hq; h += kThreads) {
-        a.match_dist[out_base + static_cast<int64_t>(h) * Tm] = INFINITY;
-        a.match_pos[out_base + static_cast<int64_t>(h) * Tm] = INT_MAX;
-        a.match_slot[out_base + static_cast<int64_t>(h) * Tm] = -1;
-      }
-      continue;
-    }
-    __syncthreads();  // previous item's smem readers are done
-    {
-      const uint4* qsrc = reinterpret_cast<const uint4*>(
-          static_cast<const char*>(a.q_pre) + static_cast<int64_t>(n) * Hq * kRowBytes);
-      for (int i = tid; i < Hq * 16; i += kThreads) q_sm[i] = qsrc[i];
-    }
-    __syncthreads();
-
-    const int64_t req_base = static_cast<int64_t>(req) * M;
-    for (int h = hslot; h < Hq; h += p2) {
-      float qf[8];
-      {
-        const uint4 qv = q_sm[h * 16 + tx];
-        qf[0] = bf16_lo(qv.x); qf[1] = bf16_hi(qv.x);
-        qf[2] = bf16_lo(qv.y); qf[3] = bf16_hi(qv.y);
-        qf[4] = bf16_lo(qv.z); qf[5] = bf16_hi(qv.z);
-        qf[6] = bf16_lo(qv.w); qf[7] = bf16_hi(qv.w);
-      }
-      float bd = INFINITY;
-      int bp = INT_MAX, bs = -1;
-      constexpr int kU = 8;
-      for (int s0 = slot_begin + sub; s0 < slot_end; s0 += kU * spar) {
-        uint4 raw[kU];
-        int pos[kU];
-        bool val[kU];
-#pragma unroll
-        for (int u = 0; u < kU; ++u) {
-          const int s = s0 + u * spar;
-          pos[u] = ring_slot_to_pos(P, M, s);
-          val[u] = s < slot_end && pos[u] >= cbeg && pos[u] < cend;
-          if (val[u])
-            raw[u] = ld_stream16(ring + ((req_base + s) * Hq + h) * kRowBytes + tx * 16);
+    auto advance = [&](ScanCursor& c) {
+      if (++c.b == nb) {
+        c.b = 0;
+        if (++c.hi == nh) {
+          c.hi = 0;
+          if (++c.k < rt) scan_load_tile(a, blockIdx.x + (r0 + c.k) * gridDim.x, c);
         }
+      }
+    };
+    auto issue = [&](int seq) {
+      if (ci.elig) {
+        const int h = hslot + ci.hi * p2;
+        const uint32_t dst = lane_base + (seq % kScanDepth) * kScanStageBytes;
+        const int64_t row0 = (static_cast<int64_t>(ci.req) * M) * Hq + h;
+        bool any = false;
 #pragma unroll
-        for (int u = 0; u < kU; ++u) {
-          if (!val[u]) continue;  // uniform across the half-warp
-          float acc = 0.0f, diff;
-          diff = qf[0] - bf16_lo(raw[u].x); acc = __fmaf_rn(diff, diff, acc);
-          diff = qf[1] - bf16_hi(raw[u].x); acc = __fmaf_rn(diff, diff, acc);
-          diff = qf[2] - bf16_lo(raw[u].y); acc = __fmaf_rn(diff, diff, acc);
-          diff = qf[3] - bf16_hi(raw[u].y); acc = __fmaf_rn(diff, diff, acc);
-          diff = qf[4] - bf16_lo(raw[u].z); acc = __fmaf_rn(diff, diff, acc);
-          diff = qf[5] - bf16_hi(raw[u].z); acc = __fmaf_rn(diff, diff, acc);
-          diff = qf[6] - bf16_lo(raw[u].w); acc = __fmaf_rn(diff, diff, acc);
-          diff = qf[7] - bf16_hi(raw[u].w); acc = __fmaf_rn(diff, diff, acc);
-#pragma unroll
-          for (int off = 8; off > 0; off >>= 1)
-            acc = __fadd_rn(acc, __shfl_xor_sync(sub_mask, acc, off, 16));
-          if (better_pair(acc, pos[u], bd, bp)) {
-            bd = acc;
-            bp = pos[u];
-            bs = s0 + u * spar;
+        for (int u = 0; u < kScanU; ++u) {
+          const int s = ci.s_begin + sub + (ci.b * kScanU + u) * spar;
+          const int pos = scan_slot_pos(ci, s);
+          if (s < ci.s_end && pos >= ci.cbeg && pos < ci.cend) {
+            cp_async16(dst + u * (kThreads * 16),
+                       ring + (row0 + static_cast<int64_t>(s) * Hq) * kRowBytes + tx * 16, 16);
+            any = true;
           }
         }
+        if (any)
+          cp_async16(dst + kScanU * (kThreads * 16),
+                     qsrc + (static_cast<int64_t>(ci.n) * Hq + h) * kRowBytes + tx * 16, 16);
       }
-      if (tx == 0) {
-        best_d_sm[h * spar + sub] = bd;
-        best_p_sm[h * spar + sub] = bp;
-        best_s_sm[h * spar + sub] = bs;
-      }
+      advance(ci);
+    };
+
+#pragma unroll
+    for (int s = 0; s < kScanDepth - 1; ++s) {
+      if (s < nseq) issue(s);
+      cp_async_commit();
     }
-    __syncthreads();
-    for (int h = tid; h < Hq; h += kThreads) {
-      float bd = INFINITY;
-      int bp = INT_MAX, bs = -1;
-      for (int s = 0; s < spar; ++s) {
-        const float d = best_d_sm[h * spar + s];
-        const int pp = best_p_sm[h * spar + s];
-        if (better_pair(d, pp, bd, bp)) {
-          bd = d;
-          bp = pp;
-          bs = best_s_sm[h * spar + s];
+    float bd = INFINITY;
+    int bp = INT_MAX, bs = -1;
+    for (int seq = 0; seq < nseq; ++seq) {
+      cp_async_wait<kScanDepth - 2>();
+      if (cc.b == 0) { bd = INFINITY; bp = INT_MAX; bs = -1; }
+      if (cc.elig) {
+        // All 8 rows of the batch are evaluated in straight-line code (rows
+        // that were not copied give garbage that is masked below), then summed
+        // across the 16 lanes by a halving exchange: after the steps at lane
+        // distance 8, 4, 2 each lane holds the partial sum of ONE row, the
+        // last step completes it.  Every addition pairs the same two operands
+        // as the reference's xor butterfly, so the result is bit-identical
+        // with a quarter of the shuffles.
+        const uint8_t* src = lane_ptr + (seq % kScanDepth) * kScanStageBytes;
+        const uint4 qv = *reinterpret_cast<const uint4*>(src + kScanU * (kThreads * 16));
+        const float q0 = bf16_lo(qv.x), q1 = bf16_hi(qv.x), q2 = bf16_lo(qv.y), q3 = bf16_hi(qv.y);
+        const float q4 = bf16_lo(qv.z), q5 = bf16_hi(qv.z), q6 = bf16_lo(qv.w), q7 = bf16_hi(qv.w);
+        float acc[kScanU];
+#pragma unroll
+        for (int u = 0; u < kScanU; ++u) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(src + u * (kThreads * 16));
+          float t = 0.0f, diff;
+          diff = q0 - bf16_lo(raw.x); t = __fmaf_rn(diff, diff, t);
+          diff = q1 - bf16_hi(raw.x); t = __fmaf_rn(diff, diff, t);
+          diff = q2 - bf16_lo(raw.y); t = __fmaf_rn(diff, diff, t);
+          diff = q3 - bf16_hi(raw.y); t = __fmaf_rn(diff, diff, t);
+          diff = q4 - bf16_lo(raw.z); t = __fmaf_rn(diff, diff, t);
+          diff = q5 - bf16_hi(raw.z); t = __fmaf_rn(diff, diff, t);
+          diff = q6 - bf16_lo(raw.w); t = __fmaf_rn(diff, diff, t);
+          diff = q7 - bf16_hi(raw.w); t = __fmaf_rn(diff, diff, t);
+          acc[u] = t;
+        }
+        const bool b3 = (tx & 8) != 0, b2 = (tx & 4) != 0, b1 = (tx & 2) != 0;
+        float w4[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const float send = b3 ? acc[r] : acc[r + 4];
+          const float keep = b3 ? acc[r + 4] : acc[r];
+          w4[r] = __fadd_rn(keep, __shfl_xor_sync(sub_mask, send, 8, 16));
+        }
+        float w2[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const float send = b2 ? w4[r] : w4[r + 2];
+          const float keep = b2 ? w4[r + 2] : w4[r];
+          w2[r] = __fadd_rn(keep, __shfl_xor_sync(sub_mask, send, 4, 16));
+        }
+        const float send1 = b1 ? w2[0] : w2[1];
+        const float keep1 = b1 ? w2[1] : w2[0];
+        const float w1 = __fadd_rn(keep1, __shfl_xor_sync(sub_mask, send1, 2, 16));
+        const float dist = __fadd_rn(w1, __shfl_xor_sync(sub_mask, w1, 1, 16));
+        const int row = (b3 ? 4 : 0) + (b2 ? 2 : 0) + (b1 ? 1 : 0);   // the row this lane ends up with
+        const int s = cc.s_begin + sub + (cc.b * kScanU + row) * spar;
+        const int pos = scan_slot_pos(cc, s);
+        if (s < cc.s_end && pos >= cc.cbeg && pos < cc.cend && better_pair(dist, pos, bd, bp)) {
+          bd = dist; bp = pos; bs = s;
         }
       }
-      a.match_dist[out_base + static_cast<int64_t>(h) * Tm] = bd;
-      a.match_pos[out_base + static_cast<int64_t>(h) * Tm] = bp;
-      a.match_slot[out_base + static_cast<int64_t>(h) * Tm] = bs;
+      if (cc.b == nb - 1) {
+        // argmin over the 16 lanes (each tracked its own rows), (distance, older position) order
+#pragma unroll
+        for (int off = 8; off > 1; off >>= 1) {
+          const float od = __shfl_xor_sync(sub_mask, bd, off, 16);
+          const int op = __shfl_xor_sync(sub_mask, bp, off, 16);
+          const int os = __shfl_xor_sync(sub_mask, bs, off, 16);
+          if (better_pair(od, op, bd, bp)) { bd = od; bp = op; bs = os; }
+        }
+      }
+      if (cc.b == nb - 1 && tx == 0) {
+        const int h = hslot + cc.hi * p2;
+        if (spar == 1) {
+          const int64_t off = (static_cast<int64_t>(cc.n) * Hq + h) * Tm + cc.tile;
+          a.match_dist[off] = bd;
+          a.match_pos[off] = bp;
+          a.match_slot[off] = bs;
+        } else {
+          const int e = cc.k * 16 + h * spar + sub;
+          part_d[e] = bd; part_p[e] = bp; part_s[e] = bs;
+        }
+      }
+      advance(cc);
+      const int nxt = seq + kScanDepth - 1;
+      if (nxt < nseq) issue(nxt);
+      cp_async_commit();
+    }
+    cp_async_wait<0>();
+    if (spar > 1) {
+      __syncthreads();
+      for (int t = tid; t < rt * Hq; t += kThreads) {
+        const int k = t / Hq, h = t - k * Hq;
+        float d0 = INFINITY;
+        int p0 = INT_MAX, s0 = -1;
+        for (int s = 0; s < spar; ++s) {
+          const int e = k * 16 + h * spar + s;
+          if (better_pair(part_d[e], part_p[e], d0, p0)) { d0 = part_d[e]; p0 = part_p[e]; s0 = part_s[e]; }
+        }
+        const int g = blockIdx.x + (r0 + k) * gridDim.x;
+        const int tile = g / a.N, n = g - tile * a.N;
+        const int64_t off = (static_cast<int64_t>(n) * Hq + h) * Tm + tile;
+        a.match_dist[off] = d0;
+        a.match_pos[off] = p0;
+        a.match_slot[off] = s0;
+      }
+      __syncthreads();
     }
   }
 }
