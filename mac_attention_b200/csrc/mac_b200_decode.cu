@@ -289,23 +289,37 @@ __device__ bool grid_barrier(unsigned nblocks) {
 
 // ---------------------------------------------------------------- phase A
 // Match scan.  The CTA owns match tiles blockIdx.x, blockIdx.x + grid, ... of
-// the (tile, request) grid.  A half-warp owns one 256-byte (slot, head) ring
-// row at a time, lane t holding dims [8t, 8t+8); distances are summed in
-// exactly the reference's order (8 sequential FMAs per lane, xor butterfly
-// 8,4,2,1; DEC.cu:1062-1069, 343-349) so thresholds and ties resolve
-// identically.  Rows reach the lanes through a per-thread cp.async ring in
-// shared memory: a batch is 8 ring rows (same head, consecutive slots) plus the
-// matching 16 bytes of the query, kScanDepth-1 batches are in flight per
-// thread, and a lane only ever reads back the bytes it copied itself, so the
-// whole scan runs without a single barrier between warps.
+// the (tile, request) grid.  Eight lanes (an "octet") own one (slot, head) ring
+// row at a time; lane j holds dims [8j, 8j+8) and, for rows that survive the
+// probe, dims [64+8j, 64+8j+8).
+//
+//  * Probe: only the first 128 bytes of every candidate row are fetched.  The
+//    64-dim partial distance, summed over the octet in the same pairing order
+//    the full sum uses, is an exact lower bound of the full distance in
+//    floating point (every addition of the full sum has operands that are >=
+//    the corresponding probe operands, and rounding is monotone).  A row whose
+//    probe is >= the hit threshold can never be a hit and is dropped; like the
+//    reference's probe (DEC.cu:996-1059) this never changes a decision.
+//  * Survivors: the second 128 bytes are fetched and the full distance is
+//    formed as in the reference (DEC.cu:1062-1069, 343-349): per-lane sums of 8
+//    sequential FMAs, then pairwise at lane distance 8 (here: in-lane, first
+//    half + second half), 4, 2, 1 -- bit-identical results, so thresholds and
+//    (distance, older position) ties resolve identically.
+//  * Rows reach the lanes through a per-thread cp.async ring in shared memory
+//    (a batch = 8 rows x 16 bytes + the two query chunks, kScanDepth-1 batches
+//    in flight).  A lane only reads back bytes it copied itself: no barrier.
+//  * The probe sums of a batch are reduced with a halving exchange (7 shuffles
+//    for 8 rows): after steps at lane distance 4, 2, 1 lane j holds row j.
 constexpr int kScanU = 8;
-constexpr int kScanDepth = 5;
-constexpr int kScanStageBytes = (kScanU + 1) * 16 * kThreads;   // 36 KB
-static_assert(kScanDepth * kScanStageBytes <= kRingBytes - 8192, "scan ring must fit");
+constexpr int kScanDepth = 4;
+constexpr int kScanLaneChunks = kScanU + 2;                          // 8 rows + 2 query chunks
+constexpr int kScanStageBytes = kScanLaneChunks * 16 * kThreads;     // 40 KB
 constexpr int kScanRoundTiles = 32;   // tiles per round when sub-results are combined in smem
+static_assert(kScanDepth * kScanStageBytes + kScanRoundTiles * 32 * 12 <= kRingBytes,
+              "scan ring must fit");
 
 struct ScanCursor {
-  int k, hi, b;                 // tile of the round, head of this half-warp, batch of the tile
+  int k, hi, b;                 // tile of the round, head of this octet, batch of the tile
   int n, tile, P, req, cbeg, cend, s_begin, s_end;
   int tail, off_lo, off_hi;     // logical position of slot s: s + (s < tail ? off_lo : off_hi)
   bool elig;
@@ -337,6 +351,24 @@ __device__ __forceinline__ void scan_load_tile(const MacB200DecodeArgs& a, int g
   }
 }
 
+// sum over 8 dims of (q - c)^2, sequential FMAs from 0 (one lane's share of a row)
+__device__ __forceinline__ float scan_dist8(const float (&q)[8], const uint4& raw) {
+  float t = 0.0f, diff;
+  diff = q[0] - bf16_lo(raw.x); t = __fmaf_rn(diff, diff, t);
+  diff = q[1] - bf16_hi(raw.x); t = __fmaf_rn(diff, diff, t);
+  diff = q[2] - bf16_lo(raw.y); t = __fmaf_rn(diff, diff, t);
+  diff = q[3] - bf16_hi(raw.y); t = __fmaf_rn(diff, diff, t);
+  diff = q[4] - bf16_lo(raw.z); t = __fmaf_rn(diff, diff, t);
+  diff = q[5] - bf16_hi(raw.z); t = __fmaf_rn(diff, diff, t);
+  diff = q[6] - bf16_lo(raw.w); t = __fmaf_rn(diff, diff, t);
+  diff = q[7] - bf16_hi(raw.w); t = __fmaf_rn(diff, diff, t);
+  return t;
+}
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x); f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
+  f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z); f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
+}
+
 __device__ void phase_match_scan(const DecodeParams& p, uint8_t* smem) {
   const MacB200DecodeArgs& a = p.a;
   const int tid = threadIdx.x;
@@ -350,38 +382,40 @@ __device__ void phase_match_scan(const DecodeParams& p, uint8_t* smem) {
 
   const int Hq = a.Hq, M = a.M, Tm = a.max_match_tiles;
   int p2 = 1;
-  while (p2 < Hq && p2 < 16) p2 <<= 1;   // heads scanned side by side
-  const int spar = 16 / p2;              // slots scanned side by side (only when Hq < 16)
-  const int hw = tid >> 4, tx = tid & 15;
-  const int hslot = hw % p2, sub = hw / p2;
-  const unsigned sub_mask = (tid & 16) ? 0xffff0000u : 0x0000ffffu;
-  const int nh = hslot < Hq ? (Hq - hslot + p2 - 1) / p2 : 0;          // heads of this half-warp
+  while (p2 < Hq && p2 < 32) p2 <<= 1;   // heads scanned side by side
+  const int spar = 32 / p2;              // slots scanned side by side (only when Hq < 32)
+  const int oct = tid >> 3, j = tid & 7;
+  const int hslot = oct % p2, sub = oct / p2;
+  const int oct_shift = ((tid & 31) >> 3) * 8;
+  const unsigned oct_mask = 0xffu << oct_shift;
+  const int nh = hslot < Hq ? (Hq - hslot + p2 - 1) / p2 : 0;          // heads of this octet
   const int nb = (a.match_tile_slots + kScanU * spar - 1) / (kScanU * spar);  // batches per tile
   const int total_tiles = a.N * Tm;
   const int my_tiles = static_cast<int>(blockIdx.x) < total_tiles
-                           ? (total_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
-                                 static_cast<int>(gridDim.x)
+                           ? (total_tiles - static_cast<int>(blockIdx.x) +
+                              static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x)
                            : 0;
   const int round_tiles = spar > 1 ? kScanRoundTiles : (my_tiles > 0 ? my_tiles : 1);
   const char* ring = static_cast<const char*>(a.query_cache);
   const char* qsrc = static_cast<const char*>(a.q_pre);
   const uint32_t lane_base = smem_u32(smem) + tid * 16;
   const uint8_t* lane_ptr = smem + tid * 16;
+  const int64_t slot_stride = static_cast<int64_t>(Hq) * kRowBytes * spar;  // bytes between rows of a batch
+  const float thr = p.thr_dist;
   // partial (per sub) results of a round, only used when spar > 1
   float* part_d = reinterpret_cast<float*>(smem + kScanDepth * kScanStageBytes);
-  int* part_p = reinterpret_cast<int*>(part_d + kScanRoundTiles * 16);
-  int* part_s = part_p + kScanRoundTiles * 16;
+  int* part_p = reinterpret_cast<int*>(part_d + kScanRoundTiles * 32);
+  int* part_s = part_p + kScanRoundTiles * 32;
 
   for (int r0 = 0; r0 < my_tiles; r0 += round_tiles) {
     const int rt = min(round_tiles, my_tiles - r0);
     const int nseq = rt * nh * nb;
     ScanCursor ci, cc;   // issue side, consume side
     ci.k = ci.hi = ci.b = 0;
-    cc.k = cc.hi = cc.b = 0;
-    if (nseq > 0) {
-      scan_load_tile(a, blockIdx.x + r0 * gridDim.x, ci);
-      cc = ci;
-    }
+    if (nseq > 0) scan_load_tile(a, blockIdx.x + r0 * gridDim.x, ci);
+    else { ci.elig = false; ci.s_begin = ci.s_end = 0; ci.P = 0; ci.req = 0; ci.n = 0; ci.tile = 0;
+           ci.cbeg = ci.cend = 0; ci.tail = ci.off_lo = ci.off_hi = 0; }
+    cc = ci;
     auto advance = [&](ScanCursor& c) {
       if (++c.b == nb) {
         c.b = 0;
@@ -391,25 +425,44 @@ __device__ void phase_match_scan(const DecodeParams& p, uint8_t* smem) {
         }
       }
     };
+    // first slot of the cursor's batch, address of its first row chunk for this lane
+    auto batch_first_slot = [&](const ScanCursor& c) { return c.s_begin + sub + c.b * kScanU * spar; };
+    auto row_ptr = [&](const ScanCursor& c, int s, int h) {
+      return ring + ((static_cast<int64_t>(c.req) * M + s) * Hq + h) * kRowBytes + j * 16;
+    };
+    auto batch_all_valid = [&](const ScanCursor& c, int s_first) {
+      const int s_last = s_first + (kScanU - 1) * spar;
+      return s_last < c.s_end && ((s_first < c.tail) == (s_last < c.tail)) &&
+             scan_slot_pos(c, s_first) >= c.cbeg && scan_slot_pos(c, s_last) < c.cend;
+    };
     auto issue = [&](int seq) {
       if (ci.elig) {
         const int h = hslot + ci.hi * p2;
         const uint32_t dst = lane_base + (seq % kScanDepth) * kScanStageBytes;
-        const int64_t row0 = (static_cast<int64_t>(ci.req) * M) * Hq + h;
+        const int s_first = batch_first_slot(ci);
+        const char* src = row_ptr(ci, s_first, h);
         bool any = false;
+        if (batch_all_valid(ci, s_first)) {
 #pragma unroll
-        for (int u = 0; u < kScanU; ++u) {
-          const int s = ci.s_begin + sub + (ci.b * kScanU + u) * spar;
-          const int pos = scan_slot_pos(ci, s);
-          if (s < ci.s_end && pos >= ci.cbeg && pos < ci.cend) {
-            cp_async16(dst + u * (kThreads * 16),
-                       ring + (row0 + static_cast<int64_t>(s) * Hq) * kRowBytes + tx * 16, 16);
-            any = true;
+          for (int u = 0; u < kScanU; ++u)
+            cp_async16(dst + u * (kThreads * 16), src + u * slot_stride, 16);
+          any = true;
+        } else {
+#pragma unroll
+          for (int u = 0; u < kScanU; ++u) {
+            const int s = s_first + u * spar;
+            const int pos = scan_slot_pos(ci, s);
+            if (s < ci.s_end && pos >= ci.cbeg && pos < ci.cend) {
+              cp_async16(dst + u * (kThreads * 16), src + u * slot_stride, 16);
+              any = true;
+            }
           }
         }
-        if (any)
-          cp_async16(dst + kScanU * (kThreads * 16),
-                     qsrc + (static_cast<int64_t>(ci.n) * Hq + h) * kRowBytes + tx * 16, 16);
+        if (any) {
+          const char* q = qsrc + (static_cast<int64_t>(ci.n) * Hq + h) * kRowBytes + j * 16;
+          cp_async16(dst + kScanU * (kThreads * 16), q, 16);
+          cp_async16(dst + (kScanU + 1) * (kThreads * 16), q + 128, 16);
+        }
       }
       advance(ci);
     };
@@ -425,69 +478,61 @@ __device__ void phase_match_scan(const DecodeParams& p, uint8_t* smem) {
       cp_async_wait<kScanDepth - 2>();
       if (cc.b == 0) { bd = INFINITY; bp = INT_MAX; bs = -1; }
       if (cc.elig) {
-        // All 8 rows of the batch are evaluated in straight-line code (rows
-        // that were not copied give garbage that is masked below), then summed
-        // across the 16 lanes by a halving exchange: after the steps at lane
-        // distance 8, 4, 2 each lane holds the partial sum of ONE row, the
-        // last step completes it.  Every addition pairs the same two operands
-        // as the reference's xor butterfly, so the result is bit-identical
-        // with a quarter of the shuffles.
         const uint8_t* src = lane_ptr + (seq % kScanDepth) * kScanStageBytes;
-        const uint4 qv = *reinterpret_cast<const uint4*>(src + kScanU * (kThreads * 16));
-        const float q0 = bf16_lo(qv.x), q1 = bf16_hi(qv.x), q2 = bf16_lo(qv.y), q3 = bf16_hi(qv.y);
-        const float q4 = bf16_lo(qv.z), q5 = bf16_hi(qv.z), q6 = bf16_lo(qv.w), q7 = bf16_hi(qv.w);
+        float qlo[8];
+        unpack8(*reinterpret_cast<const uint4*>(src + kScanU * (kThreads * 16)), qlo);
         float acc[kScanU];
 #pragma unroll
-        for (int u = 0; u < kScanU; ++u) {
-          const uint4 raw = *reinterpret_cast<const uint4*>(src + u * (kThreads * 16));
-          float t = 0.0f, diff;
-          diff = q0 - bf16_lo(raw.x); t = __fmaf_rn(diff, diff, t);
-          diff = q1 - bf16_hi(raw.x); t = __fmaf_rn(diff, diff, t);
-          diff = q2 - bf16_lo(raw.y); t = __fmaf_rn(diff, diff, t);
-          diff = q3 - bf16_hi(raw.y); t = __fmaf_rn(diff, diff, t);
-          diff = q4 - bf16_lo(raw.z); t = __fmaf_rn(diff, diff, t);
-          diff = q5 - bf16_hi(raw.z); t = __fmaf_rn(diff, diff, t);
-          diff = q6 - bf16_lo(raw.w); t = __fmaf_rn(diff, diff, t);
-          diff = q7 - bf16_hi(raw.w); t = __fmaf_rn(diff, diff, t);
-          acc[u] = t;
-        }
-        const bool b3 = (tx & 8) != 0, b2 = (tx & 4) != 0, b1 = (tx & 2) != 0;
+        for (int u = 0; u < kScanU; ++u)
+          acc[u] = scan_dist8(qlo, *reinterpret_cast<const uint4*>(src + u * (kThreads * 16)));
+        // halving exchange over the octet: lane j ends with the probe sum of row j
+        const bool b2 = (j & 4) != 0, b1 = (j & 2) != 0, b0 = (j & 1) != 0;
         float w4[4];
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
-          const float send = b3 ? acc[r] : acc[r + 4];
-          const float keep = b3 ? acc[r + 4] : acc[r];
-          w4[r] = __fadd_rn(keep, __shfl_xor_sync(sub_mask, send, 8, 16));
+          const float send = b2 ? acc[r] : acc[r + 4];
+          const float keep = b2 ? acc[r + 4] : acc[r];
+          w4[r] = __fadd_rn(keep, __shfl_xor_sync(oct_mask, send, 4, 8));
         }
         float w2[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-          const float send = b2 ? w4[r] : w4[r + 2];
-          const float keep = b2 ? w4[r + 2] : w4[r];
-          w2[r] = __fadd_rn(keep, __shfl_xor_sync(sub_mask, send, 4, 16));
+          const float send = b1 ? w4[r] : w4[r + 2];
+          const float keep = b1 ? w4[r + 2] : w4[r];
+          w2[r] = __fadd_rn(keep, __shfl_xor_sync(oct_mask, send, 2, 8));
         }
-        const float send1 = b1 ? w2[0] : w2[1];
-        const float keep1 = b1 ? w2[1] : w2[0];
-        const float w1 = __fadd_rn(keep1, __shfl_xor_sync(sub_mask, send1, 2, 16));
-        const float dist = __fadd_rn(w1, __shfl_xor_sync(sub_mask, w1, 1, 16));
-        const int row = (b3 ? 4 : 0) + (b2 ? 2 : 0) + (b1 ? 1 : 0);   // the row this lane ends up with
-        const int s = cc.s_begin + sub + (cc.b * kScanU + row) * spar;
-        const int pos = scan_slot_pos(cc, s);
-        if (s < cc.s_end && pos >= cc.cbeg && pos < cc.cend && better_pair(dist, pos, bd, bp)) {
-          bd = dist; bp = pos; bs = s;
-        }
-      }
-      if (cc.b == nb - 1) {
-        // argmin over the 16 lanes (each tracked its own rows), (distance, older position) order
+        const float send0 = b0 ? w2[0] : w2[1];
+        const float keep0 = b0 ? w2[1] : w2[0];
+        const float probe = __fadd_rn(keep0, __shfl_xor_sync(oct_mask, send0, 1, 8));
+        const int s_first = batch_first_slot(cc);
+        const int s_mine = s_first + j * spar;
+        const int pos_mine = scan_slot_pos(cc, s_mine);
+        const bool survive = s_mine < cc.s_end && pos_mine >= cc.cbeg && pos_mine < cc.cend &&
+                             probe < thr;   // NaN probes drop out here as well
+        const unsigned live = (__ballot_sync(oct_mask, survive) >> oct_shift) & 0xffu;
+        if (live != 0u) {   // octet-uniform; rare unless the ring really holds near rows
+          const int h = hslot + cc.hi * p2;
+          const char* rows = row_ptr(cc, s_first, h) + 128;
+          float qhi[8];
+          unpack8(*reinterpret_cast<const uint4*>(src + (kScanU + 1) * (kThreads * 16)), qhi);
+          uint4 raw2[kScanU];
 #pragma unroll
-        for (int off = 8; off > 1; off >>= 1) {
-          const float od = __shfl_xor_sync(sub_mask, bd, off, 16);
-          const int op = __shfl_xor_sync(sub_mask, bp, off, 16);
-          const int os = __shfl_xor_sync(sub_mask, bs, off, 16);
-          if (better_pair(od, op, bd, bp)) { bd = od; bp = op; bs = os; }
+          for (int u = 0; u < kScanU; ++u)
+            if ((live >> u) & 1u) raw2[u] = ld_stream16(rows + u * slot_stride);
+#pragma unroll
+          for (int u = 0; u < kScanU; ++u) {
+            if (!((live >> u) & 1u)) continue;
+            float d = __fadd_rn(acc[u], scan_dist8(qhi, raw2[u]));          // lane distance 8
+            d = __fadd_rn(d, __shfl_xor_sync(oct_mask, d, 4, 8));
+            d = __fadd_rn(d, __shfl_xor_sync(oct_mask, d, 2, 8));
+            d = __fadd_rn(d, __shfl_xor_sync(oct_mask, d, 1, 8));
+            const int s = s_first + u * spar;
+            const int pos = scan_slot_pos(cc, s);
+            if (better_pair(d, pos, bd, bp)) { bd = d; bp = pos; bs = s; }
+          }
         }
       }
-      if (cc.b == nb - 1 && tx == 0) {
+      if (cc.b == nb - 1 && j == 0) {
         const int h = hslot + cc.hi * p2;
         if (spar == 1) {
           const int64_t off = (static_cast<int64_t>(cc.n) * Hq + h) * Tm + cc.tile;
@@ -495,7 +540,7 @@ __device__ void phase_match_scan(const DecodeParams& p, uint8_t* smem) {
           a.match_pos[off] = bp;
           a.match_slot[off] = bs;
         } else {
-          const int e = cc.k * 16 + h * spar + sub;
+          const int e = cc.k * 32 + h * spar + sub;
           part_d[e] = bd; part_p[e] = bp; part_s[e] = bs;
         }
       }
@@ -512,7 +557,7 @@ __device__ void phase_match_scan(const DecodeParams& p, uint8_t* smem) {
         float d0 = INFINITY;
         int p0 = INT_MAX, s0 = -1;
         for (int s = 0; s < spar; ++s) {
-          const int e = k * 16 + h * spar + s;
+          const int e = k * 32 + h * spar + s;
           if (better_pair(part_d[e], part_p[e], d0, p0)) { d0 = part_d[e]; p0 = part_p[e]; s0 = part_s[e]; }
         }
         const int g = blockIdx.x + (r0 + k) * gridDim.x;
