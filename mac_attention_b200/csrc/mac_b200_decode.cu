@@ -50,7 +50,9 @@ constexpr int kRingBytes = kWarps * kWarpRingBytes;      // 192 KB
 constexpr int kMaxGroups = 4096;           // N * Hkv upper bound of one launch
 constexpr int kMaxHq = 128;
 constexpr int kOvhTok = 256;               // cost of opening a segment, in token equivalents
-constexpr int kMinPieceTok = 2048;
+constexpr int kMinPieceTok = 768;
+constexpr unsigned kTwoWavePieceTok = 16384;  // second wave of pieces only above this piece size
+constexpr unsigned kFuseMaxCost = 8192;       // groups up to this cost are never split over pieces
 constexpr int kCombineRow = kD + 8;        // padded fp32 row of the cross-warp combine buffer
 constexpr int kSmemPerm = kMaxGroups * 2;              // u16 gperm[]
 constexpr int kSmemPrefix = (kMaxGroups + 1) * 4;      // u32 cost prefix
@@ -868,12 +870,14 @@ __device__ void build_schedule(const DecodeParams& p, Schedule& sc, unsigned lon
   __syncthreads();
   sc.W = static_cast<uint32_t>(ccarry);
   // Wave-quantised piece count: as many pieces as keep a piece above
-  // kMinPieceTok, at most two per CTA, and a whole multiple of the grid once
-  // there is at least one piece per CTA.
+  // kMinPieceTok; once there is a piece per CTA, exactly one or two per CTA.
   unsigned pieces = sc.W / kMinPieceTok;
   if (pieces < 1) pieces = 1;
-  if (pieces > 2u * gridDim.x) pieces = 2u * gridDim.x;
-  if (pieces > gridDim.x) pieces = (pieces / gridDim.x) * gridDim.x;
+  if (pieces > gridDim.x) {
+    // one wave of pieces, or two when each piece still amortises its fixed cost
+    const unsigned waves = (sc.W / gridDim.x >= 2u * kTwoWavePieceTok) ? 2u : 1u;
+    pieces = waves * gridDim.x;
+  }
   if (pieces > static_cast<unsigned>(p.max_pieces)) pieces = p.max_pieces;
   sc.pieces = pieces;
   sc.ps = (sc.W + pieces - 1) / pieces;
@@ -928,12 +932,20 @@ __device__ __forceinline__ void row_piece_span(const RowGeom& row, uint32_t ps, 
   p_hi = static_cast<int>((row.a + row.c - 1) / ps);
 }
 
-// Streams logical positions [t0, t1) of request n through KV head hkv for the
-// G query heads of the group and leaves the normalised partial (o, natural-log
-// LSE) of every head in arena slot `slot`.  `row_kind`: 0 sink, 1 band, 2 tail
-// (decides each head's own sub-range inside [t0, t1)).
-__device__ void attend_segment(const DecodeParams& p, uint8_t* smem, int n, int hkv, int t0,
-                               int t1, int row_kind, int slot) {
+// One warp's share of a token row: 16-token blocks first, first+stride, ... of
+// logical positions [t0, t1).  row_kind: 0 sink, 1 band, 2 tail (decides each
+// head's own sub-range inside [t0, t1)).
+struct WarpWork {
+  int t0, t1, row_kind, first, stride;
+};
+
+// Streams the warp's blocks of request n through KV head hkv for the G query
+// heads of the group: per-warp cp.async K/V ring, mma.sync contraction, online
+// softmax.  Leaves the warp's un-normalised accumulators (rows = heads), running
+// max (log2 domain) and denominator (already summed over the quad).
+__device__ __forceinline__ void warp_stream(const DecodeParams& p, uint8_t* smem, int n, int hkv,
+                                            const WarpWork& w, float (&oacc)[16][4], float& m_run,
+                                            float& l_run) {
   const MacB200DecodeArgs& a = p.a;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int G = p.G;
@@ -941,14 +953,15 @@ __device__ void attend_segment(const DecodeParams& p, uint8_t* smem, int n, int 
   const int hrow = lane >> 2, quad = lane & 3;
   const bool has_head = hrow < G;
   const int hq = hkv * G + (has_head ? hrow : 0);
+  const int t0 = w.t0, t1 = w.t1;
 
-  // this head's own range inside the segment
+  // this head's own range inside the row
   int lo = t0, hi = t1;
   if (has_head) {
     const int rs = __ldcg(a.head_rect_start + static_cast<int64_t>(n) * a.Hq + hq);
-    if (row_kind == 1) {
+    if (w.row_kind == 1) {
       lo = max(t0, rs);
-    } else if (row_kind == 0) {
+    } else if (w.row_kind == 0) {
       const int ne = cache_end_for_pos(P, a.semantic_pos_ahead);
       int sh = p.F < ne ? p.F : ne;
       if (sh > rs) sh = rs;
@@ -970,13 +983,13 @@ __device__ void attend_segment(const DecodeParams& p, uint8_t* smem, int n, int 
     }
   }
 
-  float oacc[16][4];
 #pragma unroll
   for (int j = 0; j < 16; ++j) { oacc[j][0] = oacc[j][1] = oacc[j][2] = oacc[j][3] = 0.0f; }
-  float m_run = -INFINITY, l_run = 0.0f;
+  m_run = -INFINITY;
+  l_run = 0.0f;
 
   const int nblk = (t1 - t0 + kBlkTok - 1) / kBlkTok;
-  const int mine = warp < nblk ? (nblk - warp + kWarps - 1) / kWarps : 0;
+  const int mine = (w.stride > 0 && w.first < nblk) ? (nblk - w.first + w.stride - 1) / w.stride : 0;
   uint8_t* ring = smem + warp * kWarpRingBytes;
   const uint32_t ring_u32 = smem_u32(ring);
   const char* kbase = static_cast<const char*>(a.k_buffer) + static_cast<int64_t>(hkv) * kRowBytes;
@@ -986,7 +999,7 @@ __device__ void attend_segment(const DecodeParams& p, uint8_t* smem, int n, int 
 
   // pool row of the lane's token (lanes 0..15) of this warp's j-th block; -1 = past the end
   auto load_token = [&](int j) -> int64_t {
-    const int pos = t0 + (warp + j * kWarps) * kBlkTok + (lane & 15);
+    const int pos = t0 + (w.first + j * w.stride) * kBlkTok + (lane & 15);
     if (pos >= t1) return -1;
     if (pos == P) {
       return a.out_cache_loc_is_i64
@@ -1023,7 +1036,7 @@ __device__ void attend_segment(const DecodeParams& p, uint8_t* smem, int n, int 
     __syncwarp();
     const uint32_t kst = ring_u32 + (j % kStages) * kStageBytes;
     const uint32_t vst = kst + kBlkTok * kRowBytes;
-    const int tb = t0 + (warp + j * kWarps) * kBlkTok;
+    const int tb = t0 + (w.first + j * w.stride) * kBlkTok;
 
     // S = Q K^T for 16 tokens: two n-blocks of 8 tokens
     float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -1086,50 +1099,83 @@ __device__ void attend_segment(const DecodeParams& p, uint8_t* smem, int n, int 
   cp_async_wait<0>();
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+}
 
-  // cross-warp combine through shared memory (the K/V ring is idle now)
-  __syncthreads();
-  float* comb_o = reinterpret_cast<float*>(smem);                    // [kWarps][8][kCombineRow]
-  float* comb_m = comb_o + kWarps * 8 * kCombineRow;                 // [kWarps][8]
-  float* comb_l = comb_m + kWarps * 8;
-  {
-    float* dst = comb_o + (warp * 8 + hrow) * kCombineRow + quad * 2;
+// Cross-warp combine buffer in shared memory (aliases the idle K/V ring).
+struct CombineBuf {
+  float* o;   // [kWarps][8][kCombineRow]
+  float* m;   // [kWarps][8]
+  float* l;   // [kWarps][8]
+};
+__device__ __forceinline__ CombineBuf combine_buf(uint8_t* smem) {
+  CombineBuf c;
+  c.o = reinterpret_cast<float*>(smem);
+  c.m = c.o + kWarps * 8 * kCombineRow;
+  c.l = c.m + kWarps * 8;
+  return c;
+}
+// Every warp publishes its accumulators; returns after the CTA-wide barrier.
+__device__ __forceinline__ void combine_publish(uint8_t* smem, const float (&oacc)[16][4],
+                                                float m_run, float l_run) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int hrow = lane >> 2, quad = lane & 3;
+  __syncthreads();  // every warp is done with its K/V ring
+  const CombineBuf cb = combine_buf(smem);
+  float* dst = cb.o + (warp * 8 + hrow) * kCombineRow + quad * 2;
 #pragma unroll
-    for (int jj = 0; jj < 16; ++jj)
-      *reinterpret_cast<float2*>(dst + jj * 8) = make_float2(oacc[jj][0], oacc[jj][1]);
-    if (quad == 0) {
-      comb_m[warp * 8 + hrow] = m_run;
-      comb_l[warp * 8 + hrow] = l_run;
-    }
+  for (int jj = 0; jj < 16; ++jj)
+    *reinterpret_cast<float2*>(dst + jj * 8) = make_float2(oacc[jj][0], oacc[jj][1]);
+  if (quad == 0) {
+    cb.m[warp * 8 + hrow] = m_run;
+    cb.l[warp * 8 + hrow] = l_run;
   }
   __syncthreads();
-  if (warp < G) {
-    const int h = warp;  // warp h finalises head h; lane owns dims [4*lane, 4*lane+4)
-    float mx = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, comb_m[w * 8 + h]);
-    float lsum = 0.0f;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (mx != -INFINITY) {
-#pragma unroll
-      for (int w = 0; w < kWarps; ++w) {
-        const float wgt = ex2(comb_m[w * 8 + h] - mx);
-        lsum += comb_l[w * 8 + h] * wgt;
-        const float4 o = *reinterpret_cast<const float4*>(comb_o + (w * 8 + h) * kCombineRow + lane * 4);
-        acc.x += o.x * wgt; acc.y += o.y * wgt; acc.z += o.z * wgt; acc.w += o.w * wgt;
-      }
+}
+// Head h's normalised partial over warps [w_lo, w_hi): lane owns dims [4*lane, 4*lane+4);
+// lse is the natural-log LSE, -inf when the warps saw no token of the head.
+__device__ __forceinline__ void combine_reduce(uint8_t* smem, int h, int w_lo, int w_hi,
+                                               float4& acc, float& lse) {
+  const int lane = threadIdx.x & 31;
+  const CombineBuf cb = combine_buf(smem);
+  float mx = -INFINITY;
+  for (int w = w_lo; w < w_hi; ++w) mx = fmaxf(mx, cb.m[w * 8 + h]);
+  float lsum = 0.0f;
+  acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (mx != -INFINITY) {
+    for (int w = w_lo; w < w_hi; ++w) {
+      const float wgt = ex2(cb.m[w * 8 + h] - mx);
+      lsum += cb.l[w * 8 + h] * wgt;
+      const float4 o = *reinterpret_cast<const float4*>(cb.o + (w * 8 + h) * kCombineRow + lane * 4);
+      acc.x += o.x * wgt; acc.y += o.y * wgt; acc.z += o.z * wgt; acc.w += o.w * wgt;
     }
-    float lse = -INFINITY;
-    if (lsum > 0.0f) {
-      const float inv = 1.0f / lsum;
-      acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
-      lse = (mx + lg2(lsum)) * kLn2;
-    } else {
-      acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    float* po = p.ar.part_o + (static_cast<int64_t>(slot) * G + h) * kD + lane * 4;
+  }
+  lse = -INFINITY;
+  if (lsum > 0.0f) {
+    const float inv = 1.0f / lsum;
+    acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+    lse = (mx + lg2(lsum)) * kLn2;
+  } else {
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
+// One segment by the whole CTA: warp w takes blocks w, w+8, ...; the normalised
+// partial (o, natural-log LSE) of every head goes to arena slot `slot`.
+__device__ void attend_segment(const DecodeParams& p, uint8_t* smem, int n, int hkv, int t0,
+                               int t1, int row_kind, int slot) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float oacc[16][4];
+  float m_run, l_run;
+  const WarpWork w{t0, t1, row_kind, warp, kWarps};
+  warp_stream(p, smem, n, hkv, w, oacc, m_run, l_run);
+  combine_publish(smem, oacc, m_run, l_run);
+  if (warp < p.G) {
+    float4 acc;
+    float lse;
+    combine_reduce(smem, warp, 0, kWarps, acc, lse);
+    float* po = p.ar.part_o + (static_cast<int64_t>(slot) * p.G + warp) * kD + lane * 4;
     __stcg(reinterpret_cast<float4*>(po), acc);
-    if (lane == 0) __stcg(p.ar.part_lse + static_cast<int64_t>(slot) * 8 + h, lse);
+    if (lane == 0) __stcg(p.ar.part_lse + static_cast<int64_t>(slot) * 8 + warp, lse);
   }
   __syncthreads();  // combine buffer is free again
 }
@@ -1151,28 +1197,18 @@ __device__ __forceinline__ void merge_state(float4& o, float& lse, const float4&
   lse = m + logf(den);
 }
 
-// Runs in the CTA that retired the group's last segment: prefix state (+) band
-// partials -> ring row; (+) sink (+) tail partials -> output.  Warp h owns
-// head h, lane owns 4 dims.  Order of operations: DEC.cu:4346-4365, 4485-4520.
-__device__ void merge_group(const DecodeParams& p, const Schedule& sc, int v_idx, int g,
-                            const GroupPlan& pl) {
-  const MacB200DecodeArgs& a = p.a;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (warp >= p.G) return;
-  const int G = p.G, Hq = a.Hq, M = a.M;
-  const int n = g / a.Hkv, hkv = g - n * a.Hkv;
-  const int hq = hkv * G + warp;
-  const int64_t ho = static_cast<int64_t>(n) * Hq + hq;
-  const int req = a.req_ids[n], P = a.past_lens[n];
-  RowGeom rows[3];
-  group_rows(pl, sc.cpre[v_idx], rows);
-
-  float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-  float lse = -INFINITY;
+// Reused prefix state of head hq (warp-wide; lane owns 4 dims): the matched
+// ring row if the head is a hit with a finite LSE, else empty (DEC.cu:4346-4365).
+__device__ __forceinline__ void load_prefix_state(const MacB200DecodeArgs& a, int n, int hq,
+                                                  float4& o, float& lse) {
+  const int lane = threadIdx.x & 31;
+  const int64_t ho = static_cast<int64_t>(n) * a.Hq + hq;
+  o = make_float4(0.f, 0.f, 0.f, 0.f);
+  lse = -INFINITY;
   const int hit = __ldcg(a.head_hit + ho);
   const int mslot = __ldcg(a.head_match_slot + ho);
   if (hit != 0 && mslot >= 0) {
-    const int64_t row = (static_cast<int64_t>(req) * M + mslot) * Hq + hq;
+    const int64_t row = (static_cast<int64_t>(a.req_ids[n]) * a.M + mslot) * a.Hq + hq;
     const float pl_lse = a.lse_cache[row];
     if (isfinite(pl_lse)) {
       const uint2 raw = *reinterpret_cast<const uint2*>(
@@ -1181,6 +1217,62 @@ __device__ void merge_group(const DecodeParams& p, const Schedule& sc, int v_idx
       lse = pl_lse;
     }
   }
+}
+
+// Ring row P mod M of this step (query, state, LSE); only for requests whose
+// cache passes the readiness gate (DEC.cu:4485-4497).
+__device__ __forceinline__ void write_ring_row(const MacB200DecodeArgs& a, int n, int hq,
+                                               const float4& o, float lse) {
+  const int lane = threadIdx.x & 31;
+  const int req = a.req_ids[n];
+  if (!request_ready(a, req)) return;
+  const int64_t ho = static_cast<int64_t>(n) * a.Hq + hq;
+  const int dest = a.past_lens[n] % a.M;
+  const int64_t row = (static_cast<int64_t>(req) * a.M + dest) * a.Hq + hq;
+  const bool ok = isfinite(lse);
+  const uint2 qv = *reinterpret_cast<const uint2*>(static_cast<const char*>(a.q_pre) +
+                                                   ho * kRowBytes + lane * 8);
+  *reinterpret_cast<uint2*>(static_cast<char*>(a.query_cache) + row * kRowBytes + lane * 8) = qv;
+  uint2 ov = make_uint2(0u, 0u);
+  if (ok) {
+    ov.x = pack_bf16x2(o.x, o.y);
+    ov.y = pack_bf16x2(o.z, o.w);
+  }
+  *reinterpret_cast<uint2*>(static_cast<char*>(a.attn_cache) + row * kRowBytes + lane * 8) = ov;
+  if (lane == 0) a.lse_cache[row] = ok ? lse : -INFINITY;
+}
+
+__device__ __forceinline__ void write_output(const MacB200DecodeArgs& a, int n, int hq,
+                                             const float4& o, float lse) {
+  const int lane = threadIdx.x & 31;
+  const int64_t ho = static_cast<int64_t>(n) * a.Hq + hq;
+  const bool ok = isfinite(lse);
+  uint2 ov = make_uint2(0u, 0u);
+  if (ok) {
+    ov.x = pack_bf16x2(o.x, o.y);
+    ov.y = pack_bf16x2(o.z, o.w);
+  }
+  *reinterpret_cast<uint2*>(static_cast<char*>(a.out) + ho * kRowBytes + lane * 8) = ov;
+  if (lane == 0 && a.optional_lse) a.optional_lse[ho] = ok ? lse : -INFINITY;
+}
+
+// Runs in the CTA that retired the group's last segment: prefix state (+) band
+// partials -> ring row; (+) sink (+) tail partials -> output.  Warp h owns
+// head h, lane owns 4 dims.  Order of operations: DEC.cu:4346-4365, 4485-4520.
+__device__ void merge_group(const DecodeParams& p, const Schedule& sc, int v_idx, int g,
+                            const GroupPlan& pl) {
+  const MacB200DecodeArgs& a = p.a;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (warp >= p.G) return;
+  const int G = p.G;
+  const int n = g / a.Hkv, hkv = g - n * a.Hkv;
+  const int hq = hkv * G + warp;
+  RowGeom rows[3];
+  group_rows(pl, sc.cpre[v_idx], rows);
+
+  float4 o;
+  float lse;
+  load_prefix_state(a, n, hq, o, lse);
   auto merge_row = [&](int r) {
     if (rows[r].c == 0) return;
     int p_lo, p_hi;
@@ -1195,34 +1287,71 @@ __device__ void merge_group(const DecodeParams& p, const Schedule& sc, int v_idx
     }
   };
   merge_row(1);
-  // ring row of this step, only for requests whose cache is ready
-  if (request_ready(a, req)) {
-    const int dest = P % M;
-    const int64_t row = (static_cast<int64_t>(req) * M + dest) * Hq + hq;
-    const bool ok = isfinite(lse);
-    const uint2 qv = *reinterpret_cast<const uint2*>(static_cast<const char*>(a.q_pre) +
-                                                     ho * kRowBytes + lane * 8);
-    *reinterpret_cast<uint2*>(static_cast<char*>(a.query_cache) + row * kRowBytes + lane * 8) = qv;
-    uint2 ov = make_uint2(0u, 0u);
-    if (ok) {
-      ov.x = pack_bf16x2(o.x, o.y);
-      ov.y = pack_bf16x2(o.z, o.w);
-    }
-    *reinterpret_cast<uint2*>(static_cast<char*>(a.attn_cache) + row * kRowBytes + lane * 8) = ov;
-    if (lane == 0) a.lse_cache[row] = ok ? lse : -INFINITY;
-  }
+  write_ring_row(a, n, hq, o, lse);
   merge_row(0);
   merge_row(2);
-  {
-    const bool ok = isfinite(lse);
-    uint2 ov = make_uint2(0u, 0u);
-    if (ok) {
-      ov.x = pack_bf16x2(o.x, o.y);
-      ov.y = pack_bf16x2(o.z, o.w);
-    }
-    *reinterpret_cast<uint2*>(static_cast<char*>(a.out) + ho * kRowBytes + lane * 8) = ov;
-    if (lane == 0 && a.optional_lse) a.optional_lse[ho] = ok ? lse : -INFINITY;
+  write_output(a, n, hq, o, lse);
+}
+
+// A group whose three rows all fall inside one piece is finished by this CTA
+// alone in a single pass: the 8 warps are split over the rows in proportion to
+// their 16-token blocks, all rows stream at once, and after one shared-memory
+// combine warp h merges head h in registers (prefix (+) band -> ring row;
+// (+) sink (+) tail -> output).  No arena traffic, no arrival counter.
+__device__ void attend_group_fused(const DecodeParams& p, uint8_t* smem, int n, int hkv,
+                                   const GroupPlan& pl) {
+  const MacB200DecodeArgs& a = p.a;
+  const int warp = threadIdx.x >> 5;
+  const int G = p.G;
+  const int begin[3] = {0, pl.band_lo, pl.new_end};
+  const int end[3] = {pl.sink_hi, pl.new_end, pl.kv_len};
+  int nblk[3], nw[3] = {0, 0, 0};
+  int left = kWarps;
+#pragma unroll
+  for (int r = 0; r < 3; ++r) {
+    const int len = end[r] - begin[r];
+    nblk[r] = len > 0 ? (len + kBlkTok - 1) / kBlkTok : 0;
+    if (nblk[r] > 0) { nw[r] = 1; --left; }
   }
+  while (left > 0) {  // next warp goes to the row with the most blocks per warp
+    int best = -1;
+    float load = 0.0f;
+#pragma unroll
+    for (int r = 0; r < 3; ++r) {
+      if (nw[r] == 0) continue;
+      const float l = static_cast<float>(nblk[r]) / static_cast<float>(nw[r]);
+      if (l > load) { load = l; best = r; }
+    }
+    if (best < 0 || load <= 1.0f) break;
+    ++nw[best];
+    --left;
+  }
+  const int base[3] = {0, nw[0], nw[0] + nw[1]};
+  WarpWork w{0, 0, 2, 0, 0};
+#pragma unroll
+  for (int r = 0; r < 3; ++r)
+    if (warp >= base[r] && warp < base[r] + nw[r]) w = WarpWork{begin[r], end[r], r, warp - base[r], nw[r]};
+
+  // the reused prefix state is fetched up front so its latency hides behind the stream
+  float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+  float lse = -INFINITY;
+  const int hq = hkv * G + (warp < G ? warp : 0);
+  if (warp < G) load_prefix_state(a, n, hq, o, lse);
+
+  float oacc[16][4];
+  float m_run, l_run;
+  warp_stream(p, smem, n, hkv, w, oacc, m_run, l_run);
+  combine_publish(smem, oacc, m_run, l_run);
+  if (warp < G) {
+    float4 o2;
+    float l2;
+    if (nw[1] > 0) { combine_reduce(smem, warp, base[1], base[1] + nw[1], o2, l2); merge_state(o, lse, o2, l2); }
+    write_ring_row(a, n, hq, o, lse);
+    if (nw[0] > 0) { combine_reduce(smem, warp, base[0], base[0] + nw[0], o2, l2); merge_state(o, lse, o2, l2); }
+    if (nw[2] > 0) { combine_reduce(smem, warp, base[2], base[2] + nw[2], o2, l2); merge_state(o, lse, o2, l2); }
+    write_output(a, n, hq, o, lse);
+  }
+  __syncthreads();  // combine buffer is free again
 }
 
 __device__ void phase_attend(const DecodeParams& p, uint8_t* smem) {
@@ -1268,6 +1397,13 @@ __device__ void phase_attend(const DecodeParams& p, uint8_t* smem) {
         pl.cls = w1.x; pl.cost = w1.y; pl.mode = w1.z; pl.bad = w1.w;
       }
       const int n = g / p.a.Hkv, hkv = g - n * p.a.Hkv;
+      // A small group is never split: it belongs to the piece that holds its
+      // first cost unit and is finished there in one fused pass.
+      const uint32_t gcost = sc.cpre[v + 1] - sc.cpre[v];
+      if (gcost <= kFuseMaxCost && gcost <= 2u * sc.ps) {
+        if (sc.cpre[v] >= x0) attend_group_fused(p, smem, n, hkv, pl);
+        continue;
+      }
       RowGeom rows[3];
       group_rows(pl, sc.cpre[v], rows);
       int expected = 0, done_here = 0;
