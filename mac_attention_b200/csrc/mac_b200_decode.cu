@@ -444,13 +444,13 @@ __device__ void phase_match_scan(const DecodeParams& p, uint8_t* smem) {
         const int s_first = batch_first_slot(ci);
         const char* src = row_ptr(ci, s_first, h);
         bool any = false;
-        if (batch_all_valid(ci, s_first)) {
+        if (__builtin_expect(batch_all_valid(ci, s_first), 1)) {
 #pragma unroll
           for (int u = 0; u < kScanU; ++u)
             cp_async16(dst + u * (kThreads * 16), src + u * slot_stride, 16);
           any = true;
         } else {
-#pragma unroll
+#pragma unroll 1
           for (int u = 0; u < kScanU; ++u) {
             const int s = s_first + u * spar;
             const int pos = scan_slot_pos(ci, s);
@@ -512,7 +512,7 @@ __device__ void phase_match_scan(const DecodeParams& p, uint8_t* smem) {
         const bool survive = s_mine < cc.s_end && pos_mine >= cc.cbeg && pos_mine < cc.cend &&
                              probe < thr;   // NaN probes drop out here as well
         const unsigned live = (__ballot_sync(oct_mask, survive) >> oct_shift) & 0xffu;
-        if (live != 0u) {   // octet-uniform; rare unless the ring really holds near rows
+        if (__builtin_expect(live != 0u, 0)) {   // octet-uniform; rare unless the ring holds near rows
           const int h = hslot + cc.hi * p2;
           const char* rows = row_ptr(cc, s_first, h) + 128;
           float qhi[8];
