@@ -35,6 +35,9 @@ sys.path.insert(0, str(ROOT))
 HQ, HKV, DIM = 32, 8, 128
 CAPACITY, SEM, TILE, MTS, MAX_CONTEXT = 2048, 256, 32, 32, 131072
 LAG = 64
+# dram__bytes_read+write / bytes requested by the kernel, from the ncu captures
+# summarised under profiles/ (small cases, scaled by the units processed)
+NCU_TRAFFIC_RATIO = 1.02
 
 
 def parse_args():
@@ -58,6 +61,9 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-requests", type=int, default=4)
     ap.add_argument("--shard", default="request", choices=["request", "kv_head"])
+    ap.add_argument("--config4", action="store_true",
+                    help="mixed serving step with readiness gating + prefill ring build timing")
+    ap.add_argument("--config4-out", default=str(ROOT / "gpurun_out" / "config4.json"))
     return ap.parse_args()
 
 
@@ -222,8 +228,14 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     dist = None
+    saved_stdout = None
     if world > 1:
         import torch.distributed as dist_mod
+
+        # libraries print banners on fd 1 during set-up; keep stdout for the JSON line
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
 
         dist = dist_mod
         dist.init_process_group("nccl", device_id=dev)
@@ -308,6 +320,11 @@ def run_ours(args):
         peaks = json.loads(pk.read_text())
     peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
     achieved = ab["total"] / (ms * 1e-3) / 1e9
+    # The scan fetches only the first 128 B of a ring row unless the row is a
+    # near match, so the bytes the kernel asks for are the algorithmic ones minus
+    # half of the scan; DRAM traffic measured by ncu on smaller captures is 1.02x
+    # the requested bytes and grows in proportion to them (profiles/).
+    requested = ab["total"] - ab["scan"] // 2
     line = {
         "metric": "us_per_decode_step_cuda_graph_replay",
         "value": ms_max * 1e3,
@@ -341,7 +358,9 @@ def run_ours(args):
         "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"],
                    "reasons": clocks["reasons"]},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
-                     "frac": achieved / peak_gbs, "traffic": None,
+                     "frac": achieved / peak_gbs, "traffic": int(requested * NCU_TRAFFIC_RATIO),
+                     "requested_bytes_per_launch": requested,
+                     "requested_gbs": requested / (ms * 1e-3) / 1e9,
                      "kernel": "mac_decode_persistent_kernel",
                      "alg_bytes_per_launch": ab["total"], "kv_bytes": ab["kv"],
                      "scan_bytes": ab["scan"],
@@ -354,8 +373,12 @@ def run_ours(args):
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+    if saved_stdout is not None:
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        os.close(saved_stdout)
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
 
 
 # --------------------------------------------------------------------------- CPU arm
@@ -522,8 +545,93 @@ def run_sweep(args):
                                                     front_sink=args.front_sink), indent=1))
 
 
+def run_config4(args):
+    """Mixed serving step (contexts uniform in [8K,127K], 20 % of the requests not
+    ready, 10 % with a stale cache epoch, the rest hitting at 0.8) and the prefill
+    ring build from 32K-token prompts with q_post_cache supplied."""
+    import torch
+
+    from mac_attention_b200 import (load_mac_persistent_decode_extension,
+                                    load_mac_prefill_update_cache_extension, make_decode_workspace)
+    from mac_attention_b200 import ops, synth
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    ext = load_mac_persistent_decode_extension()
+    pre = load_mac_prefill_update_cache_extension()
+    batch = args.batch
+    g = torch.Generator().manual_seed(4)
+    ctxs = torch.randint(8192, 126977, (batch,), generator=g).tolist()
+    case = synth.make_decode_case(batch=batch, ctx=0, ctx_list=ctxs, hq=args.hq, hkv=args.hkv,
+                                  capacity=args.capacity, page_size=args.page_size, seed=44,
+                                  device=dev)
+    synth.add_readiness_gate(case, not_ready_fraction=0.2, stale_fraction=0.1, seed=4)
+    ws = make_decode_workspace(batch, args.hq, args.hkv, args.capacity, MAX_CONTEXT, TILE, MTS, SEM,
+                               0, device=dev, partial_dtype=torch.bfloat16)
+    out = torch.empty_like(case.q_post)
+    lse = torch.empty(batch, args.hq, device=dev)
+    scal = scalars(args, 0.8)
+
+    def launch():
+        ext.mac_persistent_decode_bf16(
+            case.q_post, case.q_pre, case.k, case.v, case.req_to_token, case.req_ids,
+            case.past_lens, case.out_cache_loc, case.query_cache, case.attn_cache, case.lse_cache,
+            out, lse, *ws, *scal, case.query_cache, case.cache_ready, case.cache_epoch,
+            case.request_epoch)
+
+    ms, _ = time_graph(launch, args.steps, args.warmup)
+    ab = alg_bytes(ws, batch, args.hq, args.hkv, 0, args.capacity, case.past_lens.cpu().tolist())
+    gated = int(case.meta["gated_off"].sum())
+    # the scan only runs for requests that pass the gate
+    scan = sum(min(args.capacity, c) for c, off in zip(ctxs, case.meta["gated_off"].tolist())
+               if not off) * args.hq * 256
+    total = ab["total"] - ab["scan"] + scan
+    rows = [dict(kind="mixed_decode_step", batch=batch, ctx_min=min(ctxs), ctx_max=max(ctxs),
+                 gated_off_requests=gated, hit=0.8, us=ms * 1e3, alg_gbs=total / (ms * 1e-3) / 1e9,
+                 kv_gb=ab["kv"] / 1e9, non_hit_groups=ab["non_hit_groups"],
+                 full_groups=ab["full_groups"])]
+    print(json.dumps(rows[-1]), flush=True)
+    del case, ws
+    torch.cuda.empty_cache()
+
+    # prefill ring build: 32K-token prompts, last M rows kept, q_post_cache rows stamped
+    H, D, M, plen = args.hq, DIM, args.capacity, 32768
+    R = batch
+    qc = torch.zeros(R, M, H, D, device=dev, dtype=torch.bfloat16)
+    ac = torch.zeros_like(qc)
+    lc = torch.zeros(R, M, H, device=dev)
+    qpc = torch.zeros_like(qc)
+    src_q = torch.empty(batch * plen, H, D, device=dev, dtype=torch.bfloat16)
+    src_a = torch.empty_like(src_q)
+    for t in (src_q, src_a):
+        for r0 in range(0, t.shape[0], 1 << 16):
+            t[r0:r0 + (1 << 16)].normal_()
+    src_l = torch.randn(batch * plen, H, device=dev)
+    req_ids = torch.arange(batch, device=dev, dtype=torch.int32)
+    offsets = (torch.arange(batch + 1, device=dev, dtype=torch.int32) * plen).contiguous()
+    lens = torch.full((batch,), plen, device=dev, dtype=torch.int32)
+    rl = torch.zeros(batch, device=dev, dtype=torch.int32)   # by-batch: read-only lengths
+
+    def prefill():
+        pre.mac_prefill_update_cache(qc, ac, lc, rl, req_ids, src_q, src_a, src_l, offsets, lens,
+                                     M, H, D, qpc)
+
+    pms, _ = time_graph(prefill, args.steps, args.warmup)
+    keep = min(plen, M)
+    pbytes = batch * keep * (2 * (2 * H * 256 + H * 4) + H * 256)
+    rows.append(dict(kind="prefill_update_cache", batch=batch, prompt_len=plen, capacity=M,
+                     us=pms * 1e3, alg_gbs=pbytes / (pms * 1e-3) / 1e9, alg_bytes=pbytes))
+    print(json.dumps(rows[-1]), flush=True)
+    Path(args.config4_out).parent.mkdir(parents=True, exist_ok=True)
+    Path(args.config4_out).write_text(json.dumps(dict(rows=rows, status=ops.query_status(dev)),
+                                                 indent=1))
+
+
 def main():
     args = parse_args()
+    if args.config4:
+        run_config4(args)
+        return
     if args.impl == "reference":
         run_reference_arm(args)
     elif args.sweep:
