@@ -66,7 +66,7 @@ __device__ __forceinline__ void fill_row_u16(uint8_t* dst, size_t bytes, uint16_
 }
 
 // grid = (ctas_per_request, B); CTA x of request b copies rows x, x+gridDim.x, ...
-__global__ void __launch_bounds__(kCopyThreads)
+__global__ void __launch_bounds__(kCopyThreads, 3)
 prefill_ring_copy_kernel(const PrefillParams pp) {
   const MacB200PrefillArgs& p = pp.a;
   const int b = blockIdx.y;
@@ -94,6 +94,65 @@ prefill_ring_copy_kernel(const PrefillParams pp) {
   const uint8_t* as = static_cast<const uint8_t*>(p.src_attn);
   const uint8_t* ls = reinterpret_cast<const uint8_t*>(p.src_lse);
 
+  const bool vec = ((reinterpret_cast<uintptr_t>(qc) | reinterpret_cast<uintptr_t>(ac) |
+                     reinterpret_cast<uintptr_t>(qs) | reinterpret_cast<uintptr_t>(as) |
+                     reinterpret_cast<uintptr_t>(pc) | row_bf16) & 15u) == 0;
+  if (vec) {
+    // Two ring rows per pass: all 16-byte loads of a pass (two chunks of q and
+    // of the state for both rows) are issued before the first store, so a
+    // thread keeps up to 128 bytes in flight.
+    const size_t chunks = row_bf16 / 16;
+    for (int i = 2 * blockIdx.x; i < keep; i += 2 * gridDim.x) {
+      const bool two = i + 1 < keep;
+      int d0 = base_dest + i;
+      if (d0 >= p.M) d0 -= p.M;
+      int d1 = d0 + 1;
+      if (d1 >= p.M) d1 -= p.M;
+      const size_t s0 = static_cast<size_t>(base_off + start + i), s1 = s0 + 1;
+      for (size_t c = threadIdx.x; c < chunks; c += 2 * blockDim.x) {
+        const size_t c2 = c + blockDim.x;
+        const bool more = c2 < chunks;
+        uint4 q00 = ld_stream16(qs + s0 * row_bf16 + c * 16);
+        uint4 a00 = ld_stream16(as + s0 * row_bf16 + c * 16);
+        uint4 q01 = q00, a01 = a00, q10 = q00, a10 = a00, q11 = q00, a11 = a00;
+        if (more) {
+          q01 = ld_stream16(qs + s0 * row_bf16 + c2 * 16);
+          a01 = ld_stream16(as + s0 * row_bf16 + c2 * 16);
+        }
+        if (two) {
+          q10 = ld_stream16(qs + s1 * row_bf16 + c * 16);
+          a10 = ld_stream16(as + s1 * row_bf16 + c * 16);
+          if (more) {
+            q11 = ld_stream16(qs + s1 * row_bf16 + c2 * 16);
+            a11 = ld_stream16(as + s1 * row_bf16 + c2 * 16);
+          }
+        }
+        const uint32_t nanw = 0x7fc07fc0u;
+        const uint4 nan4 = make_uint4(nanw, nanw, nanw, nanw);
+        st_stream16(qc + d0 * row_bf16 + c * 16, q00);
+        st_stream16(ac + d0 * row_bf16 + c * 16, a00);
+        if (pc) st_stream16(pc + d0 * row_bf16 + c * 16, nan4);
+        if (more) {
+          st_stream16(qc + d0 * row_bf16 + c2 * 16, q01);
+          st_stream16(ac + d0 * row_bf16 + c2 * 16, a01);
+          if (pc) st_stream16(pc + d0 * row_bf16 + c2 * 16, nan4);
+        }
+        if (two) {
+          st_stream16(qc + d1 * row_bf16 + c * 16, q10);
+          st_stream16(ac + d1 * row_bf16 + c * 16, a10);
+          if (pc) st_stream16(pc + d1 * row_bf16 + c * 16, nan4);
+          if (more) {
+            st_stream16(qc + d1 * row_bf16 + c2 * 16, q11);
+            st_stream16(ac + d1 * row_bf16 + c2 * 16, a11);
+            if (pc) st_stream16(pc + d1 * row_bf16 + c2 * 16, nan4);
+          }
+        }
+      }
+      copy_row(lc + d0 * row_f32, ls + s0 * row_f32, row_f32);
+      if (two) copy_row(lc + d1 * row_f32, ls + s1 * row_f32, row_f32);
+    }
+    return;
+  }
   for (int i = blockIdx.x; i < keep; i += gridDim.x) {
     int dest = base_dest + i;
     if (dest >= p.M) dest -= p.M;
@@ -178,8 +237,8 @@ extern "C" int mac_b200_prefill_update_cache(const MacB200PrefillArgs* a, void* 
   pp.a = *a;
   // Enough CTAs per request that one long prompt alone covers the machine,
   // few enough that 64 requests do not queue tens of thousands of idle CTAs.
-  int per_req = a->M < 64 ? a->M : 64;
-  if (a->B >= 32 && per_req > 16) per_req = 16;
+  int per_req = (a->M + 1) / 2 < 64 ? (a->M + 1) / 2 : 64;
+  if (a->B >= 32 && per_req > 32) per_req = 32;
   if (per_req < 1) per_req = 1;
   pp.ctas_per_request = per_req;
   dim3 grid(per_req, a->B);
