@@ -622,6 +622,55 @@ def run_config4(args):
     rows.append(dict(kind="prefill_update_cache", batch=batch, prompt_len=plen, capacity=M,
                      us=pms * 1e3, alg_gbs=pbytes / (pms * 1e-3) / 1e9, alg_bytes=pbytes))
     print(json.dumps(rows[-1]), flush=True)
+    del src_q, src_a, src_l, qc, ac, lc, qpc
+    torch.cuda.empty_cache()
+
+    # the producer of the prefill rows: downdate of the last M rows of every prompt
+    from mac_attention_b200 import (load_mac_decode_rope_preserve_extension,
+                                    load_mac_merge_downdate_cache_extension)
+
+    dd = load_mac_merge_downdate_cache_extension()
+    rows_dd = batch * keep
+    o_full = torch.randn(rows_dd, H, D, device=dev).to(torch.bfloat16)
+    o_win = torch.randn(rows_dd, H, D, device=dev).to(torch.bfloat16)
+    l_full = torch.randn(rows_dd, H, device=dev) + 8
+    l_win0 = l_full - torch.rand(rows_dd, H, device=dev) * 4 - 0.1
+    l_win = l_win0.clone()
+
+    def downdate():
+        dd.mac_update_then_downdate_bf16_inplace(o_full, l_full, o_win, l_win)
+
+    dms, _ = time_graph(downdate, args.steps, args.warmup)
+    dbytes = rows_dd * H * (3 * D * 2 + 3 * 4)
+    rows.append(dict(kind="update_then_downdate", rows=rows_dd * H, us=dms * 1e3,
+                     alg_gbs=dbytes / (dms * 1e-3) / 1e9, alg_bytes=dbytes))
+    print(json.dumps(rows[-1]), flush=True)
+    del o_full, o_win, l_full, l_win, l_win0
+    torch.cuda.empty_cache()
+
+    # the step before the decode path: RoPE + q preserve + KV write for the batch
+    rp = load_mac_decode_rope_preserve_extension()
+    qkv = torch.randn(batch, (args.hq + 2 * args.hkv) * D, device=dev).to(torch.bfloat16)
+    q, k, v = (qkv[:, :args.hq * D], qkv[:, args.hq * D:(args.hq + args.hkv) * D],
+               qkv[:, (args.hq + args.hkv) * D:])
+    q_pre = torch.empty(batch, args.hq, D, device=dev, dtype=torch.bfloat16)
+    pool = torch.zeros(1 << 16, args.hkv, D, device=dev, dtype=torch.bfloat16)
+    pool_v = torch.zeros_like(pool)
+    inv = 1.0 / (10000 ** (torch.arange(0, D, 2, device=dev).float() / D))
+    ang = torch.arange(131072, device=dev).float()[:, None] * inv[None, :]
+    cache = torch.cat([ang.cos(), ang.sin()], dim=1).contiguous()
+    positions = torch.randint(8192, 126977, (batch,), device=dev)
+    locs = torch.randperm(1 << 16, device=dev)[:batch]
+
+    def rope():
+        rp.mac_decode_rope_preserve_q_bf16(q, k, v, q_pre, pool, pool_v, cache, positions, locs, D,
+                                           True)
+
+    rms, _ = time_graph(rope, args.steps, args.warmup)
+    rbytes = batch * ((args.hq * 3 + args.hkv * 5) * D * 2 + D * 4)
+    rows.append(dict(kind="decode_rope_preserve", batch=batch, us=rms * 1e3,
+                     alg_gbs=rbytes / (rms * 1e-3) / 1e9, alg_bytes=rbytes))
+    print(json.dumps(rows[-1]), flush=True)
     Path(args.config4_out).parent.mkdir(parents=True, exist_ok=True)
     Path(args.config4_out).write_text(json.dumps(dict(rows=rows, status=ops.query_status(dev)),
                                                  indent=1))

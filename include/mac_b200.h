@@ -17,6 +17,8 @@
  *   mac_b200_mark_persistent_ready        mac_prefill_update_cache.cu:374-409
  *   mac_b200_invalidate_persistent_ready  mac_prefill_update_cache.cu:411-446
  *   mac_b200_update_request_state         mac_prefill_update_cache.cu:448-495
+ *   mac_b200_decode_rope_preserve_q_bf16  mac_decode_rope_preserve.cu:174-269
+ *   mac_b200_update_then_downdate_bf16_inplace  mac_merge_downdate_cache.cu:320-401
  *
  * Notation: N batch rows, Hq query heads, Hkv KV heads, G = Hq/Hkv (1..8),
  * D = 128, M ring capacity, R ring rows, P = past_lens[n] (tokens already in
@@ -228,6 +230,57 @@ int mac_b200_update_request_state(int32_t* req_len, int32_t* match_req_len,
                                   int32_t* cache_lens, const int32_t* req_ids,
                                   const int32_t* seq_lens, const int32_t* cur_lens,
                                   int32_t B, int32_t R, void* stream);
+
+/*
+ * Arguments of the decode-time fused "preserve pre-RoPE q + RoPE(q,k) + KV-pool
+ * write".  Replaces the 11 arguments of mac_decode_rope_preserve_q_bf16
+ * (mac_decode_rope_preserve.cu:174-186).  Strides are in elements; the last
+ * dimension of q, k, v is contiguous.
+ */
+typedef struct MacB200RopeArgs {
+  int64_t N;                 /* decode tokens                                             */
+  int32_t Hq, Hkv;           /* heads of q and of k/v                                     */
+  int32_t head_dim;          /* D                                                         */
+  int32_t rotary_dim;        /* = cos_sin_cache.size(1), even, <= D                       */
+  int32_t is_neox;           /* 1: pairs (d, d + rotary_dim/2); 0: pairs (2p, 2p+1)       */
+  int32_t positions_i64;     /* 0: int32, 1: int64                                        */
+  int32_t cache_locs_i64;    /* 0: int32, 1: int64                                        */
+  int32_t reserved;
+  int64_t q_stride0, k_stride0, v_stride0;  /* row strides of q, k, v                     */
+  int64_t cos_sin_stride0;   /* row stride of cos_sin_cache                               */
+  int64_t kv_pool_tokens;    /* rows of k_buffer / v_buffer                               */
+  void* q;                   /* [N, Hq*D] bf16, rotated in place                          */
+  void* k;                   /* [N, Hkv*D] bf16, rotated in place                         */
+  const void* v;             /* [N, Hkv*D] bf16                                           */
+  void* q_pre;               /* [>=N, Hq, D] bf16: q before rotation                      */
+  void* k_buffer;            /* [T, Hkv, D] bf16: row cache_locs[n] <- rotated k          */
+  void* v_buffer;            /* [T, Hkv, D] bf16: row cache_locs[n] <- v                  */
+  const float* cos_sin_cache;/* [max_pos, rotary_dim] f32: cos | sin                      */
+  const void* positions;     /* [>=N] int32|int64                                         */
+  const void* cache_locs;    /* [>=N] int32|int64                                         */
+} MacB200RopeArgs;
+
+/* Replaces mac_decode_rope_preserve_q_bf16 (mac_decode_rope_preserve.cu:174-269).
+ * Rows of cache_locs outside [0, kv_pool_tokens) are not written to the pool. */
+int mac_b200_decode_rope_preserve_q_bf16(const MacB200RopeArgs* args, void* stream);
+
+/* LSE element types of the downdate operator. */
+#define MAC_B200_LSE_F32 0
+#define MAC_B200_LSE_F16 1
+#define MAC_B200_LSE_BF16 2
+
+/*
+ * Replaces mac_update_then_downdate_bf16_inplace (mac_merge_downdate_cache.cu:320-401):
+ * for each of `rows` (token, head) rows, (out2, lse2) <- (out1, lse1) minus (out2, lse2):
+ *   lse2 <- lse1 + log(1 - exp(lse2 - lse1)),  out2 <- (out1 - exp(lse2 - lse1) * out2) * scale,
+ * with the reference's guards (window equal to the whole -> empty state; window
+ * larger than the whole -> keep (out1, lse1)).  out1/out2: [rows, D] bf16
+ * contiguous; lse1/lse2: [rows] of the given element types, natural log.
+ */
+int mac_b200_update_then_downdate_bf16_inplace(const void* out1, const void* lse1,
+                                               int32_t lse1_dtype, void* out2, void* lse2,
+                                               int32_t lse2_dtype, int64_t rows, int32_t D,
+                                               void* stream);
 
 /* Text of the last error raised on the calling thread ("" if none).
  * Stands in for the c10::Error text of the reference's TORCH_CHECKs. */

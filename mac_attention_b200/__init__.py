@@ -9,6 +9,8 @@ if the CUDA library is missing.
 """
 from .bridge import (  # noqa: F401
     install,
+    load_mac_decode_rope_preserve_extension,
+    load_mac_merge_downdate_cache_extension,
     load_mac_persistent_decode_extension,
     load_mac_prefill_update_cache_extension,
 )
@@ -16,6 +18,8 @@ from .workspace import make_decode_workspace  # noqa: F401
 
 __all__ = [
     "install",
+    "load_mac_decode_rope_preserve_extension",
+    "load_mac_merge_downdate_cache_extension",
     "load_mac_persistent_decode_extension",
     "load_mac_prefill_update_cache_extension",
     "make_decode_workspace",

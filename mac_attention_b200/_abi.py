@@ -53,6 +53,17 @@ class MacB200PrefillArgs(C.Structure):
     ]
 
 
+class MacB200RopeArgs(C.Structure):
+    _fields_ = [
+        ("N", i64), ("Hq", i32), ("Hkv", i32), ("head_dim", i32), ("rotary_dim", i32),
+        ("is_neox", i32), ("positions_i64", i32), ("cache_locs_i64", i32), ("reserved", i32),
+        ("q_stride0", i64), ("k_stride0", i64), ("v_stride0", i64), ("cos_sin_stride0", i64),
+        ("kv_pool_tokens", i64),
+        ("q", ptr), ("k", ptr), ("v", ptr), ("q_pre", ptr), ("k_buffer", ptr), ("v_buffer", ptr),
+        ("cos_sin_cache", ptr), ("positions", ptr), ("cache_locs", ptr),
+    ]
+
+
 class MacB200LaunchInfo(C.Structure):
     _fields_ = [
         ("sm_count", i32), ("ctas_per_sm", i32), ("block_threads", i32),
@@ -69,6 +80,8 @@ PROTOTYPES = {
     "mac_b200_mark_persistent_ready": (C.c_int, [ptr, ptr, ptr, ptr, i32, i32, ptr]),
     "mac_b200_invalidate_persistent_ready": (C.c_int, [ptr, ptr, ptr, ptr, i32, i32, ptr]),
     "mac_b200_update_request_state": (C.c_int, [ptr, ptr, ptr, ptr, ptr, ptr, i32, i32, ptr]),
+    "mac_b200_decode_rope_preserve_q_bf16": (C.c_int, [C.POINTER(MacB200RopeArgs), ptr]),
+    "mac_b200_update_then_downdate_bf16_inplace": (C.c_int, [ptr, ptr, i32, ptr, ptr, i32, i64, i32, ptr]),
     "mac_b200_last_error": (C.c_char_p, []),
     "mac_b200_abi_version": (C.c_int, []),
     "mac_b200_query_status": (C.c_int, [C.POINTER(C.c_uint32), ptr]),

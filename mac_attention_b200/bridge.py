@@ -48,7 +48,25 @@ def load_mac_prefill_update_cache_extension(verbose: bool = False) -> Any:
     )
 
 
-_PATCHED = ("load_mac_persistent_decode_extension", "load_mac_prefill_update_cache_extension")
+@lru_cache(maxsize=1)
+def load_mac_decode_rope_preserve_extension(verbose: bool = False) -> Any:
+    _abi.load_library()
+    from . import ops
+
+    return SimpleNamespace(mac_decode_rope_preserve_q_bf16=ops.mac_decode_rope_preserve_q_bf16)
+
+
+@lru_cache(maxsize=1)
+def load_mac_merge_downdate_cache_extension(verbose: bool = False) -> Any:
+    _abi.load_library()
+    from . import ops
+
+    return SimpleNamespace(
+        mac_update_then_downdate_bf16_inplace=ops.mac_update_then_downdate_bf16_inplace)
+
+
+_PATCHED = ("load_mac_persistent_decode_extension", "load_mac_prefill_update_cache_extension",
+            "load_mac_decode_rope_preserve_extension", "load_mac_merge_downdate_cache_extension")
 _HOOK_MODULES = (
     "mac_attention.integrations.sglang.flashinfer_hooks",
     "mac_attention.integrations.sglang.llama_hooks",
@@ -60,9 +78,9 @@ def install(bridge_module: str = "mac_attention.integrations.sglang.bridge") -> 
 
     Call before the reference's hook modules are imported (they bind the loader
     names with ``from .bridge import ...``); modules that are already imported
-    get the same names rebound.  The two loaders this package does not replace
-    (RoPE-preserve, prefill downdate) are left as they are.  Returns the names
-    of the modules that were patched.
+    get the same names rebound.  All four loaders of the reference (decode,
+    prefill update, RoPE-preserve, prefill downdate) are replaced.  Returns the
+    names of the modules that were patched.
     """
     import importlib
 

@@ -1,0 +1,196 @@
+// Prefill-side LSE downdate, in place (sm_100a).
+//
+// For every (token, head) row: the state of the whole prefix (out1, lse1) minus
+// the state of the trailing window (out2, lse2) gives the state of the prefix
+// without that window, written over (out2, lse2).  Formula and guards follow the
+// reference kernel
+// attention/src/mac_attention/integrations/sglang/csrc/mac_merge_downdate_cache.cu:116-288.
+// The reference spends one 256-thread CTA with a double-buffered shared-memory
+// stage on each 256-byte row; here a row is a handful of 16-byte chunks owned by
+// neighbouring lanes (16 lanes for D = 128); the scalars of the 8..32 rows a warp
+// handles per pass are worked out one row per lane and handed to the chunk lanes
+// by shuffle, and each thread keeps four rows in flight.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "mac_b200_common.h"
+
+namespace mac_b200 {
+namespace {
+
+constexpr int kDownThreads = 256;
+constexpr int kDownUnroll = 4;
+
+struct DowndateParams {
+  const char* out1;
+  char* out2;
+  const void* lse1;
+  void* lse2;
+  int64_t rows;
+  int32_t D, chunks, lanes_per_row, dt1, dt2;
+};
+
+__device__ __forceinline__ float load_lse(const void* p, int dt, int64_t i) {
+  if (dt == MAC_B200_LSE_F32) return static_cast<const float*>(p)[i];
+  if (dt == MAC_B200_LSE_F16) return __half2float(static_cast<const __half*>(p)[i]);
+  return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+}
+__device__ __forceinline__ void store_lse(void* p, int dt, int64_t i, float v) {
+  if (dt == MAC_B200_LSE_F32) static_cast<float*>(p)[i] = v;
+  else if (dt == MAC_B200_LSE_F16) static_cast<__half*>(p)[i] = __float2half_rn(v);
+  else static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+}
+__device__ __forceinline__ float lo_f(uint32_t p) { return __uint_as_float(p << 16); }
+__device__ __forceinline__ float hi_f(uint32_t p) { return __uint_as_float(p & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// The three scalars of a row (mac_merge_downdate_cache.cu:152-176).
+__device__ __forceinline__ void downdate_scalars(float l1, float l2, float& ret_lse, float& t,
+                                                 float& scale) {
+  const float diff = l2 - l1;
+  const float em1 = expm1f(diff);
+  const bool last_block = fabsf(em1) <= 1e-7f;
+  const bool invalid = (diff > 0.0f) && !last_block;
+  if (last_block) {
+    ret_lse = -INFINITY; t = 0.f; scale = 0.f;
+  } else if (invalid) {
+    ret_lse = l1; t = 0.f; scale = 1.f;
+  } else {
+    const float one_minus = 1.f - expf(diff);
+    ret_lse = l1 + logf(fmaxf(one_minus + 1e-7f, 1e-30f));
+    t = expf(diff);
+    scale = expf(l1 - ret_lse);
+  }
+}
+
+__global__ void __launch_bounds__(kDownThreads)
+downdate_inplace_kernel(const DowndateParams p) {
+  const int lpr = p.lanes_per_row;                   // power of two <= 32
+  const int lane = threadIdx.x & 31;
+  const int sub = lane & (lpr - 1);                  // chunk lane inside the row group
+  const int rows_per_warp = 32 / lpr;
+  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t warps_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int64_t row_bytes = static_cast<int64_t>(p.D) * 2;
+
+  const int rows_per_iter = rows_per_warp * kDownUnroll;   // <= 32: one lane per row for the scalars
+  for (int64_t base = warp_global * rows_per_iter; base < p.rows; base += warps_total * rows_per_iter) {
+    // lane r works out the three scalars of row base + r (all lanes busy), the
+    // chunk lanes fetch them by shuffle; the row's LSE is replaced right away
+    // (only this lane reads it).
+    float my_t = 0.f, my_scale = 0.f;
+    {
+      const int64_t row = base + lane;
+      if (lane < rows_per_iter && row < p.rows) {
+        float ret;
+        downdate_scalars(load_lse(p.lse1, p.dt1, row), load_lse(p.lse2, p.dt2, row), ret, my_t,
+                         my_scale);
+        store_lse(p.lse2, p.dt2, row, ret);
+      }
+    }
+    for (int c0 = 0; c0 < p.chunks; c0 += lpr) {
+      const int c = c0 + sub;
+      uint4 a[kDownUnroll], b[kDownUnroll];
+      bool live[kDownUnroll];
+#pragma unroll
+      for (int u = 0; u < kDownUnroll; ++u) {
+        const int64_t row = base + u * rows_per_warp + lane / lpr;
+        live[u] = row < p.rows && c < p.chunks;
+        if (live[u]) {
+          a[u] = *reinterpret_cast<const uint4*>(p.out1 + row * row_bytes + c * 16);
+          b[u] = *reinterpret_cast<const uint4*>(p.out2 + row * row_bytes + c * 16);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kDownUnroll; ++u) {
+        const int src = u * rows_per_warp + lane / lpr;    // the lane that owns this row's scalars
+        const float t = __shfl_sync(0xffffffffu, my_t, src);
+        const float scale = __shfl_sync(0xffffffffu, my_scale, src);
+        if (!live[u]) continue;
+        const int64_t row = base + u * rows_per_warp + lane / lpr;
+        const uint32_t x[4] = {a[u].x, a[u].y, a[u].z, a[u].w};
+        const uint32_t y[4] = {b[u].x, b[u].y, b[u].z, b[u].w};
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float r0 = (lo_f(x[i]) - t * lo_f(y[i])) * scale;
+          const float r1 = (hi_f(x[i]) - t * hi_f(y[i])) * scale;
+          o[i] = pack2(r0, r1);
+        }
+        *reinterpret_cast<uint4*>(p.out2 + row * row_bytes + c * 16) =
+            make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  }
+}
+
+// D not a multiple of 8 or unaligned bases: one thread per element pair stride.
+__global__ void __launch_bounds__(kDownThreads)
+downdate_inplace_scalar_kernel(const DowndateParams p) {
+  const __nv_bfloat16* o1 = reinterpret_cast<const __nv_bfloat16*>(p.out1);
+  __nv_bfloat16* o2 = reinterpret_cast<__nv_bfloat16*>(p.out2);
+  const int lane = threadIdx.x & 31;
+  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t warps_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  for (int64_t row = warp_global; row < p.rows; row += warps_total) {
+    float ret, t, scale;
+    downdate_scalars(load_lse(p.lse1, p.dt1, row), load_lse(p.lse2, p.dt2, row), ret, t, scale);
+    __syncwarp();
+    for (int d = lane; d < p.D; d += 32) {
+      const float r = (__bfloat162float(o1[row * p.D + d]) - t * __bfloat162float(o2[row * p.D + d])) * scale;
+      o2[row * p.D + d] = __float2bfloat16_rn(r);
+    }
+    __syncwarp();
+    if (lane == 0) store_lse(p.lse2, p.dt2, row, ret);
+  }
+}
+
+}  // namespace
+}  // namespace mac_b200
+
+using namespace mac_b200;
+
+extern "C" int mac_b200_update_then_downdate_bf16_inplace(const void* out1, const void* lse1,
+                                                          int32_t lse1_dtype, void* out2,
+                                                          void* lse2, int32_t lse2_dtype,
+                                                          int64_t rows, int32_t D,
+                                                          void* stream_v) {
+  MAC_REQUIRE(rows >= 0 && D > 0, "invalid downdate shape");
+  if (rows == 0) return MAC_B200_OK;
+  MAC_REQUIRE(out1 && lse1 && out2 && lse2, "downdate tensors must not be null");
+  MAC_REQUIRE(lse1_dtype >= 0 && lse1_dtype <= 2 && lse2_dtype >= 0 && lse2_dtype <= 2,
+              "lse must be float32, bfloat16, or float16");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  DowndateParams p;
+  p.out1 = static_cast<const char*>(out1);
+  p.out2 = static_cast<char*>(out2);
+  p.lse1 = lse1;
+  p.lse2 = lse2;
+  p.rows = rows;
+  p.D = D;
+  p.dt1 = lse1_dtype;
+  p.dt2 = lse2_dtype;
+  const bool vec = D % 8 == 0 && ((reinterpret_cast<uintptr_t>(out1) | reinterpret_cast<uintptr_t>(out2)) & 15u) == 0;
+  if (vec) {
+    p.chunks = D / 8;
+    int lpr = 1;
+    while (lpr < p.chunks && lpr < 32) lpr <<= 1;
+    p.lanes_per_row = lpr;
+    const int64_t rows_per_cta = static_cast<int64_t>(kDownThreads / 32) * (32 / lpr) * kDownUnroll;
+    int64_t blocks = (rows + rows_per_cta - 1) / rows_per_cta;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    downdate_inplace_kernel<<<static_cast<unsigned>(blocks), kDownThreads, 0, stream>>>(p);
+  } else {
+    p.chunks = 0;
+    p.lanes_per_row = 32;
+    int64_t blocks = (rows + 7) / 8;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    downdate_inplace_scalar_kernel<<<static_cast<unsigned>(blocks), kDownThreads, 0, stream>>>(p);
+  }
+  MAC_CUDA(cudaGetLastError());
+  g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+  return MAC_B200_OK;
+}

@@ -82,8 +82,8 @@ def _decode_call(
     bench_seed, bench_miss_mask, bench_layer_id,
     query_post_cache, mac_cache_ready, mac_cache_epoch, mac_request_epoch,
 ) -> None:
-    """Checks and argument marshalling shared by the decode entry points."""
-    lib = _abi.load_library()
+    """Checks and argument marshalling shared by the decode entry points; returns the
+    filled ``MacB200DecodeArgs``."""
     _check(q_post, "q_post", _BF16, 3)
     _check(q_pre, "q_pre", _BF16, 3)
     _check(k_buffer, "k_buffer", _BF16, 3)
@@ -270,11 +270,45 @@ def _decode_call(
     a.task_counts, a.phase_cycles = task_counts.data_ptr(), phase_cycles.data_ptr()
     a.cache_ready, a.cache_epoch, a.request_epoch = ready_ptr, epoch_ptr, req_epoch_ptr
 
-    with torch.cuda.device(q_post.device):
-        _abi.check(getattr(lib, entry_name)(C.byref(a), _stream_ptr(q_post.device)))
+    return a
 
 
 _DECODE_ARG_COUNT = 68
+_TENSOR_ARGS = tuple(range(0, 43)) + (64, 65, 66, 67)
+_ARG_CACHE: dict = {}
+_ARG_CACHE_MAX = 64
+_ARG_CACHE_ON = os.environ.get("MAC_B200_NO_ARG_CACHE", "0") != "1"
+
+
+def _decode_key(args):
+    """Identity of a call for the marshalling cache: every tensor's address, the
+    shapes the struct is derived from, and all scalars.  A repeat of the same
+    call (serving loops and graph warm-ups pass the same buffers every step)
+    reuses the checked argument struct instead of re-validating ~50 tensors."""
+    ptrs = tuple(args[i].data_ptr() for i in _TENSOR_ARGS)
+    return (ptrs, args[43:64], tuple(args[0].shape), tuple(args[2].shape[:2]),
+            tuple(args[4].shape), tuple(args[8].shape[:2]), tuple(args[13].shape),
+            args[42].numel(), args[12].numel(), args[7].dtype, args[0].device)
+
+
+def _decode_entry(entry_name, args) -> None:
+    lib = _abi.load_library()
+    key = _decode_key(args) if _ARG_CACHE_ON else None
+    a = _ARG_CACHE.get(key) if key is not None else None
+    if a is None:
+        a = _decode_call(entry_name, *args)
+        if key is not None:
+            if len(_ARG_CACHE) >= _ARG_CACHE_MAX:
+                _ARG_CACHE.clear()
+            _ARG_CACHE[key] = a
+    else:
+        # the reference re-reads these environment knobs on every launch
+        a.mixed_group_fallback = _env_flag("MAC_PERSISTENT_MIXED_GROUP_FALLBACK", 1)
+        a.bench_exact_quota = _env_flag("MAC_BENCH_EXACT_QUOTA", 1)
+        a.grid_cap = _env_int("MAC_PERSISTENT_COOP_CTAS", 0)
+    device = args[0].device
+    with torch.cuda.device(device):
+        _abi.check(getattr(lib, entry_name)(C.byref(a), _stream_ptr(device)))
 
 
 def mac_persistent_decode_bf16(*args) -> None:
@@ -285,7 +319,7 @@ def mac_persistent_decode_bf16(*args) -> None:
     if len(args) != _DECODE_ARG_COUNT:
         raise TypeError(f"mac_persistent_decode_bf16() takes {_DECODE_ARG_COUNT} positional "
                         f"arguments ({len(args)} given)")
-    _decode_call("mac_b200_persistent_decode_bf16", *args)
+    _decode_entry("mac_b200_persistent_decode_bf16", args)
 
 
 def mac_persistent_decode_bf16_noalloc(*args) -> None:
@@ -298,7 +332,7 @@ def mac_persistent_decode_bf16_noalloc(*args) -> None:
     if len(args) != _DECODE_ARG_COUNT:
         raise TypeError(f"mac_persistent_decode_bf16_noalloc() takes {_DECODE_ARG_COUNT} "
                         f"positional arguments ({len(args)} given)")
-    _decode_call("mac_b200_persistent_decode_bf16_noalloc", *args)
+    _decode_entry("mac_b200_persistent_decode_bf16_noalloc", args)
 
 
 def mac_prefill_update_cache(
@@ -409,6 +443,92 @@ def mac_update_request_state(req_len, match_req_len, cache_lens, req_ids, seq_le
             req_len.data_ptr(), match_req_len.data_ptr(), cache_lens.data_ptr(),
             req_ids.data_ptr(), seq_lens.data_ptr(), cur_lens.data_ptr(), B, req_len.shape[0],
             _stream_ptr(req_len.device)))
+
+
+def mac_decode_rope_preserve_q_bf16(q, k, v, q_pre, k_buffer, v_buffer, cos_sin_cache, positions,
+                                    cache_locs, head_dim, is_neox) -> None:
+    """Decode-time fused step before attention: ``q_pre <- q``, RoPE on ``q`` and ``k`` in
+    place, rotated ``k`` and ``v`` written to the KV pool at ``cache_locs``.  Arguments and
+    checks of the reference operator (``csrc/mac_decode_rope_preserve.cu:174-269``)."""
+    lib = _abi.load_library()
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _req(t.is_cuda, f"{name} must be CUDA")
+        _req(t.dtype == _BF16, f"{name} has wrong dtype")
+        _req(t.dim() == 2, f"{name} must have rank 2")
+        _req(t.stride(1) == 1, f"{name} must have contiguous last dimension")
+    for name, t in (("q_pre", q_pre), ("k_buffer", k_buffer), ("v_buffer", v_buffer)):
+        _req(t.is_cuda, f"{name} must be CUDA")
+        _req(t.dtype == _BF16, f"{name} has wrong dtype")
+        _req(t.dim() == 3, f"{name} must have rank 3")
+        _req(t.is_contiguous(), f"{name} must be contiguous")
+    _req(cos_sin_cache.is_cuda, "cos_sin_cache must be CUDA")
+    _req(cos_sin_cache.dtype == _F32, "cos_sin_cache has wrong dtype")
+    _req(cos_sin_cache.dim() == 2, "cos_sin_cache must have rank 2")
+    _req(cos_sin_cache.stride(1) == 1, "cos_sin_cache must have contiguous last dimension")
+    _req(positions.is_cuda and cache_locs.is_cuda, "positions/cache_locs must be CUDA")
+    _req(positions.dim() == 1, "positions must have rank 1")
+    _req(cache_locs.dim() == 1, "cache_locs must have rank 1")
+    _req(positions.dtype in (_I32, _I64), "positions must be int32 or int64")
+    _req(cache_locs.dtype in (_I32, _I64), "cache_locs must be int32 or int64")
+    _req(positions.is_contiguous() and cache_locs.is_contiguous(),
+         "positions/cache_locs must be contiguous")
+    head_dim = int(head_dim)
+    N = q.shape[0]
+    _req(k.shape[0] == N and v.shape[0] == N, "q/k/v batch mismatch")
+    _req(positions.shape[0] >= N and cache_locs.shape[0] >= N, "metadata batch too small")
+    _req(head_dim > 0 and q.shape[1] % head_dim == 0 and k.shape[1] % head_dim == 0,
+         "invalid head_dim")
+    Hq, Hkv = q.shape[1] // head_dim, k.shape[1] // head_dim
+    _req(v.shape[1] == Hkv * head_dim, "v shape mismatch")
+    _req(q_pre.shape[0] >= N and q_pre.shape[1] == Hq and q_pre.shape[2] == head_dim,
+         "q_pre shape mismatch")
+    _req(k_buffer.shape[1] == Hkv and k_buffer.shape[2] == head_dim, "k_buffer shape mismatch")
+    _req(v_buffer.shape == k_buffer.shape, "v_buffer shape mismatch")
+    rotary_dim = cos_sin_cache.shape[1]
+    _req(0 < rotary_dim <= head_dim and rotary_dim % 2 == 0, "invalid rotary_dim")
+    a = _abi.MacB200RopeArgs()
+    a.N, a.Hq, a.Hkv, a.head_dim, a.rotary_dim = N, Hq, Hkv, head_dim, rotary_dim
+    a.is_neox = 1 if is_neox else 0
+    a.positions_i64 = 1 if positions.dtype == _I64 else 0
+    a.cache_locs_i64 = 1 if cache_locs.dtype == _I64 else 0
+    a.q_stride0, a.k_stride0, a.v_stride0 = q.stride(0), k.stride(0), v.stride(0)
+    a.cos_sin_stride0 = cos_sin_cache.stride(0)
+    a.kv_pool_tokens = k_buffer.shape[0]
+    a.q, a.k, a.v, a.q_pre = q.data_ptr(), k.data_ptr(), v.data_ptr(), q_pre.data_ptr()
+    a.k_buffer, a.v_buffer = k_buffer.data_ptr(), v_buffer.data_ptr()
+    a.cos_sin_cache = cos_sin_cache.data_ptr()
+    a.positions, a.cache_locs = positions.data_ptr(), cache_locs.data_ptr()
+    with torch.cuda.device(q.device):
+        _abi.check(lib.mac_b200_decode_rope_preserve_q_bf16(C.byref(a), _stream_ptr(q.device)))
+
+
+_LSE_DTYPES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+
+def mac_update_then_downdate_bf16_inplace(out1, lse1, out2, lse2) -> None:
+    """``(out2, lse2) <- (out1, lse1) minus (out2, lse2)`` per (token, head) row, in place
+    (reference operator ``csrc/mac_merge_downdate_cache.cu:320-401``)."""
+    lib = _abi.load_library()
+    _req(out1.is_cuda and out2.is_cuda, "out tensors must be CUDA")
+    _req(lse1.is_cuda and lse2.is_cuda, "lse tensors must be CUDA")
+    _req(out1.dtype == _BF16 and out2.dtype == _BF16, "out tensors must be bfloat16")
+    _req(out1.dim() == 3, "out1 must be [N,H,D]")
+    _req(out2.shape == out1.shape, "out shapes must match [N,H,D]")
+    _req(lse1.dim() == 2, "lse1 must be [N,H]")
+    _req(lse2.shape == lse1.shape, "lse shapes must match [N,H]")
+    _req(tuple(lse1.shape) == tuple(out1.shape[:2]), "lse shapes must match [N,H]")
+    _req(out1.is_contiguous() and out2.is_contiguous(), "out tensors must be contiguous")
+    _req(lse1.is_contiguous() and lse2.is_contiguous(), "lse tensors must be contiguous")
+    _req(out1.device == out2.device == lse1.device == lse2.device,
+         "tensors must be on the same device")
+    for name, t in (("lse1", lse1), ("lse2", lse2)):
+        _req(t.dtype in _LSE_DTYPES, f"{name} must be float32, bfloat16, or float16; got {t.dtype}")
+    rows = out1.shape[0] * out1.shape[1]
+    with torch.cuda.device(out1.device):
+        _abi.check(lib.mac_b200_update_then_downdate_bf16_inplace(
+            out1.data_ptr(), lse1.data_ptr(), _LSE_DTYPES[lse1.dtype], out2.data_ptr(),
+            lse2.data_ptr(), _LSE_DTYPES[lse2.dtype], rows, out1.shape[2],
+            _stream_ptr(out1.device)))
 
 
 def query_status(device=None) -> int:

@@ -33,6 +33,8 @@ CSRC = REF_ROOT / "attention/src/mac_attention/integrations/sglang/csrc"
 
 DECODE_NAME = "mac_ref_persistent_decode_sm100a"
 PREFILL_NAME = "mac_ref_prefill_update_cache_sm100a"
+ROPE_NAME = "mac_ref_decode_rope_preserve_sm100a"
+DOWNDATE_NAME = "mac_ref_merge_downdate_cache_sm100a"
 
 _ARCH = ["-gencode=arch=compute_100a,code=sm_100a"]
 
@@ -70,6 +72,17 @@ def build_prefill(verbose: bool = False):
     return _load(PREFILL_NAME, CSRC / "mac_prefill_update_cache.cu", flags, verbose)
 
 
+def build_rope(verbose: bool = False):
+    flags = ["-O3", "-std=c++17", "-U__CUDA_NO_BFLOAT16_CONVERSIONS__", *_ARCH]
+    return _load(ROPE_NAME, CSRC / "mac_decode_rope_preserve.cu", flags, verbose)
+
+
+def build_downdate(verbose: bool = False):
+    flags = ["-O3", "--use_fast_math", "-Xptxas", "-O3", "-Xptxas", "-dlcm=ca", *_ARCH,
+             "-DTILE_D=1024", "-DTHREADS=256"]
+    return _load(DOWNDATE_NAME, CSRC / "mac_merge_downdate_cache.cu", flags, verbose)
+
+
 def _import_prebuilt(name: str):
     """Import ``oracle/_ref/<name>/<name>.so`` without rebuilding."""
     import importlib.util
@@ -94,13 +107,25 @@ def load_prefill():
     return _import_prebuilt(PREFILL_NAME)
 
 
+def load_rope():
+    return _import_prebuilt(ROPE_NAME)
+
+
+def load_downdate():
+    return _import_prebuilt(DOWNDATE_NAME)
+
+
 def main() -> int:
     if not CSRC.exists():
         print(f"reference sources not found under {CSRC}; nothing built")
         return 0
-    which = sys.argv[1:] or ["prefill", "decode"]
+    which = sys.argv[1:] or ["prefill", "rope", "downdate", "decode"]
     if "prefill" in which:
         build_prefill(verbose=True)
+    if "rope" in which:
+        build_rope(verbose=True)
+    if "downdate" in which:
+        build_downdate(verbose=True)
     if "decode" in which:
         build_decode(verbose=True)
     return 0

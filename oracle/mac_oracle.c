@@ -765,3 +765,82 @@ ORACLE_API float mac_oracle_threshold_distance(float threshold, int D) {
   return threshold_distance(&a);
 }
 ORACLE_API int mac_oracle_abi_struct_size(void) { return (int)sizeof(MacB200DecodeArgs); }
+
+/* ----------------------------------------------- decode RoPE + q preserve -- */
+/* attention/src/mac_attention/integrations/sglang/csrc/mac_decode_rope_preserve.cu:35-156.
+ * The rotation is evaluated the way the device compiler evaluates
+ * x0*c - x1*s and x1*c + x0*s: second product rounded, first fused. */
+static inline int64_t load_index(const void* p, int is_i64, int64_t n) {
+  return is_i64 ? ((const int64_t*)p)[n] : (int64_t)((const int32_t*)p)[n];
+}
+ORACLE_API int mac_oracle_decode_rope_preserve(const MacB200RopeArgs* a) {
+  const int64_t D = a->head_dim, R = a->rotary_dim, half = R / 2;
+  uint16_t* q = (uint16_t*)a->q;
+  uint16_t* k = (uint16_t*)a->k;
+  const uint16_t* v = (const uint16_t*)a->v;
+  uint16_t* q_pre = (uint16_t*)a->q_pre;
+  uint16_t* kb = (uint16_t*)a->k_buffer;
+  uint16_t* vb = (uint16_t*)a->v_buffer;
+  for (int64_t n = 0; n < a->N; ++n) {
+    const int64_t pos = load_index(a->positions, a->positions_i64, n);
+    const int64_t loc = load_index(a->cache_locs, a->cache_locs_i64, n);
+    const int pool_ok = loc >= 0 && loc < a->kv_pool_tokens;
+    const float* cs = a->cos_sin_cache + pos * a->cos_sin_stride0;
+    for (int which = 0; which < 2; ++which) {
+      const int64_t H = which ? a->Hkv : a->Hq;
+      for (int64_t h = 0; h < H; ++h) {
+        uint16_t* row = which ? k + n * a->k_stride0 + h * D : q + n * a->q_stride0 + h * D;
+        if (!which)
+          for (int64_t d = 0; d < D; ++d) q_pre[(n * a->Hq + h) * D + d] = row[d];
+        for (int64_t pair = 0; pair < half; ++pair) {
+          const int64_t d0 = a->is_neox ? pair : 2 * pair, d1 = a->is_neox ? pair + half : d0 + 1;
+          const float x0 = bf16_to_f32(row[d0]), x1 = bf16_to_f32(row[d1]);
+          const float c = cs[pair], s = cs[half + pair];
+          const float y0 = fmaf(x0, c, -(x1 * s));
+          const float y1 = fmaf(x1, c, x0 * s);
+          row[d0] = f32_to_bf16(y0);
+          row[d1] = f32_to_bf16(y1);
+        }
+        if (which && pool_ok)
+          for (int64_t d = 0; d < D; ++d) kb[(loc * a->Hkv + h) * D + d] = row[d];
+      }
+    }
+    if (pool_ok)
+      for (int64_t h = 0; h < a->Hkv; ++h)
+        for (int64_t d = 0; d < D; ++d)
+          vb[(loc * a->Hkv + h) * D + d] = v[n * a->v_stride0 + h * D + d];
+  }
+  return 0;
+}
+
+/* ------------------------------------------------------ prefill downdate -- */
+/* attention/src/mac_attention/integrations/sglang/csrc/mac_merge_downdate_cache.cu:116-288,
+ * float32 LSE only (the element types only change how the scalar is loaded). */
+ORACLE_API int mac_oracle_update_then_downdate(const uint16_t* out1, const float* lse1,
+                                               uint16_t* out2, float* lse2, int64_t rows,
+                                               int32_t D) {
+  for (int64_t r = 0; r < rows; ++r) {
+    const float l1 = lse1[r], l2 = lse2[r];
+    const float diff = l2 - l1;
+    const float em1 = expm1f(diff);
+    const int last_block = fabsf(em1) <= 1e-7f;
+    const int invalid = (diff > 0.0f) && !last_block;
+    float ret, t, scale;
+    if (last_block) {
+      ret = -INFINITY; t = 0.f; scale = 0.f;
+    } else if (invalid) {
+      ret = l1; t = 0.f; scale = 1.f;
+    } else {
+      const float one_minus = 1.f - expf(diff);
+      ret = l1 + logf(fmaxf(one_minus + 1e-7f, 1e-30f));
+      t = expf(diff);
+      scale = expf(l1 - ret);
+    }
+    for (int d = 0; d < D; ++d) {
+      const float o = (bf16_to_f32(out1[r * D + d]) - t * bf16_to_f32(out2[r * D + d])) * scale;
+      out2[r * D + d] = f32_to_bf16(o);
+    }
+    lse2[r] = ret;
+  }
+  return 0;
+}

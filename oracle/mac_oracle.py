@@ -219,6 +219,36 @@ def update_request_state(req_len, match_req_len, cache_lens, req_ids, seq_lens, 
                                           req_ids.shape[0], req_len.shape[0])
 
 
+def decode_rope_preserve(q, k, v, q_pre, k_buffer, v_buffer, cos_sin_cache, positions, cache_locs,
+                         head_dim, is_neox) -> None:
+    """CPU restatement of the decode RoPE + q-preserve + KV write (all tensors updated in place)."""
+    a = _abi.MacB200RopeArgs()
+    a.N = q.shape[0]
+    a.Hq, a.Hkv = q.shape[1] // head_dim, k.shape[1] // head_dim
+    a.head_dim, a.rotary_dim = head_dim, cos_sin_cache.shape[1]
+    a.is_neox = 1 if is_neox else 0
+    a.positions_i64 = 1 if positions.dtype == torch.int64 else 0
+    a.cache_locs_i64 = 1 if cache_locs.dtype == torch.int64 else 0
+    a.q_stride0, a.k_stride0, a.v_stride0 = q.stride(0), k.stride(0), v.stride(0)
+    a.cos_sin_stride0 = cos_sin_cache.stride(0)
+    a.kv_pool_tokens = k_buffer.shape[0]
+    a.q, a.k, a.v, a.q_pre = _p(q), _p(k), _p(v), _p(q_pre)
+    a.k_buffer, a.v_buffer, a.cos_sin_cache = _p(k_buffer), _p(v_buffer), _p(cos_sin_cache)
+    a.positions, a.cache_locs = _p(positions), _p(cache_locs)
+    fn = lib().mac_oracle_decode_rope_preserve
+    fn.restype, fn.argtypes = C.c_int, [C.POINTER(_abi.MacB200RopeArgs)]
+    fn(C.byref(a))
+
+
+def update_then_downdate(out1, lse1, out2, lse2) -> None:
+    """CPU restatement of the prefill downdate; float32 LSEs, ``out2``/``lse2`` in place."""
+    assert lse1.dtype == torch.float32 and lse2.dtype == torch.float32
+    fn = lib().mac_oracle_update_then_downdate
+    fn.restype = C.c_int
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32]
+    fn(_p(out1), _p(lse1), _p(out2), _p(lse2), out1.shape[0] * out1.shape[1], out1.shape[2])
+
+
 def ring_slot_to_pos(past_len, M, slot):
     return lib().mac_oracle_ring_slot_to_pos(past_len, M, slot)
 

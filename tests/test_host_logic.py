@@ -17,6 +17,9 @@ def test_loaders_expose_reference_operator_names():
     for name in ("mac_prefill_update_cache", "mac_mark_persistent_ready",
                  "mac_invalidate_persistent_ready", "mac_update_request_state"):
         assert callable(getattr(pre, name))
+    assert callable(pkg.load_mac_decode_rope_preserve_extension().mac_decode_rope_preserve_q_bf16)
+    assert callable(
+        pkg.load_mac_merge_downdate_cache_extension().mac_update_then_downdate_bf16_inplace)
     assert pkg.load_mac_persistent_decode_extension(False, fast_math=True) is dec
 
 
@@ -34,7 +37,8 @@ def test_install_rebinds_bridge_and_imported_hooks(monkeypatch):
     assert "fake_mac.bridge" in patched and hooks.__name__ in patched
     assert fake_bridge.load_mac_persistent_decode_extension is bridge.load_mac_persistent_decode_extension
     assert hooks.load_mac_persistent_decode_extension is bridge.load_mac_persistent_decode_extension
-    assert fake_bridge.load_mac_decode_rope_preserve_extension() == "rope"
+    assert fake_bridge.load_mac_decode_rope_preserve_extension is bridge.load_mac_decode_rope_preserve_extension
+    assert fake_bridge.load_mac_merge_downdate_cache_extension is bridge.load_mac_merge_downdate_cache_extension
 
 
 def test_decode_operator_rejects_cpu_tensors_like_the_reference():

@@ -179,3 +179,43 @@ def test_oracle_prefill_and_gate():
     assert ready.tolist() == [False, True, False, True, False] and ce.tolist() == [-1, 1, -1, 3, -1]
     O.invalidate_persistent_ready(ready, ce, re_, torch.tensor([3], dtype=torch.int32))
     assert ready.tolist() == [False, True, False, False, False] and re_[3] == 4 and ce[3] == -1
+
+
+def test_oracle_rope_and_downdate_against_float64():
+    """CPU: the oracle's RoPE and downdate restatements against plain float64 math."""
+    import math
+
+    g = torch.Generator().manual_seed(1)
+    N, Hq, Hkv, D = 6, 8, 2, 128
+    q = torch.randn(N, Hq * D, generator=g).to(torch.bfloat16)
+    k = torch.randn(N, Hkv * D, generator=g).to(torch.bfloat16)
+    v = torch.randn(N, Hkv * D, generator=g).to(torch.bfloat16)
+    inv = 1.0 / (10000 ** (torch.arange(0, D, 2).float() / D))
+    ang = torch.arange(512).float()[:, None] * inv[None, :]
+    cache = torch.cat([ang.cos(), ang.sin()], dim=1).contiguous()
+    pos = torch.randint(0, 512, (N,), generator=g)
+    loc = torch.randperm(32, generator=g)[:N]
+    q_pre = torch.zeros(N, Hq, D, dtype=torch.bfloat16)
+    kb = torch.zeros(32, Hkv, D, dtype=torch.bfloat16)
+    vb = torch.zeros_like(kb)
+    q0, k0 = q.clone().double().view(N, Hq, D), k.clone().double().view(N, Hkv, D)
+    O.decode_rope_preserve(q, k, v, q_pre, kb, vb, cache, pos, loc, D, True)
+    cs = cache.double()[pos]
+    c, s = cs[:, None, :64], cs[:, None, 64:]
+    for x0, x1 in ((q0, q.double().view(N, Hq, D)), (k0, k.double().view(N, Hkv, D))):
+        exp = torch.cat([x0[..., :64] * c - x0[..., 64:] * s, x0[..., 64:] * c + x0[..., :64] * s], -1)
+        assert O.rel_l2(x1, exp) < 4e-3
+    assert torch.equal(q_pre.view(N, -1).double(), q0.view(N, -1))
+    assert torch.equal(kb[loc], k.view(N, Hkv, D)) and torch.equal(vb[loc], v.view(N, Hkv, D))
+    # downdate: exp(l_out) = exp(l1) - exp(l2)
+    out1 = torch.randn(4, 2, 16, generator=g).to(torch.bfloat16)
+    out2 = torch.randn(4, 2, 16, generator=g).to(torch.bfloat16)
+    l1 = torch.randn(4, 2, generator=g) + 3
+    l2 = l1 - torch.rand(4, 2, generator=g) * 3 - 0.1
+    e_l = torch.log(torch.exp(l1.double()) - torch.exp(l2.double()))
+    t = torch.exp(l2.double() - l1.double())
+    e_o = (out1.double() - t[..., None] * out2.double()) * torch.exp(l1.double() - e_l)[..., None]
+    o2, ll2 = out2.clone(), l2.clone()
+    O.update_then_downdate(out1, l1, o2, ll2)
+    assert (ll2.double() - e_l).abs().max() < 1e-5
+    assert O.rel_l2(o2.double(), e_o) < 4e-3
