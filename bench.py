@@ -617,10 +617,22 @@ def run_config4(args):
                                      M, H, D, qpc)
 
     pms, _ = time_graph(prefill, args.steps, args.warmup)
+    ref_us = {}
+    want_ref = "refkernel" in args.baselines
+    if want_ref:
+        from oracle import build_ref
+
+        rpre = build_ref.load_prefill()
+        if rpre is not None:
+            rms_, _ = time_graph(lambda: rpre.mac_prefill_update_cache(
+                qc, ac, lc, rl, req_ids, src_q, src_a, src_l, offsets, lens, M, H, D, qpc),
+                args.steps, args.warmup)
+            ref_us["prefill"] = rms_ * 1e3
     keep = min(plen, M)
     pbytes = batch * keep * (2 * (2 * H * 256 + H * 4) + H * 256)
     rows.append(dict(kind="prefill_update_cache", batch=batch, prompt_len=plen, capacity=M,
-                     us=pms * 1e3, alg_gbs=pbytes / (pms * 1e-3) / 1e9, alg_bytes=pbytes))
+                     us=pms * 1e3, alg_gbs=pbytes / (pms * 1e-3) / 1e9, alg_bytes=pbytes,
+                     refkernel_us=ref_us.get("prefill")))
     print(json.dumps(rows[-1]), flush=True)
     del src_q, src_a, src_l, qc, ac, lc, qpc
     torch.cuda.empty_cache()
@@ -641,9 +653,16 @@ def run_config4(args):
         dd.mac_update_then_downdate_bf16_inplace(o_full, l_full, o_win, l_win)
 
     dms, _ = time_graph(downdate, args.steps, args.warmup)
+    if want_ref:
+        rdd = build_ref.load_downdate()
+        if rdd is not None:
+            rms_, _ = time_graph(lambda: rdd.mac_update_then_downdate_bf16_inplace(
+                o_full, l_full, o_win, l_win), args.steps, args.warmup)
+            ref_us["downdate"] = rms_ * 1e3
     dbytes = rows_dd * H * (3 * D * 2 + 3 * 4)
     rows.append(dict(kind="update_then_downdate", rows=rows_dd * H, us=dms * 1e3,
-                     alg_gbs=dbytes / (dms * 1e-3) / 1e9, alg_bytes=dbytes))
+                     alg_gbs=dbytes / (dms * 1e-3) / 1e9, alg_bytes=dbytes,
+                     refkernel_us=ref_us.get("downdate")))
     print(json.dumps(rows[-1]), flush=True)
     del o_full, o_win, l_full, l_win, l_win0
     torch.cuda.empty_cache()
@@ -667,9 +686,17 @@ def run_config4(args):
                                            True)
 
     rms, _ = time_graph(rope, args.steps, args.warmup)
+    if want_ref:
+        rrp = build_ref.load_rope()
+        if rrp is not None:
+            rms_, _ = time_graph(lambda: rrp.mac_decode_rope_preserve_q_bf16(
+                q, k, v, q_pre, pool, pool_v, cache, positions, locs, D, True),
+                args.steps, args.warmup)
+            ref_us["rope"] = rms_ * 1e3
     rbytes = batch * ((args.hq * 3 + args.hkv * 5) * D * 2 + D * 4)
     rows.append(dict(kind="decode_rope_preserve", batch=batch, us=rms * 1e3,
-                     alg_gbs=rbytes / (rms * 1e-3) / 1e9, alg_bytes=rbytes))
+                     alg_gbs=rbytes / (rms * 1e-3) / 1e9, alg_bytes=rbytes,
+                     refkernel_us=ref_us.get("rope")))
     print(json.dumps(rows[-1]), flush=True)
     Path(args.config4_out).parent.mkdir(parents=True, exist_ok=True)
     Path(args.config4_out).write_text(json.dumps(dict(rows=rows, status=ops.query_status(dev)),

@@ -317,7 +317,7 @@ constexpr int kScanDepth = 4;
 constexpr int kScanLaneChunks = kScanU + 2;                          // 8 rows + 2 query chunks
 constexpr int kScanStageBytes = kScanLaneChunks * 16 * kThreads;     // 40 KB
 constexpr int kScanRoundTiles = 32;   // tiles per round when sub-results are combined in smem
-static_assert(kScanDepth * kScanStageBytes + kScanRoundTiles * 32 * 12 <= kRingBytes,
+static_assert(kScanDepth * kScanStageBytes + kScanRoundTiles * (32 * 12 + 48) <= kRingBytes,
               "scan ring must fit");
 
 struct ScanCursor {
@@ -330,6 +330,19 @@ struct ScanCursor {
 // ring_slot_to_pos (DEC.cu:798-807) with the modulo hoisted out of the slot loop.
 __device__ __forceinline__ int scan_slot_pos(const ScanCursor& c, int s) {
   return s + (s < c.tail ? c.off_lo : c.off_hi);
+}
+
+// Tile descriptors of a round live in shared memory: they are worked out once
+// (one thread per tile) instead of inside the streaming loop.
+struct ScanTileInfo {
+  int n, tile, P, req, cbeg, cend, s_begin, s_end, tail, off_lo, off_hi, elig;
+};
+__device__ __forceinline__ void scan_fetch_tile(const ScanTileInfo* info, int k, ScanCursor& c) {
+  const int4* src = reinterpret_cast<const int4*>(info + k);
+  const int4 w0 = src[0], w1 = src[1], w2 = src[2];
+  c.n = w0.x; c.tile = w0.y; c.P = w0.z; c.req = w0.w;
+  c.cbeg = w1.x; c.cend = w1.y; c.s_begin = w1.z; c.s_end = w1.w;
+  c.tail = w2.x; c.off_lo = w2.y; c.off_hi = w2.z; c.elig = w2.w != 0;
 }
 
 __device__ __forceinline__ void scan_load_tile(const MacB200DecodeArgs& a, int g, ScanCursor& c) {
@@ -397,7 +410,7 @@ __device__ void phase_match_scan(const DecodeParams& p, uint8_t* smem) {
                            ? (total_tiles - static_cast<int>(blockIdx.x) +
                               static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x)
                            : 0;
-  const int round_tiles = spar > 1 ? kScanRoundTiles : (my_tiles > 0 ? my_tiles : 1);
+  const int round_tiles = kScanRoundTiles;
   const char* ring = static_cast<const char*>(a.query_cache);
   const char* qsrc = static_cast<const char*>(a.q_pre);
   const uint32_t lane_base = smem_u32(smem) + tid * 16;
@@ -408,22 +421,31 @@ __device__ void phase_match_scan(const DecodeParams& p, uint8_t* smem) {
   float* part_d = reinterpret_cast<float*>(smem + kScanDepth * kScanStageBytes);
   int* part_p = reinterpret_cast<int*>(part_d + kScanRoundTiles * 32);
   int* part_s = part_p + kScanRoundTiles * 32;
+  ScanTileInfo* tinfo = reinterpret_cast<ScanTileInfo*>(part_s + kScanRoundTiles * 32);
 
   for (int r0 = 0; r0 < my_tiles; r0 += round_tiles) {
     const int rt = min(round_tiles, my_tiles - r0);
     const int nseq = rt * nh * nb;
+    if (tid < rt) {
+      ScanCursor c;
+      scan_load_tile(a, blockIdx.x + (r0 + tid) * gridDim.x, c);
+      ScanTileInfo ti;
+      ti.n = c.n; ti.tile = c.tile; ti.P = c.P; ti.req = c.req; ti.cbeg = c.cbeg; ti.cend = c.cend;
+      ti.s_begin = c.s_begin; ti.s_end = c.s_end; ti.tail = c.tail; ti.off_lo = c.off_lo;
+      ti.off_hi = c.off_hi; ti.elig = c.elig ? 1 : 0;
+      tinfo[tid] = ti;
+    }
+    __syncthreads();
     ScanCursor ci, cc;   // issue side, consume side
     ci.k = ci.hi = ci.b = 0;
-    if (nseq > 0) scan_load_tile(a, blockIdx.x + r0 * gridDim.x, ci);
-    else { ci.elig = false; ci.s_begin = ci.s_end = 0; ci.P = 0; ci.req = 0; ci.n = 0; ci.tile = 0;
-           ci.cbeg = ci.cend = 0; ci.tail = ci.off_lo = ci.off_hi = 0; }
+    scan_fetch_tile(tinfo, 0, ci);
     cc = ci;
     auto advance = [&](ScanCursor& c) {
       if (++c.b == nb) {
         c.b = 0;
         if (++c.hi == nh) {
           c.hi = 0;
-          if (++c.k < rt) scan_load_tile(a, blockIdx.x + (r0 + c.k) * gridDim.x, c);
+          if (++c.k < rt) scan_fetch_tile(tinfo, c.k, c);
         }
       }
     };
@@ -552,8 +574,8 @@ __device__ void phase_match_scan(const DecodeParams& p, uint8_t* smem) {
       cp_async_commit();
     }
     cp_async_wait<0>();
+    __syncthreads();   // everyone is done with this round's tile descriptors
     if (spar > 1) {
-      __syncthreads();
       for (int t = tid; t < rt * Hq; t += kThreads) {
         const int k = t / Hq, h = t - k * Hq;
         float d0 = INFINITY;
