@@ -14,7 +14,7 @@ from .bridge import (  # noqa: F401
     load_mac_persistent_decode_extension,
     load_mac_prefill_update_cache_extension,
 )
-from .workspace import make_decode_workspace  # noqa: F401
+from .workspace import make_decision_workspace, make_decode_workspace  # noqa: F401
 
 __all__ = [
     "install",
@@ -22,5 +22,6 @@ __all__ = [
     "load_mac_merge_downdate_cache_extension",
     "load_mac_persistent_decode_extension",
     "load_mac_prefill_update_cache_extension",
+    "make_decision_workspace",
     "make_decode_workspace",
 ]

@@ -30,6 +30,7 @@ def load_mac_persistent_decode_extension(verbose: bool = False, fast_math: bool 
     return SimpleNamespace(
         mac_persistent_decode_bf16=ops.mac_persistent_decode_bf16,
         mac_persistent_decode_bf16_noalloc=ops.mac_persistent_decode_bf16_noalloc,
+        mac_persistent_decode_bf16_lean=ops.mac_persistent_decode_bf16_lean,
         query_status=ops.query_status,
         launch_info=ops.launch_info,
     )

@@ -384,6 +384,44 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z); f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
 }
 
+// Full distance of the rows of a batch that passed the probe (bits of `live`):
+// second 128 bytes fetched, per-lane sums completed (lane distance 8 is the
+// in-lane add of the two halves), then lane distances 4, 2, 1.  Kept out of
+// line: it runs for a handful of rows per request and would otherwise double
+// the size of the streaming loop.
+struct ScanBest {
+  float d;
+  int p, s;
+};
+__device__ __noinline__ ScanBest scan_survivors(unsigned live, float a0, float a1, float a2,
+                                                float a3, float a4, float a5, float a6, float a7,
+                                                const uint8_t* qhi_smem, const char* rows,
+                                                int64_t slot_stride, unsigned oct_mask,
+                                                int s_first, int spar, int tail, int off_lo,
+                                                int off_hi, float bd, int bp, int bs) {
+  const float acc[kScanU] = {a0, a1, a2, a3, a4, a5, a6, a7};
+  float qhi[8];
+  unpack8(*reinterpret_cast<const uint4*>(qhi_smem), qhi);
+  uint4 raw2[kScanU];
+#pragma unroll
+  for (int u = 0; u < kScanU; ++u)
+    if ((live >> u) & 1u) raw2[u] = ld_stream16(rows + u * slot_stride);
+#pragma unroll
+  for (int u = 0; u < kScanU; ++u) {
+    if (!((live >> u) & 1u)) continue;
+    float d = __fadd_rn(acc[u], scan_dist8(qhi, raw2[u]));          // lane distance 8
+    d = __fadd_rn(d, __shfl_xor_sync(oct_mask, d, 4, 8));
+    d = __fadd_rn(d, __shfl_xor_sync(oct_mask, d, 2, 8));
+    d = __fadd_rn(d, __shfl_xor_sync(oct_mask, d, 1, 8));
+    const int s = s_first + u * spar;
+    const int pos = s + (s < tail ? off_lo : off_hi);
+    if (better_pair(d, pos, bd, bp)) { bd = d; bp = pos; bs = s; }
+  }
+  ScanBest r;
+  r.d = bd; r.p = bp; r.s = bs;
+  return r;
+}
+
 __device__ void phase_match_scan(const DecodeParams& p, uint8_t* smem) {
   const MacB200DecodeArgs& a = p.a;
   const int tid = threadIdx.x;
@@ -536,24 +574,11 @@ __device__ void phase_match_scan(const DecodeParams& p, uint8_t* smem) {
         const unsigned live = (__ballot_sync(oct_mask, survive) >> oct_shift) & 0xffu;
         if (__builtin_expect(live != 0u, 0)) {   // octet-uniform; rare unless the ring holds near rows
           const int h = hslot + cc.hi * p2;
-          const char* rows = row_ptr(cc, s_first, h) + 128;
-          float qhi[8];
-          unpack8(*reinterpret_cast<const uint4*>(src + (kScanU + 1) * (kThreads * 16)), qhi);
-          uint4 raw2[kScanU];
-#pragma unroll
-          for (int u = 0; u < kScanU; ++u)
-            if ((live >> u) & 1u) raw2[u] = ld_stream16(rows + u * slot_stride);
-#pragma unroll
-          for (int u = 0; u < kScanU; ++u) {
-            if (!((live >> u) & 1u)) continue;
-            float d = __fadd_rn(acc[u], scan_dist8(qhi, raw2[u]));          // lane distance 8
-            d = __fadd_rn(d, __shfl_xor_sync(oct_mask, d, 4, 8));
-            d = __fadd_rn(d, __shfl_xor_sync(oct_mask, d, 2, 8));
-            d = __fadd_rn(d, __shfl_xor_sync(oct_mask, d, 1, 8));
-            const int s = s_first + u * spar;
-            const int pos = scan_slot_pos(cc, s);
-            if (better_pair(d, pos, bd, bp)) { bd = d; bp = pos; bs = s; }
-          }
+          const ScanBest nb_ = scan_survivors(
+              live, acc[0], acc[1], acc[2], acc[3], acc[4], acc[5], acc[6], acc[7],
+              src + (kScanU + 1) * (kThreads * 16), row_ptr(cc, s_first, h) + 128, slot_stride,
+              oct_mask, s_first, spar, cc.tail, cc.off_lo, cc.off_hi, bd, bp, bs);
+          bd = nb_.d; bp = nb_.p; bs = nb_.s;
         }
       }
       if (cc.b == nb - 1 && j == 0) {

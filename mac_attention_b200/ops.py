@@ -120,21 +120,24 @@ def _decode_call(
                     ("group_tail_end", group_tail_end), ("group_tail_tiles", group_tail_tiles),
                     ("group_mode", group_mode)):
         _check(t, name, _I32, 2)
-    for name, t in (("complete_task_go", complete_task_go),
-                    ("complete_task_tile", complete_task_tile),
-                    ("tail_task_go", tail_task_go), ("tail_task_tile", tail_task_tile),
-                    ("hit_tail_task_ho", hit_tail_task_ho),
-                    ("hit_tail_task_tile", hit_tail_task_tile), ("task_counts", task_counts)):
-        _check(t, name, _I32, 1)
-    _check_partial_o(partial_rect_o, "partial_rect_o")
-    _check(partial_rect_lse, "partial_rect_lse", _F32, 4)
-    _check_partial_o(partial_rect_reduced_o, "partial_rect_reduced_o")
-    _check(partial_rect_reduced_lse, "partial_rect_reduced_lse", _F32, 4)
-    _check_partial_o(partial_tail_o, "partial_tail_o")
-    _check(partial_tail_lse, "partial_tail_lse", _F32, 4)
-    _req(partial_rect_reduced_o.dtype == partial_rect_o.dtype
-         and partial_tail_o.dtype == partial_rect_o.dtype,
-         "all partial output workspaces must use the same dtype")
+    lean = partial_rect_o is None   # the lean operator passes no task lists / partial buffers
+    _check(task_counts, "task_counts", _I32, 1)
+    if not lean:
+        for name, t in (("complete_task_go", complete_task_go),
+                        ("complete_task_tile", complete_task_tile),
+                        ("tail_task_go", tail_task_go), ("tail_task_tile", tail_task_tile),
+                        ("hit_tail_task_ho", hit_tail_task_ho),
+                        ("hit_tail_task_tile", hit_tail_task_tile)):
+            _check(t, name, _I32, 1)
+        _check_partial_o(partial_rect_o, "partial_rect_o")
+        _check(partial_rect_lse, "partial_rect_lse", _F32, 4)
+        _check_partial_o(partial_rect_reduced_o, "partial_rect_reduced_o")
+        _check(partial_rect_reduced_lse, "partial_rect_reduced_lse", _F32, 4)
+        _check_partial_o(partial_tail_o, "partial_tail_o")
+        _check(partial_tail_lse, "partial_tail_lse", _F32, 4)
+        _req(partial_rect_reduced_o.dtype == partial_rect_o.dtype
+             and partial_tail_o.dtype == partial_rect_o.dtype,
+             "all partial output workspaces must use the same dtype")
 
     N, Hq, D = q_post.shape
     Hkv = k_buffer.shape[1]
@@ -156,38 +159,43 @@ def _decode_call(
     match_tile_slots = int(match_tile_slots)
     max_context = int(max_context)
     Tm = match_dist.shape[2]
-    Tc = partial_rect_lse.shape[2]
-    Tr = partial_rect_reduced_lse.shape[2]
-    Tt = partial_tail_lse.shape[2]
     _req(Tm >= (M + match_tile_slots - 1) // match_tile_slots, "match workspace too small")
-    _req(Tc >= (max_context + tile_tokens - 1) // tile_tokens, "rect workspace too small")
-    _req(Tr >= (max_context + tile_tokens * 32 - 1) // (tile_tokens * 32),
-         "reduced rect workspace too small")
-    _req(Tt >= (int(semantic_pos_ahead) + tile_tokens - 1) // tile_tokens,
-         "tail workspace too small")
-    _req(partial_rect_o.shape[0] >= N and tuple(partial_rect_o.shape[1:]) == (Hkv, Tc, G, D),
-         "rect output workspace has wrong shape")
-    _req(partial_rect_lse.shape[0] >= N and tuple(partial_rect_lse.shape[1:]) == (Hkv, Tc, G),
-         "rect lse workspace has wrong shape")
-    _req(partial_rect_reduced_o.shape[0] >= N
-         and tuple(partial_rect_reduced_o.shape[1:]) == (Hkv, Tr, G, D),
-         "reduced rect output workspace has wrong shape")
-    _req(partial_rect_reduced_lse.shape[0] >= N
-         and tuple(partial_rect_reduced_lse.shape[1:]) == (Hkv, Tr, G),
-         "reduced rect lse workspace has wrong shape")
-    _req(partial_tail_o.shape[0] >= N and tuple(partial_tail_o.shape[1:]) == (Hkv, Tt, G, D),
-         "tail output workspace has wrong shape")
-    _req(partial_tail_lse.shape[0] >= N and tuple(partial_tail_lse.shape[1:]) == (Hkv, Tt, G),
-         "tail lse workspace has wrong shape")
     _req(group_mode.shape[0] >= N and group_mode.shape[1] >= Hkv, "group_mode workspace too small")
-    _req(complete_task_tile.numel() == complete_task_go.numel(), "complete task shape mismatch")
-    _req(tail_task_tile.numel() == tail_task_go.numel(), "tail task shape mismatch")
-    _req(hit_tail_task_tile.numel() == hit_tail_task_ho.numel(), "hit tail task shape mismatch")
     _req(task_counts.numel() >= 9, "task_counts must have at least nine elements")
     _req(int(bench_mode) in (0, 1, 2), "unsupported synthetic MAC bench mode")
-    _req(complete_task_go.numel() >= N * Hq * Tc, "complete task workspace too small")
-    _req(tail_task_go.numel() >= N * Hkv * Tt, "tail task workspace too small")
-    _req(hit_tail_task_ho.numel() >= N * Hq * Tt, "hit tail task workspace too small")
+    if not lean:
+        Tc = partial_rect_lse.shape[2]
+        Tr = partial_rect_reduced_lse.shape[2]
+        Tt = partial_tail_lse.shape[2]
+        _req(Tm >= (M + match_tile_slots - 1) // match_tile_slots, "match workspace too small")
+        _req(Tc >= (max_context + tile_tokens - 1) // tile_tokens, "rect workspace too small")
+        _req(Tr >= (max_context + tile_tokens * 32 - 1) // (tile_tokens * 32),
+             "reduced rect workspace too small")
+        _req(Tt >= (int(semantic_pos_ahead) + tile_tokens - 1) // tile_tokens,
+             "tail workspace too small")
+        _req(partial_rect_o.shape[0] >= N and tuple(partial_rect_o.shape[1:]) == (Hkv, Tc, G, D),
+             "rect output workspace has wrong shape")
+        _req(partial_rect_lse.shape[0] >= N and tuple(partial_rect_lse.shape[1:]) == (Hkv, Tc, G),
+             "rect lse workspace has wrong shape")
+        _req(partial_rect_reduced_o.shape[0] >= N
+             and tuple(partial_rect_reduced_o.shape[1:]) == (Hkv, Tr, G, D),
+             "reduced rect output workspace has wrong shape")
+        _req(partial_rect_reduced_lse.shape[0] >= N
+             and tuple(partial_rect_reduced_lse.shape[1:]) == (Hkv, Tr, G),
+             "reduced rect lse workspace has wrong shape")
+        _req(partial_tail_o.shape[0] >= N and tuple(partial_tail_o.shape[1:]) == (Hkv, Tt, G, D),
+             "tail output workspace has wrong shape")
+        _req(partial_tail_lse.shape[0] >= N and tuple(partial_tail_lse.shape[1:]) == (Hkv, Tt, G),
+             "tail lse workspace has wrong shape")
+        _req(group_mode.shape[0] >= N and group_mode.shape[1] >= Hkv, "group_mode workspace too small")
+        _req(complete_task_tile.numel() == complete_task_go.numel(), "complete task shape mismatch")
+        _req(tail_task_tile.numel() == tail_task_go.numel(), "tail task shape mismatch")
+        _req(hit_tail_task_tile.numel() == hit_tail_task_ho.numel(), "hit tail task shape mismatch")
+        _req(task_counts.numel() >= 9, "task_counts must have at least nine elements")
+        _req(int(bench_mode) in (0, 1, 2), "unsupported synthetic MAC bench mode")
+        _req(complete_task_go.numel() >= N * Hq * Tc, "complete task workspace too small")
+        _req(tail_task_go.numel() >= N * Hkv * Tt, "tail task workspace too small")
+        _req(hit_tail_task_ho.numel() >= N * Hq * Tt, "hit tail task workspace too small")
     ws_batch = match_dist.shape[0]
     for name, t in (("match_dist", match_dist), ("match_pos", match_pos),
                     ("match_slot", match_slot)):
@@ -285,7 +293,7 @@ def _decode_key(args):
     shapes the struct is derived from, and all scalars.  A repeat of the same
     call (serving loops and graph warm-ups pass the same buffers every step)
     reuses the checked argument struct instead of re-validating ~50 tensors."""
-    ptrs = tuple(args[i].data_ptr() for i in _TENSOR_ARGS)
+    ptrs = tuple(0 if args[i] is None else args[i].data_ptr() for i in _TENSOR_ARGS)
     return (ptrs, args[43:64], tuple(args[0].shape), tuple(args[2].shape[:2]),
             tuple(args[4].shape), tuple(args[8].shape[:2]), tuple(args[13].shape),
             args[42].numel(), args[12].numel(), args[7].dtype, args[0].device)
@@ -319,6 +327,30 @@ def mac_persistent_decode_bf16(*args) -> None:
     if len(args) != _DECODE_ARG_COUNT:
         raise TypeError(f"mac_persistent_decode_bf16() takes {_DECODE_ARG_COUNT} positional "
                         f"arguments ({len(args)} given)")
+    _decode_entry("mac_b200_persistent_decode_bf16", args)
+
+
+def mac_persistent_decode_bf16_lean(q_post, q_pre, k_buffer, v_buffer, req_to_token, req_ids,
+                                    past_lens, out_cache_loc, query_cache, attn_cache, lse_cache,
+                                    out, optional_lse, decisions, *scalars_and_gate) -> None:
+    """The decode step without the reference's scheduler scratch.
+
+    The reference operator wants 30 workspace tensors, 4-9 GB of them task lists
+    and partial buffers of its own scheduler (``fi_hooks.py:1594-1649`` in the
+    reference project) that this kernel never touches.  This entry takes the 13
+    data tensors, ``decisions`` = the 18 observable workspace tensors from
+    :func:`mac_attention_b200.workspace.make_decision_workspace` (match arrays,
+    head/group decision arrays, ``task_counts``, ``phase_cycles``), then the same
+    21 scalars, ``query_post_cache`` and the three readiness-gate tensors as the
+    full operator.  Same kernel, same results."""
+    if len(decisions) != 18:
+        raise TypeError("decisions must hold the 18 tensors of make_decision_workspace()")
+    if len(scalars_and_gate) != 25:
+        raise TypeError("expected 21 scalars, query_post_cache and 3 readiness-gate tensors")
+    args = (q_post, q_pre, k_buffer, v_buffer, req_to_token, req_ids, past_lens, out_cache_loc,
+            query_cache, attn_cache, lse_cache, out, optional_lse,
+            *decisions[:16], None, None, None, None, None, None, decisions[16],
+            None, None, None, None, None, None, decisions[17], *scalars_and_gate)
     _decode_entry("mac_b200_persistent_decode_bf16", args)
 
 

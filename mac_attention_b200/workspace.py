@@ -50,3 +50,22 @@ def make_decode_workspace(batch, hq, hkv, capacity, max_context, tile_tokens, ma
         torch.empty(batch, hkv, tt, group, device=device, dtype=torch.float32),
         torch.zeros(phase_slots, device=device, dtype=torch.int64),
     ]
+
+
+def make_decision_workspace(batch, hq, hkv, capacity, match_tile_slots, *, device="cuda",
+                            phase_slots=16):
+    """The 18 observable workspace tensors only (a few hundred KB): the three
+    per-tile match arrays, six per-head and seven per-group decision arrays,
+    ``task_counts`` and ``phase_cycles`` -- what ``mac_persistent_decode_bf16_lean``
+    takes instead of the reference's 30-tensor workspace."""
+    tm = (capacity + match_tile_slots - 1) // match_tile_slots
+    i32 = dict(device=device, dtype=torch.int32)
+    return [
+        torch.empty(batch, hq, tm, device=device, dtype=torch.float32),
+        torch.empty(batch, hq, tm, **i32),
+        torch.empty(batch, hq, tm, **i32),
+        *[torch.empty(batch, hq, **i32) for _ in range(6)],
+        *[torch.empty(batch, hkv, **i32) for _ in range(7)],
+        torch.empty(9, **i32),
+        torch.zeros(phase_slots, device=device, dtype=torch.int64),
+    ]

@@ -216,6 +216,33 @@ def test_oversized_workspace_int64_loc_and_no_lse():
     assert torch.equal(out, cu.out)
 
 
+def test_lean_operator_without_scheduler_scratch_matches_full_operator():
+    from mac_attention_b200 import make_decision_workspace
+
+    ext = load_mac_persistent_decode_extension()
+    case = synth.make_decode_case(batch=3, ctx=0, ctx_list=[2000, 3500, 900], hq=32, hkv=8,
+                                  capacity=256, seed=14)
+    synth.plant_matches(case, hit_fraction=0.5, borderline_fraction=0.5, seed=3)
+    cfg = O.DecodeConfig(max_context=4096, semantic_pos_ahead=128, front_sink_tokens=16)
+    full = run_cuda(case, cfg)
+    c = case.to("cuda").clone()
+    dws = make_decision_workspace(3, 32, 8, 256, cfg.match_tile_slots)
+    assert sum(t.numel() * t.element_size() for t in dws) < 1 << 20
+    out = torch.empty_like(c.q_post)
+    lse = torch.empty(3, 32, device="cuda")
+    e = torch.empty(0)
+    ext.mac_persistent_decode_bf16_lean(c.q_post, c.q_pre, c.k, c.v, c.req_to_token, c.req_ids,
+                                        c.past_lens, c.out_cache_loc, c.query_cache, c.attn_cache,
+                                        c.lse_cache, out, lse, dws, *cfg.scalar_args(),
+                                        c.query_cache, e, e, e)
+    torch.cuda.synchronize()
+    assert torch.equal(out, full.out) and torch.equal(lse, full.lse)
+    for i, j in zip(range(16), range(16)):
+        assert torch.equal(dws[i], full.ws[j])
+    assert torch.equal(dws[16][:7], full.ws[22][:7])
+    assert torch.equal(c.attn_cache, full.case.attn_cache)
+
+
 def test_run_twice_is_bit_identical_and_graph_replay_matches():
     case = synth.make_decode_case(batch=4, ctx=2500, hq=32, hkv=8, capacity=512, seed=21)
     cfg = O.DecodeConfig(max_context=4096, bench_mode=1, bench_hit_rate=0.75, bench_seed=5)
