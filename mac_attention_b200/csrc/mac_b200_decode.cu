@@ -295,13 +295,12 @@ __device__ bool grid_barrier(unsigned nblocks) {
 // row at a time; lane j holds dims [8j, 8j+8) and, for rows that survive the
 // probe, dims [64+8j, 64+8j+8).
 //
-//  * Probe: only the first 128 bytes of every candidate row are fetched.  The
-//    64-dim partial distance, summed over the octet in the same pairing order
-//    the full sum uses, is an exact lower bound of the full distance in
-//    floating point (every addition of the full sum has operands that are >=
-//    the corresponding probe operands, and rounding is monotone).  A row whose
-//    probe is >= the hit threshold can never be a hit and is dropped; like the
-//    reference's probe (DEC.cu:996-1059) this never changes a decision.
+//  * Probe: only the first 128 bytes of every candidate row are fetched and
+//    their 64-dim partial distance is estimated in packed bf16 arithmetic with
+//    a proven relative error below 2.4 %.  The partial distance is a lower
+//    bound of the full one, so a row whose estimate is >= 1.0625 x the hit
+//    threshold can never be a hit and is dropped; like the reference's probe
+//    (DEC.cu:996-1059) this never changes a decision.
 //  * Survivors: the second 128 bytes are fetched and the full distance is
 //    formed as in the reference (DEC.cu:1062-1069, 343-349): per-lane sums of 8
 //    sequential FMAs, then pairwise at lane distance 8 (here: in-lane, first
@@ -384,24 +383,38 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z); f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
 }
 
-// Full distance of the rows of a batch that passed the probe (bits of `live`):
-// second 128 bytes fetched, per-lane sums completed (lane distance 8 is the
-// in-lane add of the two halves), then lane distances 4, 2, 1.  Kept out of
+// 8-dim partial distance in packed bf16 (probe only; see its error bound at the use).
+__device__ __forceinline__ float scan_probe8(const uint4& q, const uint4& c) {
+  const __nv_bfloat162* q2 = reinterpret_cast<const __nv_bfloat162*>(&q);
+  const __nv_bfloat162* c2 = reinterpret_cast<const __nv_bfloat162*>(&c);
+  __nv_bfloat162 acc = __floats2bfloat162_rn(0.0f, 0.0f);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 d = __hsub2(q2[i], c2[i]);
+    acc = __hfma2(d, d, acc);
+  }
+  const uint32_t bits = *reinterpret_cast<const uint32_t*>(&acc);
+  return bf16_lo(bits) + bf16_hi(bits);
+}
+
+// Exact distance of the rows of a batch that passed the probe (bits of `live`):
+// first half re-read from the staged copy, second 128 bytes fetched, per-lane
+// fp32 sums of 8 sequential FMAs, lane distance 8 = in-lane add of the two
+// halves, then lane distances 4, 2, 1 (DEC.cu:1062-1069, 343-349).  Kept out of
 // line: it runs for a handful of rows per request and would otherwise double
 // the size of the streaming loop.
 struct ScanBest {
   float d;
   int p, s;
 };
-__device__ __noinline__ ScanBest scan_survivors(unsigned live, float a0, float a1, float a2,
-                                                float a3, float a4, float a5, float a6, float a7,
-                                                const uint8_t* qhi_smem, const char* rows,
-                                                int64_t slot_stride, unsigned oct_mask,
-                                                int s_first, int spar, int tail, int off_lo,
-                                                int off_hi, float bd, int bp, int bs) {
-  const float acc[kScanU] = {a0, a1, a2, a3, a4, a5, a6, a7};
-  float qhi[8];
-  unpack8(*reinterpret_cast<const uint4*>(qhi_smem), qhi);
+__device__ __noinline__ ScanBest scan_survivors(unsigned live, const uint8_t* stage,
+                                                const char* rows, int64_t slot_stride,
+                                                unsigned oct_mask, int s_first, int spar,
+                                                int tail, int off_lo, int off_hi, float bd,
+                                                int bp, int bs) {
+  float qlo[8], qhi[8];
+  unpack8(*reinterpret_cast<const uint4*>(stage + kScanU * (kThreads * 16)), qlo);
+  unpack8(*reinterpret_cast<const uint4*>(stage + (kScanU + 1) * (kThreads * 16)), qhi);
   uint4 raw2[kScanU];
 #pragma unroll
   for (int u = 0; u < kScanU; ++u)
@@ -409,7 +422,8 @@ __device__ __noinline__ ScanBest scan_survivors(unsigned live, float a0, float a
 #pragma unroll
   for (int u = 0; u < kScanU; ++u) {
     if (!((live >> u) & 1u)) continue;
-    float d = __fadd_rn(acc[u], scan_dist8(qhi, raw2[u]));          // lane distance 8
+    const float lo = scan_dist8(qlo, *reinterpret_cast<const uint4*>(stage + u * (kThreads * 16)));
+    float d = __fadd_rn(lo, scan_dist8(qhi, raw2[u]));               // lane distance 8
     d = __fadd_rn(d, __shfl_xor_sync(oct_mask, d, 4, 8));
     d = __fadd_rn(d, __shfl_xor_sync(oct_mask, d, 2, 8));
     d = __fadd_rn(d, __shfl_xor_sync(oct_mask, d, 1, 8));
@@ -454,7 +468,7 @@ __device__ void phase_match_scan(const DecodeParams& p, uint8_t* smem) {
   const uint32_t lane_base = smem_u32(smem) + tid * 16;
   const uint8_t* lane_ptr = smem + tid * 16;
   const int64_t slot_stride = static_cast<int64_t>(Hq) * kRowBytes * spar;  // bytes between rows of a batch
-  const float thr = p.thr_dist;
+  const float thr_probe = p.thr_dist * 1.0625f;   // see the probe's error bound below
   // partial (per sub) results of a round, only used when spar > 1
   float* part_d = reinterpret_cast<float*>(smem + kScanDepth * kScanStageBytes);
   int* part_p = reinterpret_cast<int*>(part_d + kScanRoundTiles * 32);
@@ -541,12 +555,17 @@ __device__ void phase_match_scan(const DecodeParams& p, uint8_t* smem) {
       if (cc.b == 0) { bd = INFINITY; bp = INT_MAX; bs = -1; }
       if (cc.elig) {
         const uint8_t* src = lane_ptr + (seq % kScanDepth) * kScanStageBytes;
-        float qlo[8];
-        unpack8(*reinterpret_cast<const uint4*>(src + kScanU * (kThreads * 16)), qlo);
+        // Probe in packed bf16 arithmetic (two dims per instruction).  Each lane's
+        // 8-dim sum carries a relative error below 6 * 2^-8 = 2.4 % (one rounding
+        // of the difference, squared, plus four roundings of the running sum), so
+        // comparing against the threshold widened by 1/16 can only let extra rows
+        // through to the exact evaluation, never drop a row whose exact distance
+        // is below the threshold.
+        const uint4 qv = *reinterpret_cast<const uint4*>(src + kScanU * (kThreads * 16));
         float acc[kScanU];
 #pragma unroll
         for (int u = 0; u < kScanU; ++u)
-          acc[u] = scan_dist8(qlo, *reinterpret_cast<const uint4*>(src + u * (kThreads * 16)));
+          acc[u] = scan_probe8(qv, *reinterpret_cast<const uint4*>(src + u * (kThreads * 16)));
         // halving exchange over the octet: lane j ends with the probe sum of row j
         const bool b2 = (j & 4) != 0, b1 = (j & 2) != 0, b0 = (j & 1) != 0;
         float w4[4];
@@ -570,14 +589,13 @@ __device__ void phase_match_scan(const DecodeParams& p, uint8_t* smem) {
         const int s_mine = s_first + j * spar;
         const int pos_mine = scan_slot_pos(cc, s_mine);
         const bool survive = s_mine < cc.s_end && pos_mine >= cc.cbeg && pos_mine < cc.cend &&
-                             probe < thr;   // NaN probes drop out here as well
+                             probe < thr_probe;   // NaN probes drop out here as well
         const unsigned live = (__ballot_sync(oct_mask, survive) >> oct_shift) & 0xffu;
         if (__builtin_expect(live != 0u, 0)) {   // octet-uniform; rare unless the ring holds near rows
           const int h = hslot + cc.hi * p2;
           const ScanBest nb_ = scan_survivors(
-              live, acc[0], acc[1], acc[2], acc[3], acc[4], acc[5], acc[6], acc[7],
-              src + (kScanU + 1) * (kThreads * 16), row_ptr(cc, s_first, h) + 128, slot_stride,
-              oct_mask, s_first, spar, cc.tail, cc.off_lo, cc.off_hi, bd, bp, bs);
+              live, src, row_ptr(cc, s_first, h) + 128, slot_stride, oct_mask, s_first, spar,
+              cc.tail, cc.off_lo, cc.off_hi, bd, bp, bs);
           bd = nb_.d; bp = nb_.p; bs = nb_.s;
         }
       }

@@ -119,6 +119,34 @@ def test_planted_and_borderline_matches_vs_oracle(spec):
     _status_clean()
 
 
+def test_probe_never_drops_rows_whose_distance_sits_in_the_probed_half():
+    """Ring rows that differ from the query only in the first 64 dims, with a
+    squared distance within 3 % of the threshold on either side: the scan's
+    approximate probe sees the whole distance, so this is where a too tight
+    pruning margin would flip a decision."""
+    case = synth.make_decode_case(batch=2, ctx=3000, hq=32, hkv=8, capacity=512, seed=23)
+    g = torch.Generator().manual_seed(99)
+    thr = 2.0 * 128 * (1.0 - 0.45) ** 2
+    for n in range(2):
+        P = int(case.past_lens[n])
+        for h in range(32):
+            for rep in range(3):
+                pos = P - 1 - int(torch.randint(0, 500, (1,), generator=g))
+                d = torch.zeros(128)
+                d[:64] = torch.randn(64, generator=g)
+                tgt = thr * (0.97 + 0.06 * float(torch.rand((), generator=g)))
+                row = case.q_pre[n, h].float() + d * math.sqrt(tgt / float((d * d).sum()))
+                case.query_cache[n, pos % 512, h] = row.to(torch.bfloat16)
+                case.lse_cache[n, pos % 512, h] = 3.0
+    cfg = O.DecodeConfig(max_context=4096, semantic_pos_ahead=64)
+    cu = run_cuda(case, cfg)
+    orc, orc_case = run_oracle(case, cfg)
+    assert_decisions_equal(cu, orc, 2)
+    assert 5 < int(orc.head_hit.sum()) < 64
+    assert_outputs_close(cu, orc, orc_case)
+    _status_clean()
+
+
 def test_config0_shape_cpu_plumbing_case():
     """Llama-3.1-8B attention shape, batch 2, context 4096, 64 planted prior
     queries, half of the step queries near a planted one."""
