@@ -298,6 +298,16 @@ int mac_b200_abi_version(void);
 int mac_b200_query_status(uint32_t* status_out, void* stream);
 
 /*
+ * Self-test of the kernels' bounded waits (no counterpart in the reference,
+ * whose grid.sync() cannot time out).  Runs a two-CTA kernel that waits at a
+ * barrier which nothing completes, with a 2 ms limit, on barrier words of its
+ * own: both CTAs must give up and return.  Reports how many CTAs gave up and
+ * the status word they left (read and cleared like mac_b200_query_status).
+ * Synchronises the stream; a health check, not a hot-path call.
+ */
+int mac_b200_selftest_bounded_wait(uint32_t* status_out, int32_t* ctas_gave_up, void* stream);
+
+/*
  * Static launch facts of the decode kernel on the current device, for logs
  * and benchmarks (the reference prints the same under
  * MAC_PERSISTENT_DEBUG_LAUNCH, mac_decode_persistent.cu:5406-5419).

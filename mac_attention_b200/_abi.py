@@ -86,6 +86,7 @@ PROTOTYPES = {
     "mac_b200_abi_version": (C.c_int, []),
     "mac_b200_query_status": (C.c_int, [C.POINTER(C.c_uint32), ptr]),
     "mac_b200_launch_info": (C.c_int, [C.POINTER(MacB200LaunchInfo)]),
+    "mac_b200_selftest_bounded_wait": (C.c_int, [C.POINTER(C.c_uint32), C.POINTER(C.c_int32), ptr]),
 }
 
 ABI_VERSION = 1

@@ -58,7 +58,7 @@ constexpr int kSmemPerm = kMaxGroups * 2;              // u16 gperm[]
 constexpr int kSmemPrefix = (kMaxGroups + 1) * 4;      // u32 cost prefix
 constexpr int kSmemMisc = 1024;
 constexpr int kSmemBytes = kRingBytes + kSmemPerm + kSmemPrefix + 12 + kSmemMisc;
-constexpr unsigned kSpinLimit = 1u << 22;  // polls (each >= ~100 ns) before a wait gives up
+constexpr unsigned long long kBarrierLimitNs = 2000000000ull;  // a grid-barrier wait gives up after 2 s
 constexpr float kLog2e = 1.4426950408889634074f;
 constexpr float kLn2 = 0.6931471805599453094f;
 
@@ -256,26 +256,34 @@ __device__ __forceinline__ int bench_target_miss_units(const MacB200DecodeArgs& 
 }
 
 // ------------------------------------------------------------- grid barrier
-// Sense-reversing barrier on two static words.  The wait is bounded: when it
-// runs out the CTA records MAC_B200_STATUS_BARRIER_TIMEOUT and the kernel
-// returns (all CTAs observe the same failure through the return value).
-__device__ bool grid_barrier(unsigned nblocks) {
+// Sense-reversing barrier on two device words.  The wait is bounded by wall
+// time (%globaltimer): when it runs out the CTA records
+// MAC_B200_STATUS_BARRIER_TIMEOUT and the kernel returns (every CTA observes the
+// failure through the return value; none is left spinning).
+__device__ __forceinline__ unsigned long long global_ns_u64() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ bool grid_barrier_on(unsigned nblocks, unsigned* count, unsigned* gen_word,
+                                unsigned long long limit_ns) {
   __shared__ int sh_ok;
   __syncthreads();
   if (threadIdx.x == 0) {
     int ok = 1;
-    const unsigned gen = ld_acquire_u32(&g_bar_gen);
+    const unsigned gen = ld_acquire_u32(gen_word);
     __threadfence();
-    const unsigned prev = atomicAdd(&g_bar_count, 1u);
+    const unsigned prev = atomicAdd(count, 1u);
     if (prev == nblocks - 1) {
-      g_bar_count = 0;
+      *count = 0;
       __threadfence();
-      atomicAdd(&g_bar_gen, 1u);
+      atomicAdd(gen_word, 1u);
     } else {
+      const unsigned long long t0 = global_ns_u64();
       unsigned polls = 0;
-      while (ld_acquire_u32(&g_bar_gen) == gen) {
+      while (ld_acquire_u32(gen_word) == gen) {
         __nanosleep(40);
-        if (++polls > kSpinLimit) {
+        if ((++polls & 31u) == 0u && global_ns_u64() - t0 > limit_ns) {
           atomicOr(&g_status, MAC_B200_STATUS_BARRIER_TIMEOUT);
           ok = 0;
           break;
@@ -287,6 +295,19 @@ __device__ bool grid_barrier(unsigned nblocks) {
   }
   __syncthreads();
   return sh_ok != 0;
+}
+__device__ bool grid_barrier(unsigned nblocks) {
+  return grid_barrier_on(nblocks, &g_bar_count, &g_bar_gen, kBarrierLimitNs);
+}
+
+// Self-test of the bounded wait: two CTAs meet at a barrier that expects three,
+// on words of their own, with a 2 ms limit.  Nothing ever completes it; both
+// give up, set the status bit and return.
+__device__ unsigned g_selftest_count = 0;
+__device__ unsigned g_selftest_gen = 0;
+__global__ void bounded_wait_selftest_kernel(int* gave_up) {
+  const bool ok = grid_barrier_on(gridDim.x + 1, &g_selftest_count, &g_selftest_gen, 2000000ull);
+  if (threadIdx.x == 0 && !ok) atomicAdd(gave_up, 1);
 }
 
 // ---------------------------------------------------------------- phase A
@@ -1842,6 +1863,26 @@ extern "C" int mac_b200_query_status(uint32_t* status_out, void* stream_v) {
     }
   }
   return MAC_B200_OK;
+}
+
+extern "C" int mac_b200_selftest_bounded_wait(uint32_t* status_out, int32_t* ctas_gave_up,
+                                              void* stream_v) {
+  MAC_REQUIRE(status_out != nullptr && ctas_gave_up != nullptr, "outputs must not be null");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  int* d_count = nullptr;
+  MAC_CUDA(cudaMalloc(&d_count, sizeof(int)));
+  MAC_CUDA(cudaMemsetAsync(d_count, 0, sizeof(int), stream));
+  bounded_wait_selftest_kernel<<<2, 32, 0, stream>>>(d_count);
+  MAC_CUDA(cudaGetLastError());
+  g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+  MAC_CUDA(cudaStreamSynchronize(stream));
+  int gave_up = 0;
+  MAC_CUDA(cudaMemcpy(&gave_up, d_count, sizeof(int), cudaMemcpyDeviceToHost));
+  MAC_CUDA(cudaFree(d_count));
+  *ctas_gave_up = gave_up;
+  const unsigned zero = 0;
+  MAC_CUDA(cudaMemcpyToSymbol(g_selftest_count, &zero, sizeof(zero)));
+  return mac_b200_query_status(status_out, stream_v);
 }
 
 extern "C" int mac_b200_launch_info(MacB200LaunchInfo* info) {

@@ -573,6 +573,17 @@ def query_status(device=None) -> int:
     return int(v.value)
 
 
+def selftest_bounded_wait(device=None):
+    """Runs the library's bounded-wait self-test; returns ``(status_word, ctas_that_gave_up)``."""
+    lib = _abi.load_library()
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    status, gave_up = C.c_uint32(0), C.c_int32(0)
+    with torch.cuda.device(dev):
+        _abi.check(lib.mac_b200_selftest_bounded_wait(C.byref(status), C.byref(gave_up),
+                                                      _stream_ptr(dev)))
+    return int(status.value), int(gave_up.value)
+
+
 def launch_info(device=None) -> dict:
     lib = _abi.load_library()
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)

@@ -25,7 +25,7 @@ def _declared_functions():
 
 def test_header_functions_are_exported(lib):
     names = _declared_functions()
-    assert len(names) == 12
+    assert len(names) == 13
     for n in names:
         assert hasattr(lib, n), n
     assert sorted(_abi.PROTOTYPES) == names

@@ -352,6 +352,55 @@ def test_malformed_rows_are_zeroed_and_flagged():
     assert ops.query_status() == 0  # reading clears it
 
 
+def test_bounded_wait_gives_up_and_reports_without_hanging():
+    """A wait that nothing completes runs out after its limit, the kernel
+    returns, the status word says so, and the next decode step works."""
+    status, gave_up = ops.selftest_bounded_wait()
+    assert gave_up == 2
+    assert status & 0x1
+    assert ops.query_status() == 0
+    case = synth.make_decode_case(batch=2, ctx=600, hq=8, hkv=2, capacity=64, seed=3)
+    cfg = O.DecodeConfig(max_context=1024, semantic_pos_ahead=16)
+    cu = run_cuda(case, cfg)
+    orc, orc_case = run_oracle(case, cfg)
+    assert_outputs_close(cu, orc, orc_case)
+    _status_clean()
+
+
+def test_scratch_growth_is_refused_during_graph_capture():
+    ext = load_mac_persistent_decode_extension()
+    cfg = O.DecodeConfig(max_context=256, semantic_pos_ahead=16)
+    # far more KV groups than any other test: the scratch arena has to grow
+    if ops.launch_info()["arena_bytes"] > (45 << 20):
+        pytest.skip("the scratch arena is already large enough for this shape")
+    case = synth.make_decode_case(batch=500, ctx=40, hq=64, hkv=8, capacity=8, seed=1).to("cuda")
+    ws = make_decode_workspace(500, 64, 8, 8, 256, 32, 32, 16)
+    out = torch.empty_like(case.q_post)
+    lse = torch.empty(500, 64, device="cuda")
+    e = torch.empty(0)
+
+    def launch():
+        ext.mac_persistent_decode_bf16(case.q_post, case.q_pre, case.k, case.v, case.req_to_token,
+                                       case.req_ids, case.past_lens, case.out_cache_loc,
+                                       case.query_cache, case.attn_cache, case.lse_cache, out, lse,
+                                       *ws, *cfg.scalar_args(), case.query_cache, e, e, e)
+
+    graph = torch.cuda.CUDAGraph()
+    with pytest.raises(RuntimeError, match="captured"):
+        with torch.cuda.graph(graph):
+            launch()
+    torch.cuda.synchronize()
+    launch()                      # eager call grows the arena ...
+    torch.cuda.synchronize()
+    graph2 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph2):  # ... after which capture works
+        launch()
+    graph2.replay()
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all()
+    _status_clean()
+
+
 def test_argument_errors_raise_like_the_reference():
     ext = load_mac_persistent_decode_extension()
     case = synth.make_decode_case(batch=1, ctx=100, hq=8, hkv=2, capacity=16, seed=1).to("cuda")
