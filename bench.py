@@ -634,7 +634,75 @@ def run_config4(args):
                      us=pms * 1e3, alg_gbs=pbytes / (pms * 1e-3) / 1e9, alg_bytes=pbytes,
                      refkernel_us=ref_us.get("prefill")))
     print(json.dumps(rows[-1]), flush=True)
-    del src_q, src_a, src_l, qc, ac, lc, qpc
+
+    # the same ring build from the un-downdated prefill outputs: one pass
+    # (band-LSE scale + downdate + ring write + ready mark) against the hook's
+    # sequence of operators, which downdates every prompt row
+    band_a = torch.empty_like(src_q)
+    for r0 in range(0, band_a.shape[0], 1 << 16):
+        band_a[r0:r0 + (1 << 16)].normal_()
+    full_l = src_l + 8
+    band_l2 = (full_l - torch.rand_like(full_l) * 4 - 0.1) / math.log(2.0)   # log2-domain producer
+    ready = torch.zeros(R, device=dev, dtype=torch.bool)
+    cache_epoch = torch.full((R,), -1, device=dev, dtype=torch.int64)
+    request_epoch = torch.zeros(R, device=dev, dtype=torch.int64)
+
+    def build_one_pass():
+        pre.mac_prefill_downdate_update_cache(
+            qc, ac, lc, rl, req_ids, src_q, src_a, full_l, band_a, band_l2, offsets, lens, M, H, D,
+            qpc, band_lse_scale=math.log(2.0), ready=ready, cache_epoch=cache_epoch,
+            request_epoch=request_epoch)
+
+    bms, _ = time_graph(build_one_pass, args.steps, args.warmup)
+    from mac_attention_b200 import load_mac_merge_downdate_cache_extension as _load_dd
+
+    def sequence(dd_mod, pre_mod):
+        band_l = band_l2 * math.log(2.0)
+        dd_mod.mac_update_then_downdate_bf16_inplace(src_a, full_l, band_a, band_l)
+        pre_mod.mac_prefill_update_cache(qc, ac, lc, rl, req_ids, src_q, band_a, band_l, offsets,
+                                         lens, M, H, D, qpc)
+        pre_mod.mac_mark_persistent_ready(ready, cache_epoch, request_epoch, req_ids)
+
+    few = max(3, min(args.steps, 10))
+    sms, _ = time_graph(lambda: sequence(_load_dd(), pre), few, 3)
+    if want_ref:
+        rdd_, rpre_ = build_ref.load_downdate(), build_ref.load_prefill()
+        if rdd_ is not None and rpre_ is not None:
+            rms_, _ = time_graph(lambda: sequence(rdd_, rpre_), few, 3)
+            ref_us["build_sequence"] = rms_ * 1e3
+    bbytes = batch * keep * H * (3 * 256 + 8 + 3 * 256 + 4)
+    rows.append(dict(kind="prefill_downdate_update_cache (one pass)", batch=batch, prompt_len=plen,
+                     capacity=M, us=bms * 1e3, alg_gbs=bbytes / (bms * 1e-3) / 1e9,
+                     alg_bytes=bbytes, operator_sequence_us=sms * 1e3,
+                     refkernel_sequence_us=ref_us.get("build_sequence")))
+    print(json.dumps(rows[-1]), flush=True)
+    # sink-exclusive rows (F = 128): the same pass plus each row's attention over
+    # the sink tokens, computed in the kernel from q_post and the paged K/V
+    Fs = 128
+    q_post_rows = torch.empty_like(src_q)
+    for r0 in range(0, q_post_rows.shape[0], 1 << 16):
+        q_post_rows[r0:r0 + (1 << 16)].normal_()
+    pool_k = torch.randn(batch * Fs, args.hkv, D, device=dev).to(torch.bfloat16)
+    pool_v = torch.randn(batch * Fs, args.hkv, D, device=dev).to(torch.bfloat16)
+    r2t = torch.arange(batch * Fs, device=dev, dtype=torch.int32).view(batch, Fs).contiguous()
+
+    def build_sink_exclusive():
+        pre.mac_prefill_downdate_update_cache(
+            qc, ac, lc, rl, req_ids, src_q, src_a, full_l, band_a, band_l2, offsets, lens, M, H, D,
+            qpc, band_lse_scale=math.log(2.0), sink_mode=ops.SINK_EXCLUDE, ready=ready,
+            cache_epoch=cache_epoch, request_epoch=request_epoch, q_post=q_post_rows,
+            k_buffer=pool_k, v_buffer=pool_v, req_to_token=r2t, front_sink_tokens=Fs,
+            semantic_pos_ahead=SEM)
+
+    xms, _ = time_graph(build_sink_exclusive, args.steps, args.warmup)
+    xbytes = bbytes + batch * keep * H * 256
+    xflops = 4.0 * batch * keep * H * Fs * D
+    rows.append(dict(kind="prefill_downdate_update_cache (sink-exclusive, F=128)", batch=batch,
+                     prompt_len=plen, capacity=M, us=xms * 1e3,
+                     alg_gbs=xbytes / (xms * 1e-3) / 1e9, alg_bytes=xbytes,
+                     sink_attention_tflops=xflops / (xms * 1e-3) / 1e12))
+    print(json.dumps(rows[-1]), flush=True)
+    del src_q, src_a, src_l, qc, ac, lc, qpc, band_a, full_l, band_l2, q_post_rows, pool_k, pool_v
     torch.cuda.empty_cache()
 
     # the producer of the prefill rows: downdate of the last M rows of every prompt

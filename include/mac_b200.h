@@ -232,6 +232,68 @@ int mac_b200_update_request_state(int32_t* req_len, int32_t* match_req_len,
                                   int32_t B, int32_t R, void* stream);
 
 /*
+ * One-pass prefill ring build: LSE downdate + ring write + readiness mark.
+ *
+ * The reference's prefill hook (flashinfer_hooks.py:2459-2492) runs, per layer,
+ *   band_lse *= ln 2                                   (elementwise, all rows)
+ *   mac_update_then_downdate_bf16_inplace(full, band)  (all rows, in place)
+ *   mac_prefill_update_cache(ring, q, band, band_lse)  (last min(len, M) rows)
+ *   mac_mark_persistent_ready(...)
+ * and, when front_sink_tokens > 0, first overwrites the LSE with -inf so that
+ * prefill rows can never match (flashinfer_hooks.py:2205-2215).  Only the last
+ * min(len, M) rows of a request ever reach the ring, so this entry point
+ * downdates just those rows on their way into the ring and marks the requests
+ * ready, in one pass over the data.  The ring contents are those of the
+ * sequence above; the band tensors are NOT modified (the reference overwrites
+ * them with the downdated state and never reads them again).
+ *
+ * sink_mode selects what front-sink handling the ring rows get:
+ *   MAC_B200_SINK_NONE        F == 0: ring row = full - band.
+ *   MAC_B200_SINK_UNMATCHABLE the reference's behaviour for F > 0: same state,
+ *                             LSE = -inf (row can never be reused).
+ *   MAC_B200_SINK_EXCLUDE     no counterpart in the reference (its comment at
+ *                             flashinfer_hooks.py:2205-2215 describes it as not
+ *                             implemented): the attention of each row's post-RoPE
+ *                             query over the sink tokens [0, min(F, E)),
+ *                             E = max(pos + 1 - S, 0), is computed in the kernel
+ *                             and subtracted too, so the ring row covers exactly
+ *                             [min(F, E), E) as decode-written rows do and is
+ *                             matchable at once.  Needs D = 128, F <= 128.
+ */
+#define MAC_B200_SINK_NONE 0
+#define MAC_B200_SINK_UNMATCHABLE 1
+#define MAC_B200_SINK_EXCLUDE 2
+
+typedef struct MacB200PrefillBuildArgs {
+  MacB200PrefillArgs ring;       /* ring.src_attn / ring.src_lse: state of the FULL prefix of
+                                    each row; ring.src_lse holds full_lse_dtype elements      */
+  const void* band_attn;         /* [src_rows,H,D] bf16: state of each row's trailing window  */
+  const void* band_lse;          /* [src_rows,H], band_lse_dtype elements                     */
+  int32_t full_lse_dtype;        /* MAC_B200_LSE_*                                            */
+  int32_t band_lse_dtype;        /* MAC_B200_LSE_*                                            */
+  float band_lse_scale;          /* band LSE is multiplied by this first (ln 2 for a log2-
+                                    domain producer, 1 otherwise)                             */
+  int32_t sink_mode;             /* MAC_B200_SINK_*                                           */
+  uint8_t* ready;                /* [R] or NULL: readiness gate to mark (all three or none)   */
+  int64_t* cache_epoch;          /* [R]                                                       */
+  const int64_t* request_epoch;  /* [R]                                                       */
+  /* MAC_B200_SINK_EXCLUDE only */
+  int32_t Hkv;                   /* KV heads; H % Hkv == 0                                    */
+  int32_t front_sink_tokens;     /* F                                                         */
+  int32_t semantic_pos_ahead;    /* S: a row at position pos has prefix end E = pos + 1 - S   */
+  int32_t req_to_token_rows;
+  int32_t req_to_token_stride;
+  float sm_scale;
+  int64_t kv_tokens;             /* rows of k_buffer / v_buffer                               */
+  const void* q_post;            /* [src_rows,H,D] bf16 post-RoPE queries                     */
+  const void* k_buffer;          /* [kv_tokens,Hkv,D] bf16                                    */
+  const void* v_buffer;          /* [kv_tokens,Hkv,D] bf16                                    */
+  const int32_t* req_to_token;   /* [rows,stride] logical position -> KV pool row             */
+} MacB200PrefillBuildArgs;
+
+int mac_b200_prefill_downdate_update_cache(const MacB200PrefillBuildArgs* args, void* stream);
+
+/*
  * Arguments of the decode-time fused "preserve pre-RoPE q + RoPE(q,k) + KV-pool
  * write".  Replaces the 11 arguments of mac_decode_rope_preserve_q_bf16
  * (mac_decode_rope_preserve.cu:174-186).  Strides are in elements; the last

@@ -53,6 +53,20 @@ class MacB200PrefillArgs(C.Structure):
     ]
 
 
+class MacB200PrefillBuildArgs(C.Structure):
+    _fields_ = [
+        ("ring", MacB200PrefillArgs),
+        ("band_attn", ptr), ("band_lse", ptr),
+        ("full_lse_dtype", i32), ("band_lse_dtype", i32), ("band_lse_scale", C.c_float),
+        ("sink_mode", i32),
+        ("ready", ptr), ("cache_epoch", ptr), ("request_epoch", ptr),
+        ("Hkv", i32), ("front_sink_tokens", i32), ("semantic_pos_ahead", i32),
+        ("req_to_token_rows", i32), ("req_to_token_stride", i32), ("sm_scale", C.c_float),
+        ("kv_tokens", i64),
+        ("q_post", ptr), ("k_buffer", ptr), ("v_buffer", ptr), ("req_to_token", ptr),
+    ]
+
+
 class MacB200RopeArgs(C.Structure):
     _fields_ = [
         ("N", i64), ("Hq", i32), ("Hkv", i32), ("head_dim", i32), ("rotary_dim", i32),
@@ -77,6 +91,7 @@ PROTOTYPES = {
     "mac_b200_persistent_decode_bf16": (C.c_int, [C.POINTER(MacB200DecodeArgs), ptr]),
     "mac_b200_persistent_decode_bf16_noalloc": (C.c_int, [C.POINTER(MacB200DecodeArgs), ptr]),
     "mac_b200_prefill_update_cache": (C.c_int, [C.POINTER(MacB200PrefillArgs), ptr]),
+    "mac_b200_prefill_downdate_update_cache": (C.c_int, [C.POINTER(MacB200PrefillBuildArgs), ptr]),
     "mac_b200_mark_persistent_ready": (C.c_int, [ptr, ptr, ptr, ptr, i32, i32, ptr]),
     "mac_b200_invalidate_persistent_ready": (C.c_int, [ptr, ptr, ptr, ptr, i32, i32, ptr]),
     "mac_b200_update_request_state": (C.c_int, [ptr, ptr, ptr, ptr, ptr, ptr, i32, i32, ptr]),

@@ -46,6 +46,8 @@ def load_mac_prefill_update_cache_extension(verbose: bool = False) -> Any:
         mac_mark_persistent_ready=ops.mac_mark_persistent_ready,
         mac_invalidate_persistent_ready=ops.mac_invalidate_persistent_ready,
         mac_update_request_state=ops.mac_update_request_state,
+        # not in the reference module: downdate + ring write + ready mark in one pass
+        mac_prefill_downdate_update_cache=ops.mac_prefill_downdate_update_cache,
     )
 
 

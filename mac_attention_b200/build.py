@@ -15,8 +15,9 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libmac_b200.so"
 SOURCES = ["mac_b200_api.cu", "mac_b200_prefill.cu", "mac_b200_decode.cu", "mac_b200_rope.cu",
-           "mac_b200_downdate.cu"]
-HEADERS = [CSRC / "mac_b200_common.h", PKG.parent / "include" / "mac_b200.h"]
+           "mac_b200_downdate.cu", "mac_b200_prefill_build.cu"]
+HEADERS = [CSRC / "mac_b200_common.h", CSRC / "mac_b200_state_math.cuh",
+           PKG.parent / "include" / "mac_b200.h"]
 
 
 def _nvcc() -> str:

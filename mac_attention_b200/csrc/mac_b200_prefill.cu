@@ -13,6 +13,7 @@
 // streaming load/store, and the request_length bump runs as a second tiny
 // kernel so it cannot race the reads of L_before.
 #include "mac_b200_common.h"
+#include "mac_b200_state_math.cuh"
 
 namespace mac_b200 {
 namespace {
@@ -23,19 +24,6 @@ struct PrefillParams {
   MacB200PrefillArgs a;
   int ctas_per_request;
 };
-
-__device__ __forceinline__ uint4 ld_stream16(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
-__device__ __forceinline__ void st_stream16(void* p, uint4 v) {
-  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y),
-               "r"(v.z), "r"(v.w)
-               : "memory");
-}
 
 // Copies `bytes` from src to dst with 16-byte vectors when both are aligned,
 // else with the widest unit that divides everything.

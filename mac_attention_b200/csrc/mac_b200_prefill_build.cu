@@ -1,0 +1,664 @@
+// One-pass prefill ring build (sm_100a): LSE downdate + ring write + readiness
+// mark for the rows that reach the ring.
+//
+// The reference's prefill hook
+// (attention/src/mac_attention/integrations/sglang/flashinfer_hooks.py:2459-2492)
+// scales the band LSE, downdates EVERY prompt row in place
+// (csrc/mac_merge_downdate_cache.cu:116-288), copies the last min(len, M) rows of
+// each request into its ring (csrc/mac_prefill_update_cache.cu:201-269) and marks
+// the requests ready (same file, 374-409): four launches and, for a 32K prompt
+// with a 2K ring, sixteen times more downdate traffic than the ring needs.  Here
+// the rows bound for the ring are downdated on their way into it: each
+// (row, head) state is read once from the full-prefix and band tensors and
+// written once, to the ring.  The band tensors are left as they were.
+#include "mac_b200_common.h"
+#include "mac_b200_state_math.cuh"
+
+namespace mac_b200 {
+namespace {
+
+constexpr int kBuildThreads = 256;
+constexpr int kBuildMaxH = 256;  // heads whose row scalars fit the shared-memory tables
+
+struct RowSpan {
+  int req, keep, start, base_off, base_dest;
+  bool ok;
+};
+
+// Which rows of request b go where (mac_prefill_update_cache.cu:214-236).
+__device__ __forceinline__ RowSpan row_span(const MacB200PrefillArgs& p, int b) {
+  RowSpan s{};
+  s.ok = false;
+  s.req = p.req_ids[b];
+  const int Ni = p.lens[b];
+  if (Ni <= 0 || p.M <= 0) return s;
+  if (s.req < 0 || s.req >= p.R) return s;
+  s.start = Ni > p.M ? Ni - p.M : 0;
+  s.keep = Ni - s.start;
+  s.base_off = p.offsets[b];
+  if (s.base_off < 0 || s.base_off + Ni > p.src_rows) return s;
+  int L_before = p.request_length_by_batch ? p.request_length[b] : p.request_length[s.req];
+  if (L_before < 0) L_before = 0;
+  s.base_dest = static_cast<int>((static_cast<int64_t>(L_before) + s.start) % p.M);
+  s.ok = true;
+  return s;
+}
+
+struct ChunkLoads {
+  uint4 q[2][2], full[2][2], band[2][2];  // [row of the pair][chunk c, chunk c + blockDim]
+};
+
+__device__ __forceinline__ uint4 downdate_chunk(uint4 x4, uint4 y4, float t, float scale) {
+  const uint32_t x[4] = {x4.x, x4.y, x4.z, x4.w};
+  const uint32_t y[4] = {y4.x, y4.y, y4.z, y4.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float r0 = (lo_f(x[i]) - t * lo_f(y[i])) * scale;
+    const float r1 = (hi_f(x[i]) - t * hi_f(y[i])) * scale;
+    o[i] = pack2(r0, r1);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// grid = (ctas_per_request, B); CTA x of request b handles row pairs x, x+gridDim.x, ...
+__global__ void __launch_bounds__(kBuildThreads, 2)
+prefill_downdate_ring_kernel(const MacB200PrefillBuildArgs a) {
+  const MacB200PrefillArgs& p = a.ring;
+  const RowSpan sp = row_span(p, blockIdx.y);
+  if (!sp.ok) return;
+  const int H = p.H, D = p.D;
+  const size_t row_bf16 = static_cast<size_t>(H) * D * 2;
+  uint8_t* qc = static_cast<uint8_t*>(p.q_cache) + static_cast<size_t>(sp.req) * p.M * row_bf16;
+  uint8_t* ac = static_cast<uint8_t*>(p.attn_cache) + static_cast<size_t>(sp.req) * p.M * row_bf16;
+  float* lc = p.lse_cache + static_cast<size_t>(sp.req) * p.M * H;
+  uint8_t* pc = p.q_post_cache
+                    ? static_cast<uint8_t*>(p.q_post_cache) + static_cast<size_t>(sp.req) * p.M * row_bf16
+                    : nullptr;
+  const uint8_t* qs = static_cast<const uint8_t*>(p.src_q);
+  const uint8_t* fs = static_cast<const uint8_t*>(p.src_attn);
+  const uint8_t* bs = static_cast<const uint8_t*>(a.band_attn);
+  const bool unmatchable = a.sink_mode == MAC_B200_SINK_UNMATCHABLE;
+  const uint32_t nanw = 0x7fc07fc0u;
+  const uint4 nan4 = make_uint4(nanw, nanw, nanw, nanw);
+
+  const bool vec = D % 8 == 0 && H <= kBuildMaxH &&
+                   ((reinterpret_cast<uintptr_t>(qc) | reinterpret_cast<uintptr_t>(ac) |
+                     reinterpret_cast<uintptr_t>(qs) | reinterpret_cast<uintptr_t>(fs) |
+                     reinterpret_cast<uintptr_t>(bs) | reinterpret_cast<uintptr_t>(pc)) & 15u) == 0;
+  if (!vec) {
+    // Element-wise path for odd head sizes or unaligned bases.
+    const __nv_bfloat16* f16 = reinterpret_cast<const __nv_bfloat16*>(fs);
+    const __nv_bfloat16* b16 = reinterpret_cast<const __nv_bfloat16*>(bs);
+    const uint16_t* q16 = reinterpret_cast<const uint16_t*>(qs);
+    for (int i = blockIdx.x; i < sp.keep; i += gridDim.x) {
+      int dest = sp.base_dest + i;
+      if (dest >= p.M) dest -= p.M;
+      const size_t srow = static_cast<size_t>(sp.base_off + sp.start + i);
+      for (int e = threadIdx.x; e < H * D; e += blockDim.x) {
+        const int h = e / D;
+        float ret, t, scale;
+        downdate_scalars(load_lse(p.src_lse, a.full_lse_dtype, srow * H + h),
+                         __fmul_rn(load_lse(a.band_lse, a.band_lse_dtype, srow * H + h),
+                                   a.band_lse_scale),  // rounded product, as a separate scale op
+                         ret, t, scale);
+        const float r = (__bfloat162float(f16[srow * H * D + e]) -
+                         t * __bfloat162float(b16[srow * H * D + e])) * scale;
+        reinterpret_cast<__nv_bfloat16*>(ac)[static_cast<size_t>(dest) * H * D + e] =
+            __float2bfloat16_rn(r);
+        reinterpret_cast<uint16_t*>(qc)[static_cast<size_t>(dest) * H * D + e] = q16[srow * H * D + e];
+        if (pc) reinterpret_cast<uint16_t*>(pc)[static_cast<size_t>(dest) * H * D + e] = 0x7fc0;
+        if (e == h * D) lc[static_cast<size_t>(dest) * H + h] = unmatchable ? -INFINITY : ret;
+      }
+    }
+    return;
+  }
+
+  __shared__ float s_t[2][2 * kBuildMaxH];
+  __shared__ float s_scale[2][2 * kBuildMaxH];
+  const int chunks = static_cast<int>(row_bf16 / 16);
+  const int cph = D / 8;  // 16-byte chunks per head
+  int par = 0;
+  for (int i = 2 * blockIdx.x; i < sp.keep; i += 2 * gridDim.x, par ^= 1) {
+    const bool two = i + 1 < sp.keep;
+    int d0 = sp.base_dest + i;
+    if (d0 >= p.M) d0 -= p.M;
+    int d1 = d0 + 1;
+    if (d1 >= p.M) d1 -= p.M;
+    const size_t s0 = static_cast<size_t>(sp.base_off + sp.start + i), s1 = s0 + 1;
+
+    // First pass of row loads goes out before the LSE arithmetic, so that the
+    // exp/log chain of the scalars overlaps the memory latency.
+    ChunkLoads L;
+    auto issue = [&](int c) {
+      const int c2 = c + blockDim.x;
+      const bool more = c2 < chunks;
+      L.q[0][0] = ld_stream16(qs + s0 * row_bf16 + static_cast<size_t>(c) * 16);
+      L.full[0][0] = ld_stream16(fs + s0 * row_bf16 + static_cast<size_t>(c) * 16);
+      L.band[0][0] = ld_stream16(bs + s0 * row_bf16 + static_cast<size_t>(c) * 16);
+      if (more) {
+        L.q[0][1] = ld_stream16(qs + s0 * row_bf16 + static_cast<size_t>(c2) * 16);
+        L.full[0][1] = ld_stream16(fs + s0 * row_bf16 + static_cast<size_t>(c2) * 16);
+        L.band[0][1] = ld_stream16(bs + s0 * row_bf16 + static_cast<size_t>(c2) * 16);
+      }
+      if (two) {
+        L.q[1][0] = ld_stream16(qs + s1 * row_bf16 + static_cast<size_t>(c) * 16);
+        L.full[1][0] = ld_stream16(fs + s1 * row_bf16 + static_cast<size_t>(c) * 16);
+        L.band[1][0] = ld_stream16(bs + s1 * row_bf16 + static_cast<size_t>(c) * 16);
+        if (more) {
+          L.q[1][1] = ld_stream16(qs + s1 * row_bf16 + static_cast<size_t>(c2) * 16);
+          L.full[1][1] = ld_stream16(fs + s1 * row_bf16 + static_cast<size_t>(c2) * 16);
+          L.band[1][1] = ld_stream16(bs + s1 * row_bf16 + static_cast<size_t>(c2) * 16);
+        }
+      }
+    };
+    auto finish = [&](int c) {
+      const int c2 = c + blockDim.x;
+      const bool more = c2 < chunks;
+      const int h0 = c / cph, h1 = c2 / cph;
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        if (r == 1 && !two) break;
+        const size_t drow = static_cast<size_t>(r ? d1 : d0) * row_bf16;
+        st_stream16(qc + drow + static_cast<size_t>(c) * 16, L.q[r][0]);
+        st_stream16(ac + drow + static_cast<size_t>(c) * 16,
+                    downdate_chunk(L.full[r][0], L.band[r][0], s_t[par][r * H + h0],
+                                   s_scale[par][r * H + h0]));
+        if (pc) st_stream16(pc + drow + static_cast<size_t>(c) * 16, nan4);
+        if (more) {
+          st_stream16(qc + drow + static_cast<size_t>(c2) * 16, L.q[r][1]);
+          st_stream16(ac + drow + static_cast<size_t>(c2) * 16,
+                      downdate_chunk(L.full[r][1], L.band[r][1], s_t[par][r * H + h1],
+                                     s_scale[par][r * H + h1]));
+          if (pc) st_stream16(pc + drow + static_cast<size_t>(c2) * 16, nan4);
+        }
+      }
+    };
+
+    const bool first = static_cast<int>(threadIdx.x) < chunks;
+    if (first) issue(threadIdx.x);
+    for (int idx = threadIdx.x; idx < (two ? 2 : 1) * H; idx += blockDim.x) {
+      const int r = idx >= H ? 1 : 0;
+      const int h = idx - r * H;
+      const size_t srow = r ? s1 : s0;
+      const int drow = r ? d1 : d0;
+      float ret, t, scale;
+      downdate_scalars(load_lse(p.src_lse, a.full_lse_dtype, srow * H + h),
+                       __fmul_rn(load_lse(a.band_lse, a.band_lse_dtype, srow * H + h),
+                                 a.band_lse_scale),  // rounded product, as a separate scale op
+                       ret, t, scale);
+      s_t[par][idx] = t;
+      s_scale[par][idx] = scale;
+      lc[static_cast<size_t>(drow) * H + h] = unmatchable ? -INFINITY : ret;
+    }
+    __syncthreads();
+    if (first) finish(threadIdx.x);
+    for (int c = threadIdx.x + 2 * blockDim.x; c < chunks; c += 2 * blockDim.x) {
+      issue(c);
+      finish(c);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------
+// Sink-exclusive build (MAC_B200_SINK_EXCLUDE).
+//
+// A ring row must cover [min(F, E), E).  The prefill producers give the state
+// of [0, pos] and of the trailing window [E, pos]; what is left to remove is
+// the row's attention over the sink tokens [0, F), which nobody has computed.
+// It is a small dense problem -- 16 query rows x F <= 128 keys x D = 128 per
+// warp tile -- done here on the tensor cores (mma.sync m16n8k16, bf16 in, fp32
+// accumulate) straight from shared memory, inside the pass that also streams
+// the row through the two downdates into the ring.  The kernel stays bound by
+// the HBM stream of the rows, the sink K/V of a (request, KV head) are read
+// once per CTA.
+//
+// CTA = (slice of a request's ring rows, one KV head); 8 independent warps.  A
+// warp tile is 16 MMA rows = 16/G consecutive tokens x the G query heads of the
+// KV head.  Per tile the warp
+//   1. cp.asyncs its q_post, q_pre, full and band rows into its own staging,
+//   2. S = Q K^T over the sink keys, softmax (log2 domain), O = P V,
+//   3. works out both downdates' scalars per row,
+//   4. parks the normalised sink state in shared memory and streams
+//      ((full - t1*band)*s1 - t2*sink)*s2 to the ring in 16-byte chunks.
+constexpr int kSxD = 128;
+constexpr int kSxRowBytes = kSxD * 2;
+constexpr int kSxMaxF = 128;
+constexpr int kSxWarps = 8;
+constexpr int kSxThreads = kSxWarps * 32;
+constexpr int kSxSinkStride = 136;                     // floats per parked sink row
+constexpr int kSxRegionA = 16 * kSxSinkStride * 4;     // q_post + q_pre staging, then the sink state
+constexpr int kSxRegionRows = 16 * kSxRowBytes;        // one staged 16-row tensor
+constexpr int kSxWarpBytes = kSxRegionA + 2 * kSxRegionRows + 16 * 16;
+constexpr int kSxKvBytes = 2 * kSxMaxF * kSxRowBytes;
+constexpr int kSxSmemBytes = kSxKvBytes + kSxWarps * kSxWarpBytes;
+static_assert(kSxRegionA >= 2 * kSxRegionRows, "q_post and q_pre staging must fit region A");
+
+__device__ __forceinline__ uint32_t sx_smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void sx_cp_async16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src),
+               "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void sx_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void sx_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
+}
+__device__ __forceinline__ void sx_ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1,
+                                               uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void sx_ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1,
+                                                     uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+// D(16x8,f32) += A(16x16,bf16,row) * B(16x8,bf16,col)
+__device__ __forceinline__ void sx_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                       uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float sx_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// grid = (slices, Hkv, B)
+__global__ void __launch_bounds__(kSxThreads, 1)
+prefill_sink_exclusive_ring_kernel(const MacB200PrefillBuildArgs a) {
+  extern __shared__ __align__(128) uint8_t sx_smem[];
+  const MacB200PrefillArgs& p = a.ring;
+  const RowSpan sp = row_span(p, blockIdx.z);
+  if (!sp.ok) return;
+  if (sp.req >= a.req_to_token_rows) return;
+  const int H = p.H, Hkv = a.Hkv, G = H / Hkv;
+  const int kh = blockIdx.y;
+  const int F = a.front_sink_tokens;
+  const int nkb = (F + 15) >> 4;  // 16-key blocks
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int quad = lane & 3, rlo = lane >> 2, rhi = rlo + 8;
+
+  // ---- sink K/V of this (request, KV head) -> shared memory, swizzled rows
+  uint8_t* ks = sx_smem;
+  uint8_t* vs = sx_smem + kSxMaxF * kSxRowBytes;
+  {
+    const int32_t* table = a.req_to_token + static_cast<int64_t>(sp.req) * a.req_to_token_stride;
+    const char* kb = static_cast<const char*>(a.k_buffer) + static_cast<int64_t>(kh) * kSxRowBytes;
+    const char* vb = static_cast<const char*>(a.v_buffer) + static_cast<int64_t>(kh) * kSxRowBytes;
+    const int64_t tok_stride = static_cast<int64_t>(Hkv) * kSxRowBytes;
+    for (int task = tid; task < nkb * 16 * 16; task += kSxThreads) {
+      const int j = task >> 4, c = task & 15;
+      int64_t tok = -1;
+      if (j < F && j < a.req_to_token_stride) tok = table[j];
+      const bool ok = tok >= 0 && tok < a.kv_tokens;
+      const int64_t off = (ok ? tok : 0) * tok_stride + c * 16;
+      const uint32_t dst = j * kSxRowBytes + ((c ^ (j & 7)) << 4);
+      sx_cp_async16(sx_smem_u32(ks) + dst, kb + off, ok ? 16 : 0);
+      sx_cp_async16(sx_smem_u32(vs) + dst, vb + off, ok ? 16 : 0);
+    }
+    sx_commit();
+    sx_wait<0>();
+    __syncthreads();
+  }
+
+  uint8_t* wbase = sx_smem + kSxKvBytes + warp * kSxWarpBytes;
+  uint8_t* regA = wbase;                           // q_post rows | q_pre rows, later the sink state
+  uint8_t* fullS = wbase + kSxRegionA;
+  uint8_t* bandS = fullS + kSxRegionRows;
+  float4* scal = reinterpret_cast<float4*>(bandS + kSxRegionRows);  // per row: t1, s1, t2, s2 (<0: empty)
+  const uint32_t regA_u32 = sx_smem_u32(regA), full_u32 = sx_smem_u32(fullS),
+                 band_u32 = sx_smem_u32(bandS);
+  const uint32_t ks_u32 = sx_smem_u32(ks), vs_u32 = sx_smem_u32(vs);
+
+  const int TG = 16 / G;                            // tokens per warp tile
+  const int ntiles = (sp.keep + TG - 1) / TG;
+  const size_t row_bf16 = static_cast<size_t>(H) * kSxRowBytes;
+  const char* qpost = static_cast<const char*>(a.q_post);
+  const char* qpre = static_cast<const char*>(p.src_q);
+  const char* fsrc = static_cast<const char*>(p.src_attn);
+  const char* bsrc = static_cast<const char*>(a.band_attn);
+  char* qc = static_cast<char*>(p.q_cache) + static_cast<size_t>(sp.req) * p.M * row_bf16;
+  char* ac = static_cast<char*>(p.attn_cache) + static_cast<size_t>(sp.req) * p.M * row_bf16;
+  char* pc = p.q_post_cache
+                 ? static_cast<char*>(p.q_post_cache) + static_cast<size_t>(sp.req) * p.M * row_bf16
+                 : nullptr;
+  float* lc = p.lse_cache + static_cast<size_t>(sp.req) * p.M * H;
+  const float scale_log2 = a.sm_scale * 1.4426950408889634f;
+  const int64_t pos0 = static_cast<int64_t>(p.request_length_by_batch
+                                                ? p.request_length[blockIdx.z]
+                                                : p.request_length[sp.req]);
+  const int64_t pos_base = (pos0 < 0 ? 0 : pos0) + sp.start;
+  const uint32_t nanw = 0x7fc07fc0u;
+  const uint4 nan4 = make_uint4(nanw, nanw, nanw, nanw);
+
+  for (int tile = blockIdx.x * kSxWarps + warp; tile < ntiles; tile += gridDim.x * kSxWarps) {
+    const int i0 = tile * TG;
+    // geometry of MMA row r: token i0 + r / G, head kh * G + r % G
+    auto tok_of = [&](int r) { return i0 + r / G; };
+    auto src_off = [&](int r) {   // byte offset of the row in a [rows, H, D] tensor
+      return (static_cast<size_t>(sp.base_off + sp.start + tok_of(r)) * H + kh * G + (r % G)) *
+             kSxRowBytes;
+    };
+    auto dst_off = [&](int r) {   // byte offset of the row in this request's ring
+      int d = sp.base_dest + tok_of(r);
+      if (d >= p.M) d -= p.M;
+      return (static_cast<size_t>(d) * H + kh * G + (r % G)) * kSxRowBytes;
+    };
+
+    // ---- 1. stage the tile: lane owns chunk (lane & 15) of rows 2j + (lane >> 4)
+    const int c = lane & 15;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int r = 2 * j + (lane >> 4);
+      const bool ok = tok_of(r) < sp.keep;
+      const size_t so = ok ? src_off(r) + c * 16 : 0;
+      sx_cp_async16(regA_u32 + r * kSxRowBytes + ((c ^ (r & 7)) << 4), qpost + so, ok ? 16 : 0);
+      sx_cp_async16(regA_u32 + kSxRegionRows + r * kSxRowBytes + c * 16, qpre + so, ok ? 16 : 0);
+    }
+    sx_commit();
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int r = 2 * j + (lane >> 4);
+      const bool ok = tok_of(r) < sp.keep;
+      const size_t so = ok ? src_off(r) + c * 16 : 0;
+      sx_cp_async16(full_u32 + r * kSxRowBytes + c * 16, fsrc + so, ok ? 16 : 0);
+      sx_cp_async16(band_u32 + r * kSxRowBytes + c * 16, bsrc + so, ok ? 16 : 0);
+    }
+    sx_commit();
+    sx_wait<1>();
+    __syncwarp();
+
+    // q_pre rows go to the ring as they are; the NaN stamp of q_post_cache too
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int r = 2 * j + (lane >> 4);
+      if (tok_of(r) < sp.keep) {
+        const uint4 v = *reinterpret_cast<const uint4*>(regA + kSxRegionRows + r * kSxRowBytes + c * 16);
+        const size_t d = dst_off(r) + c * 16;
+        st_stream16(qc + d, v);
+        if (pc) st_stream16(pc + d, nan4);
+      }
+    }
+
+    // ---- 2. S = Q K^T, softmax, O = P V
+    uint32_t qa[8][4];
+    {
+      const int mi = lane >> 3;
+      const int r = ((mi & 1) << 3) + (lane & 7);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        const int chunk = 2 * kk + (mi >> 1);
+        sx_ldmatrix_x4(regA_u32 + r * kSxRowBytes + ((chunk ^ (r & 7)) << 4), qa[kk][0], qa[kk][1],
+                       qa[kk][2], qa[kk][3]);
+      }
+    }
+    float s[8][2][4];
+#pragma unroll
+    for (int kb = 0; kb < 8; ++kb) {
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) s[kb][nb][0] = s[kb][nb][1] = s[kb][nb][2] = s[kb][nb][3] = 0.f;
+      if (kb < nkb) {
+        const int mi = lane >> 3;
+        const int r = kb * 16 + ((mi >> 1) << 3) + (lane & 7);
+        const uint32_t row_addr = ks_u32 + r * kSxRowBytes;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const int chunk = 2 * kk + (mi & 1);
+          uint32_t b0, b1, b2, b3;
+          sx_ldmatrix_x4(row_addr + ((chunk ^ (r & 7)) << 4), b0, b1, b2, b3);
+          sx_mma(s[kb][0], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], b0, b1);
+          sx_mma(s[kb][1], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], b2, b3);
+        }
+      }
+    }
+    float m_lo = -INFINITY, m_hi = -INFINITY;
+#pragma unroll
+    for (int kb = 0; kb < 8; ++kb) {
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = kb * 16 + nb * 8 + quad * 2 + (e & 1);
+          const float v = key < F ? s[kb][nb][e] * scale_log2 : -INFINITY;
+          s[kb][nb][e] = v;
+          if (e < 2) m_lo = fmaxf(m_lo, v); else m_hi = fmaxf(m_hi, v);
+        }
+      }
+    }
+    m_lo = fmaxf(m_lo, __shfl_xor_sync(0xffffffffu, m_lo, 1));
+    m_lo = fmaxf(m_lo, __shfl_xor_sync(0xffffffffu, m_lo, 2));
+    m_hi = fmaxf(m_hi, __shfl_xor_sync(0xffffffffu, m_hi, 1));
+    m_hi = fmaxf(m_hi, __shfl_xor_sync(0xffffffffu, m_hi, 2));
+    const float mu_lo = m_lo == -INFINITY ? 0.f : m_lo, mu_hi = m_hi == -INFINITY ? 0.f : m_hi;
+    float sum_lo = 0.f, sum_hi = 0.f;
+    uint32_t pa[8][4];
+#pragma unroll
+    for (int kb = 0; kb < 8; ++kb) {
+      float e[2][4];
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) {
+        e[nb][0] = sx_ex2(s[kb][nb][0] - mu_lo);
+        e[nb][1] = sx_ex2(s[kb][nb][1] - mu_lo);
+        e[nb][2] = sx_ex2(s[kb][nb][2] - mu_hi);
+        e[nb][3] = sx_ex2(s[kb][nb][3] - mu_hi);
+        sum_lo += e[nb][0] + e[nb][1];
+        sum_hi += e[nb][2] + e[nb][3];
+      }
+      pa[kb][0] = pack2(e[0][0], e[0][1]);
+      pa[kb][1] = pack2(e[0][2], e[0][3]);
+      pa[kb][2] = pack2(e[1][0], e[1][1]);
+      pa[kb][3] = pack2(e[1][2], e[1][3]);
+    }
+    sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 1);
+    sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 2);
+    sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 1);
+    sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 2);
+    float o[16][4];
+#pragma unroll
+    for (int jj = 0; jj < 16; ++jj) o[jj][0] = o[jj][1] = o[jj][2] = o[jj][3] = 0.f;
+#pragma unroll
+    for (int kb = 0; kb < 8; ++kb) {
+      if (kb < nkb) {
+        const int mi = lane >> 3;
+        const int r = kb * 16 + ((mi & 1) << 3) + (lane & 7);
+        const uint32_t row_addr = vs_u32 + r * kSxRowBytes;
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          const int chunk = 2 * jj + (mi >> 1);
+          uint32_t b0, b1, b2, b3;
+          sx_ldmatrix_x4_trans(row_addr + ((chunk ^ (r & 7)) << 4), b0, b1, b2, b3);
+          sx_mma(o[2 * jj], pa[kb][0], pa[kb][1], pa[kb][2], pa[kb][3], b0, b1);
+          sx_mma(o[2 * jj + 1], pa[kb][0], pa[kb][1], pa[kb][2], pa[kb][3], b2, b3);
+        }
+      }
+    }
+
+    // ---- 3. scalars of both downdates, one quad leader per row pair
+    __syncwarp();   // every lane is done with the staged q rows: region A is free
+    if (quad == 0) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int r = half ? rhi : rlo;
+        if (tok_of(r) >= sp.keep) continue;
+        const int h = kh * G + (r % G);
+        const size_t srow = static_cast<size_t>(sp.base_off + sp.start + tok_of(r));
+        float ret1, t1, s1;
+        downdate_scalars(load_lse(p.src_lse, a.full_lse_dtype, srow * H + h),
+                         __fmul_rn(load_lse(a.band_lse, a.band_lse_dtype, srow * H + h),
+                                   a.band_lse_scale),
+                         ret1, t1, s1);
+        int64_t E = pos_base + tok_of(r) + 1 - a.semantic_pos_ahead;
+        if (E < 0) E = 0;
+        float ret2 = -INFINITY, t2 = 0.f, s2 = -1.f;  // s2 < 0: the row holds the empty state
+        if (E > F) {
+          const float m = half ? m_hi : m_lo, sum = half ? sum_hi : sum_lo;
+          const float lse_sink = (m + log2f(sum)) * 0.6931471805599453f;
+          downdate_scalars(ret1, lse_sink, ret2, t2, s2);
+        }
+        scal[r] = make_float4(t1, s1, t2, s2);
+        int d = sp.base_dest + tok_of(r);
+        if (d >= p.M) d -= p.M;
+        lc[static_cast<size_t>(d) * H + h] = ret2;
+      }
+    }
+    // ---- 4. park the normalised sink state, then stream the rows to the ring
+    {
+      const float inv_lo = sum_lo > 0.f ? 1.f / sum_lo : 0.f;
+      const float inv_hi = sum_hi > 0.f ? 1.f / sum_hi : 0.f;
+      float* plo = reinterpret_cast<float*>(regA) + rlo * kSxSinkStride + quad * 2;
+      float* phi = reinterpret_cast<float*>(regA) + rhi * kSxSinkStride + quad * 2;
+#pragma unroll
+      for (int jj = 0; jj < 16; ++jj) {
+        *reinterpret_cast<float2*>(plo + jj * 8) = make_float2(o[jj][0] * inv_lo, o[jj][1] * inv_lo);
+        *reinterpret_cast<float2*>(phi + jj * 8) = make_float2(o[jj][2] * inv_hi, o[jj][3] * inv_hi);
+      }
+    }
+    sx_wait<0>();
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int r = 2 * j + (lane >> 4);
+      if (tok_of(r) >= sp.keep) continue;
+      const uint4 f4 = *reinterpret_cast<const uint4*>(fullS + r * kSxRowBytes + c * 16);
+      const uint4 b4 = *reinterpret_cast<const uint4*>(bandS + r * kSxRowBytes + c * 16);
+      const float4 k4 = scal[r];
+      const float* sk = reinterpret_cast<const float*>(regA) + r * kSxSinkStride + c * 8;
+      const float4 k0 = *reinterpret_cast<const float4*>(sk);
+      const float4 k1 = *reinterpret_cast<const float4*>(sk + 4);
+      const float sink[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
+      const uint32_t x[4] = {f4.x, f4.y, f4.z, f4.w};
+      const uint32_t y[4] = {b4.x, b4.y, b4.z, b4.w};
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float mid0 = (lo_f(x[i]) - k4.x * lo_f(y[i])) * k4.y;
+        const float mid1 = (hi_f(x[i]) - k4.x * hi_f(y[i])) * k4.y;
+        const float r0 = (mid0 - k4.z * sink[2 * i]) * k4.w;
+        const float r1 = (mid1 - k4.z * sink[2 * i + 1]) * k4.w;
+        w[i] = k4.w < 0.f ? 0u : pack2(r0, r1);
+      }
+      st_stream16(ac + dst_off(r) + c * 16, make_uint4(w[0], w[1], w[2], w[3]));
+    }
+    __syncwarp();   // the next tile's staging overwrites what other lanes just read
+  }
+}
+
+// Runs after every CTA of the build kernel has read L_before (stream order):
+// bumps request_length in the by-request mode and marks the requests ready
+// (mac_prefill_update_cache.cu:262-267 and 374-409).
+__global__ void prefill_build_finish_kernel(const MacB200PrefillBuildArgs a) {
+  const MacB200PrefillArgs& p = a.ring;
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= p.B) return;
+  const int req = p.req_ids[b];
+  if (req < 0 || req >= p.R) return;
+  if (a.ready) {
+    a.cache_epoch[req] = a.request_epoch[req];
+    a.ready[req] = 1;
+  }
+  if (p.request_length_by_batch) return;
+  const int Ni = p.lens[b];
+  if (Ni <= 0 || p.M <= 0) return;
+  const int base_off = p.offsets[b];
+  if (base_off < 0 || base_off + Ni > p.src_rows) return;
+  atomicAdd(&p.request_length[req], Ni);
+}
+
+}  // namespace
+}  // namespace mac_b200
+
+using namespace mac_b200;
+
+extern "C" int mac_b200_prefill_downdate_update_cache(const MacB200PrefillBuildArgs* args,
+                                                      void* stream_v) {
+  MAC_REQUIRE(args != nullptr, "prefill build args must not be null");
+  const MacB200PrefillBuildArgs& a = *args;
+  const MacB200PrefillArgs& p = a.ring;
+  if (p.M <= 0 || p.B <= 0) return MAC_B200_OK;
+  MAC_REQUIRE(p.R > 0, "R must be > 0");
+  MAC_REQUIRE(p.H > 0 && p.D > 0, "num_heads and head_dim must be > 0");
+  MAC_REQUIRE(p.q_cache && p.attn_cache && p.lse_cache, "ring tensors must not be null");
+  MAC_REQUIRE(p.request_length && p.req_ids && p.offsets && p.lens,
+              "batch metadata must not be null");
+  MAC_REQUIRE(p.src_rows == 0 || (p.src_q && p.src_attn && p.src_lse && a.band_attn && a.band_lse),
+              "source tensors must not be null");
+  MAC_REQUIRE(a.full_lse_dtype >= 0 && a.full_lse_dtype <= 2 && a.band_lse_dtype >= 0 &&
+                  a.band_lse_dtype <= 2,
+              "lse must be float32, bfloat16, or float16");
+  MAC_REQUIRE(a.sink_mode >= MAC_B200_SINK_NONE && a.sink_mode <= MAC_B200_SINK_EXCLUDE,
+              "unknown sink_mode");
+  const bool gate_any = a.ready || a.cache_epoch || a.request_epoch;
+  const bool gate_all = a.ready && a.cache_epoch && a.request_epoch;
+  MAC_REQUIRE(!gate_any || gate_all, "ready, cache_epoch and request_epoch go together");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (a.sink_mode == MAC_B200_SINK_EXCLUDE) {
+    MAC_REQUIRE(a.q_post && a.k_buffer && a.v_buffer && a.req_to_token,
+                "sink-exclusive build needs q_post, k_buffer, v_buffer and req_to_token");
+    MAC_REQUIRE(a.Hkv > 0 && p.H % a.Hkv == 0, "H must be divisible by Hkv");
+    MAC_REQUIRE(a.front_sink_tokens >= 0 && a.semantic_pos_ahead >= 0, "negative F or S");
+    MAC_REQUIRE(a.req_to_token_rows > 0 && a.req_to_token_stride >= a.front_sink_tokens,
+                "req_to_token has fewer columns than front_sink_tokens");
+    const int G = p.H / a.Hkv;
+    if (p.D != kSxD)
+      return fail(MAC_B200_EUNSUPPORTED, "sink-exclusive build supports D=128 only (got %d)", p.D);
+    if (a.front_sink_tokens > kSxMaxF)
+      return fail(MAC_B200_EUNSUPPORTED, "front_sink_tokens=%d exceeds this build's limit of %d",
+                  a.front_sink_tokens, kSxMaxF);
+    if (G > 16 || (16 % G) != 0)
+      return fail(MAC_B200_EUNSUPPORTED, "sink-exclusive build needs a GQA group of 1, 2, 4, 8 or 16");
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(p.q_cache) | reinterpret_cast<uintptr_t>(p.attn_cache) |
+                           reinterpret_cast<uintptr_t>(p.q_post_cache) | reinterpret_cast<uintptr_t>(p.src_q) |
+                           reinterpret_cast<uintptr_t>(p.src_attn) | reinterpret_cast<uintptr_t>(a.band_attn) |
+                           reinterpret_cast<uintptr_t>(a.q_post) | reinterpret_cast<uintptr_t>(a.k_buffer) |
+                           reinterpret_cast<uintptr_t>(a.v_buffer);
+    MAC_REQUIRE((bits & 15u) == 0, "sink-exclusive build needs 16-byte aligned tensors");
+    int device = 0;
+    MAC_CUDA(cudaGetDevice(&device));
+    // the attribute is per device: set it on every call (cheap, no synchronisation)
+    MAC_CUDA(cudaFuncSetAttribute(prefill_sink_exclusive_ring_kernel,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, kSxSmemBytes));
+    int sms = 148;
+    MAC_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    const int TG = 16 / G;
+    const int max_tiles = ((p.M < 1 ? 1 : p.M) + TG - 1) / TG;
+    const int pairs = p.B * a.Hkv;
+    int slices = (4 * sms + pairs - 1) / pairs;               // about four CTAs per SM in total
+    const int max_slices = (max_tiles + kSxWarps - 1) / kSxWarps;
+    if (slices > max_slices) slices = max_slices;
+    if (slices < 1) slices = 1;
+    dim3 grid(slices, a.Hkv, p.B);
+    prefill_sink_exclusive_ring_kernel<<<grid, kSxThreads, kSxSmemBytes, stream>>>(a);
+    MAC_CUDA(cudaGetLastError());
+    g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+    if (!p.request_length_by_batch || a.ready) {
+      prefill_build_finish_kernel<<<(p.B + 127) / 128, 128, 0, stream>>>(a);
+      MAC_CUDA(cudaGetLastError());
+      g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+    }
+    return MAC_B200_OK;
+  }
+  int per_req = (p.M + 1) / 2 < 64 ? (p.M + 1) / 2 : 64;
+  if (p.B >= 32 && per_req > 32) per_req = 32;
+  if (per_req < 1) per_req = 1;
+  dim3 grid(per_req, p.B);
+  prefill_downdate_ring_kernel<<<grid, kBuildThreads, 0, stream>>>(a);
+  MAC_CUDA(cudaGetLastError());
+  g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+  if (!p.request_length_by_batch || a.ready) {
+    prefill_build_finish_kernel<<<(p.B + 127) / 128, 128, 0, stream>>>(a);
+    MAC_CUDA(cudaGetLastError());
+    g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+  }
+  return MAC_B200_OK;
+}

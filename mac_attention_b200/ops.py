@@ -422,6 +422,118 @@ def mac_prefill_update_cache(
         _abi.check(lib.mac_b200_prefill_update_cache(C.byref(a), _stream_ptr(q_cache.device)))
 
 
+SINK_NONE, SINK_UNMATCHABLE, SINK_EXCLUDE = 0, 1, 2
+
+
+def mac_prefill_downdate_update_cache(
+    q_cache, attn_cache, lse_cache, request_length, req_ids, src_q, full_attn, full_lse,
+    band_attn, band_lse, offsets, lens, capacity, num_heads, head_dim, q_post_cache=None, *,
+    band_lse_scale=1.0, sink_mode=SINK_NONE, ready=None, cache_epoch=None, request_epoch=None,
+    q_post=None, k_buffer=None, v_buffer=None, req_to_token=None, front_sink_tokens=0,
+    semantic_pos_ahead=0, sm_scale=None,
+) -> None:
+    """One-pass prefill ring build: downdate + ring write + ready mark.
+
+    Equivalent, for the ring, to the reference hook's sequence
+    (``flashinfer_hooks.py:2459-2492``)::
+
+        band_lse = band_lse * band_lse_scale
+        mac_update_then_downdate_bf16_inplace(full_attn, full_lse, band_attn, band_lse)
+        [band_lse = -inf                      if sink_mode == SINK_UNMATCHABLE]
+        mac_prefill_update_cache(..., src_q, band_attn, band_lse, ...)
+        mac_mark_persistent_ready(ready, cache_epoch, request_epoch, req_ids)   # if given
+
+    but only the rows that reach the ring are downdated and ``band_attn`` /
+    ``band_lse`` are left untouched.  ``SINK_EXCLUDE`` additionally removes each
+    row's attention over the front-sink tokens, computed from ``q_post`` and the
+    paged K/V pool, so that prefill rows are matchable under ``front_sink_tokens > 0``.
+    """
+    lib = _abi.load_library()
+    capacity, num_heads, head_dim = int(capacity), int(num_heads), int(head_dim)
+    if capacity <= 0 or req_ids.shape[0] == 0:
+        return
+    for name, t, dt in (("q_cache", q_cache, _BF16), ("attn_cache", attn_cache, _BF16),
+                        ("lse_cache", lse_cache, _F32), ("request_length", request_length, _I32),
+                        ("req_ids", req_ids, _I32), ("lens", lens, _I32),
+                        ("offsets", offsets, _I32), ("src_q", src_q, _BF16),
+                        ("full_attn", full_attn, _BF16), ("band_attn", band_attn, _BF16),
+                        ("full_lse", full_lse, None), ("band_lse", band_lse, None)):
+        _req(t.is_cuda, f"{name} must be CUDA")
+        _req(t.is_contiguous(), f"{name} must be contiguous")
+        if dt is None:
+            _req(t.dtype in _LSE_DTYPES, f"{name} must be float32, bfloat16, or float16; got {t.dtype}")
+        else:
+            _req(t.dtype == dt, f"{name} has wrong dtype")
+    R = q_cache.shape[0]
+    _req(R > 0, "R must be > 0")
+    _req(q_cache.dim() == 4, "q_cache must be [R,M,H,D]")
+    _req(q_cache.shape[1] == capacity, "capacity (M) mismatch")
+    _req(q_cache.shape[2] == num_heads, "num_heads (H) mismatch")
+    _req(q_cache.shape[3] == head_dim, "head_dim (D) mismatch")
+    _req(attn_cache.shape == q_cache.shape, "attn_cache must match q_cache")
+    _req(tuple(lse_cache.shape) == (R, capacity, num_heads), "lse_cache shape mismatch")
+    _req(src_q.dim() == 3 and src_q.shape[1] == num_heads and src_q.shape[2] == head_dim,
+         "src_q must be [sumN,H,D]")
+    _req(full_attn.shape == src_q.shape, "full_attn must match src_q")
+    _req(band_attn.shape == src_q.shape, "band_attn must match src_q")
+    for name, t in (("full_lse", full_lse), ("band_lse", band_lse)):
+        _req(t.dim() == 2 and tuple(t.shape) == tuple(src_q.shape[:2]), f"{name} must be [sumN,H]")
+    B = req_ids.shape[0]
+    _req(offsets.shape[0] == B + 1, "offsets must be [B+1]")
+    _req(lens.shape[0] == B, "lens must be [B]")
+    _req(request_length.shape[0] in (R, B), "request_length must be [R] or [B]")
+    sink_mode = int(sink_mode)
+    _req(sink_mode in (SINK_NONE, SINK_UNMATCHABLE, SINK_EXCLUDE), "unknown sink_mode")
+    a = _abi.MacB200PrefillBuildArgs()
+    r = a.ring
+    r.R, r.M, r.H, r.D, r.B = R, capacity, num_heads, head_dim, B
+    r.src_rows = src_q.shape[0]
+    r.request_length_by_batch = 1 if request_length.shape[0] == B else 0
+    r.q_cache, r.attn_cache, r.lse_cache = (q_cache.data_ptr(), attn_cache.data_ptr(),
+                                            lse_cache.data_ptr())
+    r.q_post_cache = None
+    if q_post_cache is not None and q_post_cache.numel() > 0:
+        _req(q_post_cache.is_cuda and q_post_cache.is_contiguous(), "q_post_cache must be contiguous CUDA")
+        _req(q_post_cache.dtype == _BF16, "q_post_cache has wrong dtype")
+        _req(q_post_cache.shape == q_cache.shape, "q_post_cache must match q_cache")
+        r.q_post_cache = q_post_cache.data_ptr()
+    r.request_length, r.req_ids = request_length.data_ptr(), req_ids.data_ptr()
+    r.src_q, r.src_attn, r.src_lse = src_q.data_ptr(), full_attn.data_ptr(), full_lse.data_ptr()
+    r.offsets, r.lens = offsets.data_ptr(), lens.data_ptr()
+    a.band_attn, a.band_lse = band_attn.data_ptr(), band_lse.data_ptr()
+    a.full_lse_dtype, a.band_lse_dtype = _LSE_DTYPES[full_lse.dtype], _LSE_DTYPES[band_lse.dtype]
+    a.band_lse_scale = float(band_lse_scale)
+    a.sink_mode = sink_mode
+    if ready is not None or cache_epoch is not None or request_epoch is not None:
+        _req(ready is not None and cache_epoch is not None and request_epoch is not None,
+             "ready, cache_epoch and request_epoch go together")
+        _check_gate(ready, cache_epoch, request_epoch, req_ids)
+        _req(ready.shape[0] == R, "ready must be [R]")
+        a.ready, a.cache_epoch, a.request_epoch = (ready.data_ptr(), cache_epoch.data_ptr(),
+                                                   request_epoch.data_ptr())
+    if sink_mode == SINK_EXCLUDE:
+        for name, t in (("q_post", q_post), ("k_buffer", k_buffer), ("v_buffer", v_buffer),
+                        ("req_to_token", req_to_token)):
+            _req(t is not None, f"{name} is required for SINK_EXCLUDE")
+            _req(t.is_cuda and t.is_contiguous(), f"{name} must be contiguous CUDA")
+        _req(q_post.dtype == _BF16 and q_post.shape == src_q.shape, "q_post must match src_q")
+        _req(k_buffer.dtype == _BF16 and v_buffer.dtype == _BF16, "k_buffer / v_buffer must be bfloat16")
+        _req(k_buffer.dim() == 3 and k_buffer.shape[2] == head_dim, "k_buffer must be [T,Hkv,D]")
+        _req(v_buffer.shape == k_buffer.shape, "v_buffer must match k_buffer")
+        _req(num_heads % k_buffer.shape[1] == 0, "num_heads must be divisible by Hkv")
+        _req(req_to_token.dtype == _I32 and req_to_token.dim() == 2, "req_to_token must be int32 [rows,cols]")
+        _req(int(front_sink_tokens) >= 0 and int(semantic_pos_ahead) >= 0, "negative F or S")
+        a.Hkv = k_buffer.shape[1]
+        a.front_sink_tokens, a.semantic_pos_ahead = int(front_sink_tokens), int(semantic_pos_ahead)
+        a.req_to_token_rows, a.req_to_token_stride = req_to_token.shape
+        a.sm_scale = float(head_dim ** -0.5 if sm_scale is None else sm_scale)
+        a.kv_tokens = k_buffer.shape[0]
+        a.q_post, a.k_buffer, a.v_buffer = q_post.data_ptr(), k_buffer.data_ptr(), v_buffer.data_ptr()
+        a.req_to_token = req_to_token.data_ptr()
+    with torch.cuda.device(q_cache.device):
+        _abi.check(lib.mac_b200_prefill_downdate_update_cache(C.byref(a), _stream_ptr(q_cache.device)))
+
+
 def _check_gate(ready, cache_epoch, request_epoch, req_ids) -> None:
     for name, t, dt in (("ready", ready, torch.bool), ("cache_epoch", cache_epoch, _I64),
                         ("request_epoch", request_epoch, _I64), ("req_ids", req_ids, _I32)):

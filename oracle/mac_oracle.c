@@ -28,6 +28,7 @@
 #include <limits.h>
 #include <pthread.h>
 #include <stdatomic.h>
+#include <stddef.h>
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
@@ -765,6 +766,10 @@ ORACLE_API float mac_oracle_threshold_distance(float threshold, int D) {
   return threshold_distance(&a);
 }
 ORACLE_API int mac_oracle_abi_struct_size(void) { return (int)sizeof(MacB200DecodeArgs); }
+ORACLE_API int mac_oracle_build_struct_size(void) { return (int)sizeof(MacB200PrefillBuildArgs); }
+ORACLE_API int mac_oracle_build_struct_tail_offset(void) {
+  return (int)offsetof(MacB200PrefillBuildArgs, req_to_token);
+}
 
 /* ----------------------------------------------- decode RoPE + q preserve -- */
 /* attention/src/mac_attention/integrations/sglang/csrc/mac_decode_rope_preserve.cu:35-156.
@@ -816,31 +821,151 @@ ORACLE_API int mac_oracle_decode_rope_preserve(const MacB200RopeArgs* a) {
 /* ------------------------------------------------------ prefill downdate -- */
 /* attention/src/mac_attention/integrations/sglang/csrc/mac_merge_downdate_cache.cu:116-288,
  * float32 LSE only (the element types only change how the scalar is loaded). */
+static void downdate_scalars_f(float l1, float l2, float* ret, float* t, float* scale) {
+  const float diff = l2 - l1;
+  const float em1 = expm1f(diff);
+  const int last_block = fabsf(em1) <= 1e-7f;
+  const int invalid = (diff > 0.0f) && !last_block;
+  if (last_block) {
+    *ret = -INFINITY; *t = 0.f; *scale = 0.f;
+  } else if (invalid) {
+    *ret = l1; *t = 0.f; *scale = 1.f;
+  } else {
+    const float one_minus = 1.f - expf(diff);
+    *ret = l1 + logf(fmaxf(one_minus + 1e-7f, 1e-30f));
+    *t = expf(diff);
+    *scale = expf(l1 - *ret);
+  }
+}
+
 ORACLE_API int mac_oracle_update_then_downdate(const uint16_t* out1, const float* lse1,
                                                uint16_t* out2, float* lse2, int64_t rows,
                                                int32_t D) {
   for (int64_t r = 0; r < rows; ++r) {
-    const float l1 = lse1[r], l2 = lse2[r];
-    const float diff = l2 - l1;
-    const float em1 = expm1f(diff);
-    const int last_block = fabsf(em1) <= 1e-7f;
-    const int invalid = (diff > 0.0f) && !last_block;
     float ret, t, scale;
-    if (last_block) {
-      ret = -INFINITY; t = 0.f; scale = 0.f;
-    } else if (invalid) {
-      ret = l1; t = 0.f; scale = 1.f;
-    } else {
-      const float one_minus = 1.f - expf(diff);
-      ret = l1 + logf(fmaxf(one_minus + 1e-7f, 1e-30f));
-      t = expf(diff);
-      scale = expf(l1 - ret);
-    }
+    downdate_scalars_f(lse1[r], lse2[r], &ret, &t, &scale);
     for (int d = 0; d < D; ++d) {
       const float o = (bf16_to_f32(out1[r * D + d]) - t * bf16_to_f32(out2[r * D + d])) * scale;
       out2[r * D + d] = f32_to_bf16(o);
     }
     lse2[r] = ret;
   }
+  return 0;
+}
+
+/* ------------------------------------------------ one-pass prefill build -- */
+/* The ring contents the reference hook's operator sequence leaves
+ * (attention/src/mac_attention/integrations/sglang/flashinfer_hooks.py:2459-2492:
+ * band-LSE scale, downdate, ring copy, ready mark; -inf LSE under front sink,
+ * 2205-2215), restated per ring row; float32 LSE inputs only.
+ * MAC_B200_SINK_EXCLUDE has no reference implementation: it restates the
+ * invariant the reference's comment gives -- a ring row covers exactly
+ * [min(F, E), E) -- by removing the row's attention over the sink tokens
+ * [0, min(F, E)), evaluated here in double precision, with a second downdate;
+ * rows with E <= F hold the empty state (0, -inf), as decode-written rows do
+ * (DEC.cu:4485-4497). */
+typedef struct {
+  const MacB200PrefillBuildArgs* a;
+  int b, req, start, keep, base_off, base_dest, L;
+} BuildCtx;
+
+static void build_row_item(void* ctx, int i) {
+  const BuildCtx* c = (const BuildCtx*)ctx;
+  const MacB200PrefillBuildArgs* a = c->a;
+  const MacB200PrefillArgs* p = &a->ring;
+  const int H = p->H, D = p->D;
+  int dest = c->base_dest + i;
+  if (dest >= p->M) dest -= p->M;
+  const size_t src = (size_t)(c->base_off + c->start + i);
+  const size_t dst = (size_t)c->req * p->M + dest;
+  const uint16_t* full = (const uint16_t*)p->src_attn + src * H * D;
+  const uint16_t* band = (const uint16_t*)a->band_attn + src * H * D;
+  uint16_t* orow = (uint16_t*)p->attn_cache + dst * H * D;
+  memcpy((uint16_t*)p->q_cache + dst * H * D, (const uint16_t*)p->src_q + src * H * D,
+         (size_t)H * D * 2);
+  if (p->q_post_cache) {
+    uint16_t* r = (uint16_t*)p->q_post_cache + dst * H * D;
+    for (int e = 0; e < H * D; ++e) r[e] = 0x7fc0;
+  }
+  const int64_t pos = (int64_t)c->L + c->start + i;
+  int64_t E = pos + 1 - a->semantic_pos_ahead;
+  if (E < 0) E = 0;
+  const int F = a->front_sink_tokens;
+  double* osink = (double*)malloc(sizeof(double) * D);
+  double* sc = (double*)malloc(sizeof(double) * (F > 0 ? F : 1));
+  for (int h = 0; h < H; ++h) {
+    float ret, t, scale;
+    downdate_scalars_f(((const float*)p->src_lse)[src * H + h],
+                       ((const float*)a->band_lse)[src * H + h] * a->band_lse_scale, &ret, &t,
+                       &scale);
+    if (a->sink_mode != MAC_B200_SINK_EXCLUDE) {
+      for (int d = 0; d < D; ++d)
+        orow[h * D + d] = f32_to_bf16(
+            (bf16_to_f32(full[h * D + d]) - t * bf16_to_f32(band[h * D + d])) * scale);
+      p->lse_cache[dst * H + h] = a->sink_mode == MAC_B200_SINK_UNMATCHABLE ? -INFINITY : ret;
+      continue;
+    }
+    if (E <= F) {
+      for (int d = 0; d < D; ++d) orow[h * D + d] = 0;
+      p->lse_cache[dst * H + h] = -INFINITY;
+      continue;
+    }
+    const int kh = h / (H / a->Hkv);
+    const uint16_t* q = (const uint16_t*)a->q_post + (src * H + h) * D;
+    double m = -INFINITY;
+    for (int j = 0; j < F; ++j) {
+      const int64_t tok = a->req_to_token[(int64_t)c->req * a->req_to_token_stride + j];
+      const uint16_t* k = (const uint16_t*)a->k_buffer + (tok * a->Hkv + kh) * D;
+      double dot = 0.0;
+      for (int d = 0; d < D; ++d) dot += (double)bf16_to_f32(q[d]) * (double)bf16_to_f32(k[d]);
+      sc[j] = dot * (double)a->sm_scale;
+      if (sc[j] > m) m = sc[j];
+    }
+    double sum = 0.0;
+    for (int d = 0; d < D; ++d) osink[d] = 0.0;
+    for (int j = 0; j < F; ++j) {
+      const int64_t tok = a->req_to_token[(int64_t)c->req * a->req_to_token_stride + j];
+      const uint16_t* v = (const uint16_t*)a->v_buffer + (tok * a->Hkv + kh) * D;
+      const double w = exp(sc[j] - m);
+      sum += w;
+      for (int d = 0; d < D; ++d) osink[d] += w * (double)bf16_to_f32(v[d]);
+    }
+    const float lse_sink = (float)(m + log(sum));
+    float ret2, t2, scale2;
+    downdate_scalars_f(ret, lse_sink, &ret2, &t2, &scale2);
+    for (int d = 0; d < D; ++d) {
+      const float mid = (bf16_to_f32(full[h * D + d]) - t * bf16_to_f32(band[h * D + d])) * scale;
+      orow[h * D + d] = f32_to_bf16((mid - t2 * (float)(osink[d] / sum)) * scale2);
+    }
+    p->lse_cache[dst * H + h] = ret2;
+  }
+  free(sc);
+  free(osink);
+}
+
+ORACLE_API int mac_oracle_prefill_build(const MacB200PrefillBuildArgs* a) {
+  const MacB200PrefillArgs* p = &a->ring;
+  if (p->M <= 0 || p->B <= 0) return 0;
+  for (int b = 0; b < p->B; ++b) {
+    BuildCtx c;
+    c.a = a;
+    c.b = b;
+    c.req = p->req_ids[b];
+    const int Ni = p->lens[b];
+    if (Ni <= 0) continue;
+    if (c.req < 0 || c.req >= p->R) continue;
+    c.start = Ni > p->M ? Ni - p->M : 0;
+    c.keep = Ni - c.start;
+    c.base_off = p->offsets[b];
+    if (c.base_off < 0 || c.base_off + Ni > p->src_rows) continue;
+    c.L = p->request_length_by_batch ? p->request_length[b] : p->request_length[c.req];
+    if (c.L < 0) c.L = 0;
+    c.base_dest = (int)(((int64_t)c.L + c.start) % p->M);
+    parallel_for(c.keep, build_row_item, &c);
+    if (!p->request_length_by_batch) p->request_length[c.req] += Ni;
+  }
+  if (a->ready)
+    mac_oracle_mark_persistent_ready(a->ready, a->cache_epoch, a->request_epoch, p->req_ids, p->B,
+                                     p->R);
   return 0;
 }

@@ -249,6 +249,46 @@ def update_then_downdate(out1, lse1, out2, lse2) -> None:
     fn(_p(out1), _p(lse1), _p(out2), _p(lse2), out1.shape[0] * out1.shape[1], out1.shape[2])
 
 
+def prefill_build(q_cache, attn_cache, lse_cache, request_length, req_ids, src_q, full_attn,
+                  full_lse, band_attn, band_lse, offsets, lens, capacity, num_heads, head_dim,
+                  q_post_cache=None, *, band_lse_scale=1.0, sink_mode=0, ready=None,
+                  cache_epoch=None, request_epoch=None, q_post=None, k_buffer=None, v_buffer=None,
+                  req_to_token=None, front_sink_tokens=0, semantic_pos_ahead=0,
+                  sm_scale=None) -> None:
+    """CPU restatement of the one-pass prefill ring build (float32 LSE inputs)."""
+    if capacity <= 0 or req_ids.shape[0] == 0:
+        return
+    assert full_lse.dtype == torch.float32 and band_lse.dtype == torch.float32
+    a = _abi.MacB200PrefillBuildArgs()
+    r = a.ring
+    r.R, r.M, r.H, r.D, r.B = q_cache.shape[0], capacity, num_heads, head_dim, req_ids.shape[0]
+    r.src_rows = src_q.shape[0]
+    r.request_length_by_batch = 1 if request_length.shape[0] == req_ids.shape[0] else 0
+    r.q_cache, r.attn_cache, r.lse_cache = _p(q_cache), _p(attn_cache), _p(lse_cache)
+    r.q_post_cache = _p(q_post_cache) if q_post_cache is not None and q_post_cache.numel() else None
+    r.request_length, r.req_ids = _p(request_length), _p(req_ids)
+    r.src_q, r.src_attn, r.src_lse = _p(src_q), _p(full_attn), _p(full_lse)
+    r.offsets, r.lens = _p(offsets), _p(lens)
+    a.band_attn, a.band_lse = _p(band_attn), _p(band_lse)
+    a.band_lse_scale, a.sink_mode = float(band_lse_scale), int(sink_mode)
+    keep = []
+    if ready is not None:
+        rd = ready.view(torch.uint8) if ready.dtype == torch.bool else ready
+        keep.append(rd)
+        a.ready, a.cache_epoch, a.request_epoch = _p(rd), _p(cache_epoch), _p(request_epoch)
+    if int(sink_mode) == 2:
+        a.Hkv = k_buffer.shape[1]
+        a.front_sink_tokens, a.semantic_pos_ahead = int(front_sink_tokens), int(semantic_pos_ahead)
+        a.req_to_token_rows, a.req_to_token_stride = req_to_token.shape
+        a.sm_scale = float(head_dim ** -0.5 if sm_scale is None else sm_scale)
+        a.kv_tokens = k_buffer.shape[0]
+        a.q_post, a.k_buffer, a.v_buffer = _p(q_post), _p(k_buffer), _p(v_buffer)
+        a.req_to_token = _p(req_to_token)
+    fn = lib().mac_oracle_prefill_build
+    fn.restype, fn.argtypes = C.c_int, [C.POINTER(_abi.MacB200PrefillBuildArgs)]
+    fn(C.byref(a))
+
+
 def ring_slot_to_pos(past_len, M, slot):
     return lib().mac_oracle_ring_slot_to_pos(past_len, M, slot)
 

@@ -25,7 +25,7 @@ def _declared_functions():
 
 def test_header_functions_are_exported(lib):
     names = _declared_functions()
-    assert len(names) == 13
+    assert len(names) == 14
     for n in names:
         assert hasattr(lib, n), n
     assert sorted(_abi.PROTOTYPES) == names
@@ -42,6 +42,9 @@ def test_struct_layout_matches_c():
     from oracle import mac_oracle as O
 
     assert O.lib().mac_oracle_abi_struct_size() == ctypes.sizeof(_abi.MacB200DecodeArgs)
+    assert O.lib().mac_oracle_build_struct_size() == ctypes.sizeof(_abi.MacB200PrefillBuildArgs)
+    assert (O.lib().mac_oracle_build_struct_tail_offset()
+            == _abi.MacB200PrefillBuildArgs.req_to_token.offset)
 
 
 def test_argument_validation_needs_no_gpu(lib):

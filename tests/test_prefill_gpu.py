@@ -149,3 +149,125 @@ def test_prefill_then_decode_hits_the_prefill_rows():
     assert_decisions_equal(cu, orc, 2)
     assert cu.ws[3][0].sum() == H and (cu.ws[5][0] == 999).all() and cu.ws[3][1].sum() == 0
     assert_outputs_close(cu, orc, orc_case)
+
+
+# --------------------------------------------------------------------------
+# One-pass build: downdate + ring write + ready mark
+# --------------------------------------------------------------------------
+def _build_inputs(R, M, H, D, lens, req_ids, L0, seed, lse_dtypes=(torch.float32, torch.float32)):
+    t = _prefill_inputs(R, M, H, D, lens, req_ids, L0, seed)
+    g = torch.Generator().manual_seed(seed + 100)
+    rows = t["src_q"].shape[0]
+    t["full_attn"] = t.pop("src_attn")
+    full_lse = torch.randn(rows, H, generator=g) + 3.0
+    band_lse = full_lse - torch.rand(rows, H, generator=g) * 4.0 - 0.05
+    if rows >= 4:
+        band_lse[0, 0] = full_lse[0, 0]            # band is the whole prefix -> empty state
+        band_lse[1, 0] = full_lse[1, 0] + 1.0      # inconsistent pair -> keep the full state
+        band_lse[2, 0] = float("-inf")             # empty band
+        band_lse[rows - 1, H - 1] = full_lse[rows - 1, H - 1]
+    t.pop("src_lse")
+    t["full_lse"] = full_lse.to(lse_dtypes[0])
+    t["band_lse"] = band_lse.to(lse_dtypes[1])
+    t["band_attn"] = torch.randn(rows, H, D, generator=g).to(torch.bfloat16)
+    t["ready"] = torch.zeros(R, dtype=torch.bool)
+    t["cache_epoch"] = torch.full((R,), -1, dtype=torch.int64)
+    t["request_epoch"] = torch.arange(R, dtype=torch.int64) + 5
+    return t
+
+
+def _sequential(mod, t, M, H, D, scale, unmatchable):
+    """The reference hook's sequence of operators, on the tensors of ``t`` (modified)."""
+    band_lse = (t["band_lse"].float() * scale).to(t["band_lse"].dtype) if scale != 1.0 else t["band_lse"]
+    mod["downdate"](t["full_attn"], t["full_lse"], t["band_attn"], band_lse)
+    lse32 = band_lse.float()
+    if unmatchable:
+        lse32 = torch.full_like(lse32, float("-inf"))
+    mod["prefill"](t["q_cache"], t["attn_cache"], t["lse_cache"], t["request_length"],
+                   t["req_ids"], t["src_q"], t["band_attn"], lse32.contiguous(), t["offsets"], t["lens"],
+                   M, H, D, t["q_post_cache"])
+    mod["mark"](t["ready"], t["cache_epoch"], t["request_epoch"], t["req_ids"])
+
+
+@pytest.mark.parametrize("spec", [
+    dict(R=6, M=16, H=8, D=128, lens=[5, 40, 0, 16], req_ids=[3, 0, 1, 5], L0=[7, 0, 0, 30, 0, 2]),
+    dict(R=4, M=512, H=32, D=128, lens=[2048, 100, 513], req_ids=[2, 9, 0], L0=[0, 0, 100, 0]),
+    dict(R=3, M=8, H=3, D=20, lens=[9, 3], req_ids=[1, -1], L0=[0, -5, 0]),
+    dict(R=3, M=64, H=40, D=64, lens=[70, 33], req_ids=[2, 0], L0=[11, 0, 50], scale=0.6931471805599453),
+    dict(R=5, M=32, H=4, D=128, lens=[10, 50, 7], req_ids=[4, 2, 0], L0=[3, 64, 9], unmatchable=True),
+    dict(R=2, M=32, H=8, D=128, lens=[40, 20], req_ids=[1, 0], L0=[0, 0],
+         lse_dtypes=(torch.bfloat16, torch.float16)),
+], ids=["small", "qwen_ring", "odd_dims_bad_req", "ln2_scale", "unmatchable", "narrow_lse"])
+def test_prefill_build_matches_the_operator_sequence(spec):
+    ext = load_mac_prefill_update_cache_extension()
+    from mac_attention_b200 import ops
+    M, H, D = spec["M"], spec["H"], spec["D"]
+    scale, unm = spec.get("scale", 1.0), spec.get("unmatchable", False)
+    t = _build_inputs(spec["R"], M, H, D, spec["lens"], spec["req_ids"], spec["L0"], seed=3,
+                      lse_dtypes=spec.get("lse_dtypes", (torch.float32, torch.float32)))
+    # (a) CPU oracle of the sequence (oracle LSE arithmetic is fp32)
+    cpu = {k: v.clone() for k, v in t.items()}
+    cpu["full_lse"], cpu["band_lse"] = cpu["full_lse"].float(), cpu["band_lse"].float()
+    _sequential(dict(downdate=O.update_then_downdate, prefill=O.prefill_update_cache,
+                     mark=O.mark_persistent_ready), cpu, M, H, D, scale, unm)
+    # (b) the same sequence through the separate CUDA operators
+    seq = {k: v.cuda() for k, v in t.items()}
+    _sequential(dict(downdate=ops.mac_update_then_downdate_bf16_inplace,
+                     prefill=ext.mac_prefill_update_cache, mark=ext.mac_mark_persistent_ready),
+                seq, M, H, D, scale, unm)
+    # (c) the one-pass operator
+    one = {k: v.cuda() for k, v in t.items()}
+    band_before = one["band_attn"].clone()
+    ext.mac_prefill_downdate_update_cache(
+        one["q_cache"], one["attn_cache"], one["lse_cache"], one["request_length"], one["req_ids"],
+        one["src_q"], one["full_attn"], one["full_lse"], one["band_attn"], one["band_lse"],
+        one["offsets"], one["lens"], M, H, D, one["q_post_cache"], band_lse_scale=scale,
+        sink_mode=ops.SINK_UNMATCHABLE if unm else ops.SINK_NONE, ready=one["ready"],
+        cache_epoch=one["cache_epoch"], request_epoch=one["request_epoch"])
+    torch.cuda.synchronize()
+    assert torch.equal(one["band_attn"], band_before)
+    narrow = "lse_dtypes" in spec
+    for name in ("q_cache", "q_post_cache", "request_length", "ready", "cache_epoch"):
+        a, b, c = one[name].cpu(), seq[name].cpu(), cpu[name]
+        if a.dtype == torch.bfloat16:
+            a, b, c = a.view(torch.int16), b.view(torch.int16), c.view(torch.int16)
+        assert torch.equal(a, b), name
+        assert torch.equal(a, c), name
+    if not narrow:
+        # same arithmetic as the separate operators: identical bits
+        assert torch.equal(one["attn_cache"].view(torch.int16), seq["attn_cache"].view(torch.int16))
+        assert torch.equal(one["lse_cache"].view(torch.int32), seq["lse_cache"].view(torch.int32))
+    else:
+        # the separate operators round the downdated LSE to its narrow type on the way
+        assert O.rel_l2(one["attn_cache"].float().cpu(), seq["attn_cache"].float().cpu()) <= 2e-3
+    fin_gpu, fin_cpu = torch.isfinite(one["lse_cache"].cpu()), torch.isfinite(cpu["lse_cache"])
+    assert torch.equal(fin_gpu, fin_cpu)
+    both = fin_gpu & fin_cpu
+    assert torch.allclose(one["lse_cache"].cpu()[both], cpu["lse_cache"][both], rtol=1e-4, atol=2e-2 if narrow else 1e-4)
+    assert O.rel_l2(one["attn_cache"].float().cpu(), cpu["attn_cache"].float()) <= 2e-3
+
+
+def test_prefill_build_argument_errors():
+    ext = load_mac_prefill_update_cache_extension()
+    t = {k: v.cuda() for k, v in _build_inputs(2, 4, 2, 128, [3], [0], [0, 0], 0).items()}
+
+    def call(**kw):
+        a = dict(t)
+        a.update(kw)
+        extra = {k: a[k] for k in ("ready", "cache_epoch", "request_epoch") if a.get(k) is not None}
+        ext.mac_prefill_downdate_update_cache(
+            a["q_cache"], a["attn_cache"], a["lse_cache"], a["request_length"], a["req_ids"],
+            a["src_q"], a["full_attn"], a["full_lse"], a["band_attn"], a["band_lse"], a["offsets"],
+            a["lens"], 4, 2, 128, a["q_post_cache"], sink_mode=a.get("sink_mode", 0), **extra)
+
+    with pytest.raises(RuntimeError, match="band_attn must match"):
+        call(band_attn=t["band_attn"][:2].contiguous())
+    with pytest.raises(RuntimeError, match="float32, bfloat16, or float16"):
+        call(band_lse=t["band_lse"].double())
+    with pytest.raises(RuntimeError, match="go together"):
+        call(cache_epoch=None)
+    with pytest.raises(RuntimeError, match="sink_mode"):
+        call(sink_mode=7)
+    call()
+    torch.cuda.synchronize()
+    assert bool(t["ready"][0]) and not bool(t["ready"][1])
