@@ -63,6 +63,10 @@ def parse_args():
     ap.add_argument("--shard", default="request", choices=["request", "kv_head"])
     ap.add_argument("--config4", action="store_true",
                     help="mixed serving step with readiness gating + prefill ring build timing")
+    ap.add_argument("--config4-part", choices=["all", "prefill"], default="all",
+                    help="with --config4: run every row, or only the prefill ring-build rows")
+    ap.add_argument("--prompt-len", type=int, default=32768,
+                    help="with --config4: prompt length of the prefill ring-build rows")
     ap.add_argument("--config4-out", default=str(ROOT / "gpurun_out" / "config4.json"))
     return ap.parse_args()
 
@@ -560,42 +564,44 @@ def run_config4(args):
     ext = load_mac_persistent_decode_extension()
     pre = load_mac_prefill_update_cache_extension()
     batch = args.batch
-    g = torch.Generator().manual_seed(4)
-    ctxs = torch.randint(8192, 126977, (batch,), generator=g).tolist()
-    case = synth.make_decode_case(batch=batch, ctx=0, ctx_list=ctxs, hq=args.hq, hkv=args.hkv,
-                                  capacity=args.capacity, page_size=args.page_size, seed=44,
-                                  device=dev)
-    synth.add_readiness_gate(case, not_ready_fraction=0.2, stale_fraction=0.1, seed=4)
-    ws = make_decode_workspace(batch, args.hq, args.hkv, args.capacity, MAX_CONTEXT, TILE, MTS, SEM,
-                               0, device=dev, partial_dtype=torch.bfloat16)
-    out = torch.empty_like(case.q_post)
-    lse = torch.empty(batch, args.hq, device=dev)
-    scal = scalars(args, 0.8)
+    rows = []
+    if args.config4_part == "all":
+        g = torch.Generator().manual_seed(4)
+        ctxs = torch.randint(8192, 126977, (batch,), generator=g).tolist()
+        case = synth.make_decode_case(batch=batch, ctx=0, ctx_list=ctxs, hq=args.hq, hkv=args.hkv,
+                                      capacity=args.capacity, page_size=args.page_size, seed=44,
+                                      device=dev)
+        synth.add_readiness_gate(case, not_ready_fraction=0.2, stale_fraction=0.1, seed=4)
+        ws = make_decode_workspace(batch, args.hq, args.hkv, args.capacity, MAX_CONTEXT, TILE, MTS, SEM,
+                                   0, device=dev, partial_dtype=torch.bfloat16)
+        out = torch.empty_like(case.q_post)
+        lse = torch.empty(batch, args.hq, device=dev)
+        scal = scalars(args, 0.8)
 
-    def launch():
-        ext.mac_persistent_decode_bf16(
-            case.q_post, case.q_pre, case.k, case.v, case.req_to_token, case.req_ids,
-            case.past_lens, case.out_cache_loc, case.query_cache, case.attn_cache, case.lse_cache,
-            out, lse, *ws, *scal, case.query_cache, case.cache_ready, case.cache_epoch,
-            case.request_epoch)
+        def launch():
+            ext.mac_persistent_decode_bf16(
+                case.q_post, case.q_pre, case.k, case.v, case.req_to_token, case.req_ids,
+                case.past_lens, case.out_cache_loc, case.query_cache, case.attn_cache, case.lse_cache,
+                out, lse, *ws, *scal, case.query_cache, case.cache_ready, case.cache_epoch,
+                case.request_epoch)
 
-    ms, _ = time_graph(launch, args.steps, args.warmup)
-    ab = alg_bytes(ws, batch, args.hq, args.hkv, 0, args.capacity, case.past_lens.cpu().tolist())
-    gated = int(case.meta["gated_off"].sum())
-    # the scan only runs for requests that pass the gate
-    scan = sum(min(args.capacity, c) for c, off in zip(ctxs, case.meta["gated_off"].tolist())
-               if not off) * args.hq * 256
-    total = ab["total"] - ab["scan"] + scan
-    rows = [dict(kind="mixed_decode_step", batch=batch, ctx_min=min(ctxs), ctx_max=max(ctxs),
-                 gated_off_requests=gated, hit=0.8, us=ms * 1e3, alg_gbs=total / (ms * 1e-3) / 1e9,
-                 kv_gb=ab["kv"] / 1e9, non_hit_groups=ab["non_hit_groups"],
-                 full_groups=ab["full_groups"])]
-    print(json.dumps(rows[-1]), flush=True)
-    del case, ws
-    torch.cuda.empty_cache()
+        ms, _ = time_graph(launch, args.steps, args.warmup)
+        ab = alg_bytes(ws, batch, args.hq, args.hkv, 0, args.capacity, case.past_lens.cpu().tolist())
+        gated = int(case.meta["gated_off"].sum())
+        # the scan only runs for requests that pass the gate
+        scan = sum(min(args.capacity, c) for c, off in zip(ctxs, case.meta["gated_off"].tolist())
+                   if not off) * args.hq * 256
+        total = ab["total"] - ab["scan"] + scan
+        rows = [dict(kind="mixed_decode_step", batch=batch, ctx_min=min(ctxs), ctx_max=max(ctxs),
+                     gated_off_requests=gated, hit=0.8, us=ms * 1e3, alg_gbs=total / (ms * 1e-3) / 1e9,
+                     kv_gb=ab["kv"] / 1e9, non_hit_groups=ab["non_hit_groups"],
+                     full_groups=ab["full_groups"])]
+        print(json.dumps(rows[-1]), flush=True)
+        del case, ws
+        torch.cuda.empty_cache()
 
     # prefill ring build: 32K-token prompts, last M rows kept, q_post_cache rows stamped
-    H, D, M, plen = args.hq, DIM, args.capacity, 32768
+    H, D, M, plen = args.hq, DIM, args.capacity, args.prompt_len
     R = batch
     qc = torch.zeros(R, M, H, D, device=dev, dtype=torch.bfloat16)
     ac = torch.zeros_like(qc)
@@ -705,6 +711,11 @@ def run_config4(args):
     del src_q, src_a, src_l, qc, ac, lc, qpc, band_a, full_l, band_l2, q_post_rows, pool_k, pool_v
     torch.cuda.empty_cache()
 
+    if args.config4_part == "prefill":
+        Path(args.config4_out).parent.mkdir(parents=True, exist_ok=True)
+        Path(args.config4_out).write_text(json.dumps(dict(rows=rows, status=ops.query_status(dev)),
+                                                     indent=1))
+        return
     # the producer of the prefill rows: downdate of the last M rows of every prompt
     from mac_attention_b200 import (load_mac_decode_rope_preserve_extension,
                                     load_mac_merge_downdate_cache_extension)

@@ -262,8 +262,7 @@ __device__ __forceinline__ void sx_ldmatrix_x4_trans(uint32_t addr, uint32_t& r0
 // D(16x8,f32) += A(16x16,bf16,row) * B(16x8,bf16,col)
 __device__ __forceinline__ void sx_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                        uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
       "{%8,%9}, {%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -274,15 +273,17 @@ __device__ __forceinline__ float sx_ex2(float x) {
   return y;
 }
 
-// grid = (slices, Hkv, B)
+// grid = (slices, Hkv, B); G = query heads per KV head
+template <int G>
 __global__ void __launch_bounds__(kSxThreads, 1)
 prefill_sink_exclusive_ring_kernel(const MacB200PrefillBuildArgs a) {
   extern __shared__ __align__(128) uint8_t sx_smem[];
+  constexpr int TG = 16 / G;                        // tokens per warp tile
   const MacB200PrefillArgs& p = a.ring;
   const RowSpan sp = row_span(p, blockIdx.z);
   if (!sp.ok) return;
   if (sp.req >= a.req_to_token_rows) return;
-  const int H = p.H, Hkv = a.Hkv, G = H / Hkv;
+  const int H = p.H, Hkv = a.Hkv;
   const int kh = blockIdx.y;
   const int F = a.front_sink_tokens;
   const int nkb = (F + 15) >> 4;  // 16-key blocks
@@ -316,12 +317,11 @@ prefill_sink_exclusive_ring_kernel(const MacB200PrefillBuildArgs a) {
   uint8_t* regA = wbase;                           // q_post rows | q_pre rows, later the sink state
   uint8_t* fullS = wbase + kSxRegionA;
   uint8_t* bandS = fullS + kSxRegionRows;
-  float4* scal = reinterpret_cast<float4*>(bandS + kSxRegionRows);  // per row: t1, s1, t2, s2 (<0: empty)
+  float4* scal = reinterpret_cast<float4*>(bandS + kSxRegionRows);  // per row: A, B, C, empty flag
   const uint32_t regA_u32 = sx_smem_u32(regA), full_u32 = sx_smem_u32(fullS),
                  band_u32 = sx_smem_u32(bandS);
   const uint32_t ks_u32 = sx_smem_u32(ks), vs_u32 = sx_smem_u32(vs);
 
-  const int TG = 16 / G;                            // tokens per warp tile
   const int ntiles = (sp.keep + TG - 1) / TG;
   const size_t row_bf16 = static_cast<size_t>(H) * kSxRowBytes;
   const char* qpost = static_cast<const char*>(a.q_post);
@@ -342,36 +342,36 @@ prefill_sink_exclusive_ring_kernel(const MacB200PrefillBuildArgs a) {
   const uint32_t nanw = 0x7fc07fc0u;
   const uint4 nan4 = make_uint4(nanw, nanw, nanw, nanw);
 
+  // What this lane moves in the 16-byte passes: chunk c of MMA rows 2j + (lane >> 4).
+  // MMA row r = token r / G of the tile, head kh * G + r % G.
+  const int c = lane & 15;
+  const int r_half = lane >> 4;
+  const size_t src_base = static_cast<size_t>(sp.base_off + sp.start) * row_bf16 +
+                          static_cast<size_t>(kh * G) * kSxRowBytes + c * 16;
+  const size_t head_base = static_cast<size_t>(kh * G) * kSxRowBytes + c * 16;
+  const int mi = lane >> 3, l7 = lane & 7;
+
   for (int tile = blockIdx.x * kSxWarps + warp; tile < ntiles; tile += gridDim.x * kSxWarps) {
     const int i0 = tile * TG;
-    // geometry of MMA row r: token i0 + r / G, head kh * G + r % G
-    auto tok_of = [&](int r) { return i0 + r / G; };
-    auto src_off = [&](int r) {   // byte offset of the row in a [rows, H, D] tensor
-      return (static_cast<size_t>(sp.base_off + sp.start + tok_of(r)) * H + kh * G + (r % G)) *
-             kSxRowBytes;
-    };
-    auto dst_off = [&](int r) {   // byte offset of the row in this request's ring
-      int d = sp.base_dest + tok_of(r);
-      if (d >= p.M) d -= p.M;
-      return (static_cast<size_t>(d) * H + kh * G + (r % G)) * kSxRowBytes;
-    };
+    const size_t tile_src = src_base + static_cast<size_t>(i0) * row_bf16;
+    int dbase = sp.base_dest + i0;                  // ring row of the tile's first token
+    if (dbase >= p.M) dbase -= p.M;
 
-    // ---- 1. stage the tile: lane owns chunk (lane & 15) of rows 2j + (lane >> 4)
-    const int c = lane & 15;
+    // ---- 1. stage the tile
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const int r = 2 * j + (lane >> 4);
-      const bool ok = tok_of(r) < sp.keep;
-      const size_t so = ok ? src_off(r) + c * 16 : 0;
+      const int r = 2 * j + r_half;
+      const bool ok = i0 + r / G < sp.keep;
+      const size_t so = ok ? tile_src + static_cast<size_t>(r / G) * row_bf16 + (r % G) * kSxRowBytes : 0;
       sx_cp_async16(regA_u32 + r * kSxRowBytes + ((c ^ (r & 7)) << 4), qpost + so, ok ? 16 : 0);
       sx_cp_async16(regA_u32 + kSxRegionRows + r * kSxRowBytes + c * 16, qpre + so, ok ? 16 : 0);
     }
     sx_commit();
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const int r = 2 * j + (lane >> 4);
-      const bool ok = tok_of(r) < sp.keep;
-      const size_t so = ok ? src_off(r) + c * 16 : 0;
+      const int r = 2 * j + r_half;
+      const bool ok = i0 + r / G < sp.keep;
+      const size_t so = ok ? tile_src + static_cast<size_t>(r / G) * row_bf16 + (r % G) * kSxRowBytes : 0;
       sx_cp_async16(full_u32 + r * kSxRowBytes + c * 16, fsrc + so, ok ? 16 : 0);
       sx_cp_async16(band_u32 + r * kSxRowBytes + c * 16, bsrc + so, ok ? 16 : 0);
     }
@@ -382,154 +382,164 @@ prefill_sink_exclusive_ring_kernel(const MacB200PrefillBuildArgs a) {
     // q_pre rows go to the ring as they are; the NaN stamp of q_post_cache too
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const int r = 2 * j + (lane >> 4);
-      if (tok_of(r) < sp.keep) {
+      const int r = 2 * j + r_half;
+      if (i0 + r / G < sp.keep) {
         const uint4 v = *reinterpret_cast<const uint4*>(regA + kSxRegionRows + r * kSxRowBytes + c * 16);
-        const size_t d = dst_off(r) + c * 16;
-        st_stream16(qc + d, v);
-        if (pc) st_stream16(pc + d, nan4);
+        int d = dbase + r / G;
+        if (d >= p.M) d -= p.M;
+        const size_t doff = static_cast<size_t>(d) * row_bf16 + head_base + (r % G) * kSxRowBytes;
+        st_stream16(qc + doff, v);
+        if (pc) st_stream16(pc + doff, nan4);
       }
     }
 
-    // ---- 2. S = Q K^T, softmax, O = P V
-    uint32_t qa[8][4];
-    {
-      const int mi = lane >> 3;
-      const int r = ((mi & 1) << 3) + (lane & 7);
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {
-        const int chunk = 2 * kk + (mi >> 1);
-        sx_ldmatrix_x4(regA_u32 + r * kSxRowBytes + ((chunk ^ (r & 7)) << 4), qa[kk][0], qa[kk][1],
-                       qa[kk][2], qa[kk][3]);
-      }
-    }
+    // ---- 2. S = Q K^T (k-step outermost: 2 * nkb independent accumulators per step)
     float s[8][2][4];
 #pragma unroll
-    for (int kb = 0; kb < 8; ++kb) {
+    for (int kb = 0; kb < 8; ++kb)
 #pragma unroll
       for (int nb = 0; nb < 2; ++nb) s[kb][nb][0] = s[kb][nb][1] = s[kb][nb][2] = s[kb][nb][3] = 0.f;
-      if (kb < nkb) {
-        const int mi = lane >> 3;
-        const int r = kb * 16 + ((mi >> 1) << 3) + (lane & 7);
-        const uint32_t row_addr = ks_u32 + r * kSxRowBytes;
+    {
+      const uint32_t qrow = regA_u32 + (((mi & 1) << 3) + l7) * kSxRowBytes;
+      const uint32_t krow = ks_u32 + (((mi >> 1) << 3) + l7) * kSxRowBytes;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const int chunk = 2 * kk + (mi & 1);
-          uint32_t b0, b1, b2, b3;
-          sx_ldmatrix_x4(row_addr + ((chunk ^ (r & 7)) << 4), b0, b1, b2, b3);
-          sx_mma(s[kb][0], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], b0, b1);
-          sx_mma(s[kb][1], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], b2, b3);
+      for (int kk = 0; kk < 8; ++kk) {
+        uint32_t q0, q1, q2, q3;
+        sx_ldmatrix_x4(qrow + (((2 * kk + (mi >> 1)) ^ l7) << 4), q0, q1, q2, q3);
+        const uint32_t ksw = ((2 * kk + (mi & 1)) ^ l7) << 4;
+#pragma unroll
+        for (int kb = 0; kb < 8; ++kb) {
+          if (kb < nkb) {
+            uint32_t b0, b1, b2, b3;
+            sx_ldmatrix_x4(krow + kb * 16 * kSxRowBytes + ksw, b0, b1, b2, b3);
+            sx_mma(s[kb][0], q0, q1, q2, q3, b0, b1);
+            sx_mma(s[kb][1], q0, q1, q2, q3, b2, b3);
+          }
         }
       }
+    }
+    // softmax over the F sink keys, log2 domain; keys >= F only exist in the last block
+    if (F & 15) {
+#pragma unroll
+      for (int kb = 0; kb < 8; ++kb)
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            s[kb][nb][e] = kb * 16 + nb * 8 + quad * 2 + (e & 1) >= F ? -INFINITY : s[kb][nb][e];
     }
     float m_lo = -INFINITY, m_hi = -INFINITY;
 #pragma unroll
     for (int kb = 0; kb < 8; ++kb) {
-#pragma unroll
-      for (int nb = 0; nb < 2; ++nb) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int key = kb * 16 + nb * 8 + quad * 2 + (e & 1);
-          const float v = key < F ? s[kb][nb][e] * scale_log2 : -INFINITY;
-          s[kb][nb][e] = v;
-          if (e < 2) m_lo = fmaxf(m_lo, v); else m_hi = fmaxf(m_hi, v);
-        }
+      if (kb < nkb) {
+        m_lo = fmaxf(m_lo, fmaxf(fmaxf(s[kb][0][0], s[kb][0][1]), fmaxf(s[kb][1][0], s[kb][1][1])));
+        m_hi = fmaxf(m_hi, fmaxf(fmaxf(s[kb][0][2], s[kb][0][3]), fmaxf(s[kb][1][2], s[kb][1][3])));
       }
     }
     m_lo = fmaxf(m_lo, __shfl_xor_sync(0xffffffffu, m_lo, 1));
     m_lo = fmaxf(m_lo, __shfl_xor_sync(0xffffffffu, m_lo, 2));
     m_hi = fmaxf(m_hi, __shfl_xor_sync(0xffffffffu, m_hi, 1));
     m_hi = fmaxf(m_hi, __shfl_xor_sync(0xffffffffu, m_hi, 2));
-    const float mu_lo = m_lo == -INFINITY ? 0.f : m_lo, mu_hi = m_hi == -INFINITY ? 0.f : m_hi;
+    // scaled maxima (sm_scale > 0); -inf only when there is no sink key at all
+    const float ms_lo = m_lo == -INFINITY ? 0.f : m_lo * scale_log2;
+    const float ms_hi = m_hi == -INFINITY ? 0.f : m_hi * scale_log2;
     float sum_lo = 0.f, sum_hi = 0.f;
     uint32_t pa[8][4];
 #pragma unroll
     for (int kb = 0; kb < 8; ++kb) {
-      float e[2][4];
+      if (kb < nkb) {
+        float e[2][4];
 #pragma unroll
-      for (int nb = 0; nb < 2; ++nb) {
-        e[nb][0] = sx_ex2(s[kb][nb][0] - mu_lo);
-        e[nb][1] = sx_ex2(s[kb][nb][1] - mu_lo);
-        e[nb][2] = sx_ex2(s[kb][nb][2] - mu_hi);
-        e[nb][3] = sx_ex2(s[kb][nb][3] - mu_hi);
-        sum_lo += e[nb][0] + e[nb][1];
-        sum_hi += e[nb][2] + e[nb][3];
+        for (int nb = 0; nb < 2; ++nb) {
+          e[nb][0] = sx_ex2(fmaf(s[kb][nb][0], scale_log2, -ms_lo));
+          e[nb][1] = sx_ex2(fmaf(s[kb][nb][1], scale_log2, -ms_lo));
+          e[nb][2] = sx_ex2(fmaf(s[kb][nb][2], scale_log2, -ms_hi));
+          e[nb][3] = sx_ex2(fmaf(s[kb][nb][3], scale_log2, -ms_hi));
+        }
+        sum_lo += (e[0][0] + e[0][1]) + (e[1][0] + e[1][1]);
+        sum_hi += (e[0][2] + e[0][3]) + (e[1][2] + e[1][3]);
+        pa[kb][0] = pack2(e[0][0], e[0][1]);
+        pa[kb][1] = pack2(e[0][2], e[0][3]);
+        pa[kb][2] = pack2(e[1][0], e[1][1]);
+        pa[kb][3] = pack2(e[1][2], e[1][3]);
       }
-      pa[kb][0] = pack2(e[0][0], e[0][1]);
-      pa[kb][1] = pack2(e[0][2], e[0][3]);
-      pa[kb][2] = pack2(e[1][0], e[1][1]);
-      pa[kb][3] = pack2(e[1][2], e[1][3]);
     }
     sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 1);
     sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 2);
     sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 1);
     sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 2);
+    // O = P V (unnormalised)
     float o[16][4];
 #pragma unroll
     for (int jj = 0; jj < 16; ++jj) o[jj][0] = o[jj][1] = o[jj][2] = o[jj][3] = 0.f;
+    {
+      const uint32_t vrow = vs_u32 + (((mi & 1) << 3) + l7) * kSxRowBytes;
 #pragma unroll
-    for (int kb = 0; kb < 8; ++kb) {
-      if (kb < nkb) {
-        const int mi = lane >> 3;
-        const int r = kb * 16 + ((mi & 1) << 3) + (lane & 7);
-        const uint32_t row_addr = vs_u32 + r * kSxRowBytes;
+      for (int kb = 0; kb < 8; ++kb) {
+        if (kb < nkb) {
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj) {
-          const int chunk = 2 * jj + (mi >> 1);
-          uint32_t b0, b1, b2, b3;
-          sx_ldmatrix_x4_trans(row_addr + ((chunk ^ (r & 7)) << 4), b0, b1, b2, b3);
-          sx_mma(o[2 * jj], pa[kb][0], pa[kb][1], pa[kb][2], pa[kb][3], b0, b1);
-          sx_mma(o[2 * jj + 1], pa[kb][0], pa[kb][1], pa[kb][2], pa[kb][3], b2, b3);
+          for (int jj = 0; jj < 8; ++jj) {
+            uint32_t b0, b1, b2, b3;
+            sx_ldmatrix_x4_trans(vrow + kb * 16 * kSxRowBytes + (((2 * jj + (mi >> 1)) ^ l7) << 4),
+                                 b0, b1, b2, b3);
+            sx_mma(o[2 * jj], pa[kb][0], pa[kb][1], pa[kb][2], pa[kb][3], b0, b1);
+            sx_mma(o[2 * jj + 1], pa[kb][0], pa[kb][1], pa[kb][2], pa[kb][3], b2, b3);
+          }
         }
       }
     }
 
-    // ---- 3. scalars of both downdates, one quad leader per row pair
+    // ---- 3. both downdates folded into three factors per row, by one quad leader:
+    //   state = full * A - band * B - sink_unnormalised * C
     __syncwarp();   // every lane is done with the staged q rows: region A is free
     if (quad == 0) {
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         const int r = half ? rhi : rlo;
-        if (tok_of(r) >= sp.keep) continue;
+        const int tk = i0 + r / G;
+        if (tk >= sp.keep) continue;
         const int h = kh * G + (r % G);
-        const size_t srow = static_cast<size_t>(sp.base_off + sp.start + tok_of(r));
+        const size_t srow = static_cast<size_t>(sp.base_off + sp.start + tk);
         float ret1, t1, s1;
         downdate_scalars(load_lse(p.src_lse, a.full_lse_dtype, srow * H + h),
                          __fmul_rn(load_lse(a.band_lse, a.band_lse_dtype, srow * H + h),
                                    a.band_lse_scale),
                          ret1, t1, s1);
-        int64_t E = pos_base + tok_of(r) + 1 - a.semantic_pos_ahead;
+        int64_t E = pos_base + tk + 1 - a.semantic_pos_ahead;
         if (E < 0) E = 0;
-        float ret2 = -INFINITY, t2 = 0.f, s2 = -1.f;  // s2 < 0: the row holds the empty state
+        float ret2 = -INFINITY, fa = 0.f, fb = 0.f, fc = 0.f, empty = 1.f;
         if (E > F) {
-          const float m = half ? m_hi : m_lo, sum = half ? sum_hi : sum_lo;
-          const float lse_sink = (m + log2f(sum)) * 0.6931471805599453f;
+          const float ms = half ? ms_hi : ms_lo, sum = half ? sum_hi : sum_lo;
+          const float lse_sink = sum > 0.f ? (ms + log2f(sum)) * 0.6931471805599453f : -INFINITY;
+          float t2, s2;
           downdate_scalars(ret1, lse_sink, ret2, t2, s2);
+          fa = s1 * s2;
+          fb = t1 * fa;
+          fc = sum > 0.f ? t2 * s2 / sum : 0.f;
+          empty = 0.f;
         }
-        scal[r] = make_float4(t1, s1, t2, s2);
-        int d = sp.base_dest + tok_of(r);
+        scal[r] = make_float4(fa, fb, fc, empty);
+        int d = dbase + r / G;
         if (d >= p.M) d -= p.M;
         lc[static_cast<size_t>(d) * H + h] = ret2;
       }
     }
-    // ---- 4. park the normalised sink state, then stream the rows to the ring
+    // ---- 4. park the sink state, then stream the rows to the ring
     {
-      const float inv_lo = sum_lo > 0.f ? 1.f / sum_lo : 0.f;
-      const float inv_hi = sum_hi > 0.f ? 1.f / sum_hi : 0.f;
       float* plo = reinterpret_cast<float*>(regA) + rlo * kSxSinkStride + quad * 2;
       float* phi = reinterpret_cast<float*>(regA) + rhi * kSxSinkStride + quad * 2;
 #pragma unroll
       for (int jj = 0; jj < 16; ++jj) {
-        *reinterpret_cast<float2*>(plo + jj * 8) = make_float2(o[jj][0] * inv_lo, o[jj][1] * inv_lo);
-        *reinterpret_cast<float2*>(phi + jj * 8) = make_float2(o[jj][2] * inv_hi, o[jj][3] * inv_hi);
+        *reinterpret_cast<float2*>(plo + jj * 8) = make_float2(o[jj][0], o[jj][1]);
+        *reinterpret_cast<float2*>(phi + jj * 8) = make_float2(o[jj][2], o[jj][3]);
       }
     }
     sx_wait<0>();
     __syncwarp();
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const int r = 2 * j + (lane >> 4);
-      if (tok_of(r) >= sp.keep) continue;
+      const int r = 2 * j + r_half;
+      if (i0 + r / G >= sp.keep) continue;
       const uint4 f4 = *reinterpret_cast<const uint4*>(fullS + r * kSxRowBytes + c * 16);
       const uint4 b4 = *reinterpret_cast<const uint4*>(bandS + r * kSxRowBytes + c * 16);
       const float4 k4 = scal[r];
@@ -542,13 +552,14 @@ prefill_sink_exclusive_ring_kernel(const MacB200PrefillBuildArgs a) {
       uint32_t w[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float mid0 = (lo_f(x[i]) - k4.x * lo_f(y[i])) * k4.y;
-        const float mid1 = (hi_f(x[i]) - k4.x * hi_f(y[i])) * k4.y;
-        const float r0 = (mid0 - k4.z * sink[2 * i]) * k4.w;
-        const float r1 = (mid1 - k4.z * sink[2 * i + 1]) * k4.w;
-        w[i] = k4.w < 0.f ? 0u : pack2(r0, r1);
+        const float r0 = fmaf(lo_f(x[i]), k4.x, fmaf(-lo_f(y[i]), k4.y, -(sink[2 * i] * k4.z)));
+        const float r1 = fmaf(hi_f(x[i]), k4.x, fmaf(-hi_f(y[i]), k4.y, -(sink[2 * i + 1] * k4.z)));
+        w[i] = k4.w != 0.f ? 0u : pack2(r0, r1);
       }
-      st_stream16(ac + dst_off(r) + c * 16, make_uint4(w[0], w[1], w[2], w[3]));
+      int d = dbase + r / G;
+      if (d >= p.M) d -= p.M;
+      st_stream16(ac + static_cast<size_t>(d) * row_bf16 + head_base + (r % G) * kSxRowBytes,
+                  make_uint4(w[0], w[1], w[2], w[3]));
     }
     __syncwarp();   // the next tile's staging overwrites what other lanes just read
   }
@@ -623,11 +634,18 @@ extern "C" int mac_b200_prefill_downdate_update_cache(const MacB200PrefillBuildA
                            reinterpret_cast<uintptr_t>(a.q_post) | reinterpret_cast<uintptr_t>(a.k_buffer) |
                            reinterpret_cast<uintptr_t>(a.v_buffer);
     MAC_REQUIRE((bits & 15u) == 0, "sink-exclusive build needs 16-byte aligned tensors");
+    MAC_REQUIRE(a.sm_scale > 0.f, "sm_scale must be positive");
     int device = 0;
     MAC_CUDA(cudaGetDevice(&device));
+    void (*kernel)(MacB200PrefillBuildArgs) =
+        G == 1 ? prefill_sink_exclusive_ring_kernel<1>
+        : G == 2 ? prefill_sink_exclusive_ring_kernel<2>
+        : G == 4 ? prefill_sink_exclusive_ring_kernel<4>
+        : G == 8 ? prefill_sink_exclusive_ring_kernel<8>
+                 : prefill_sink_exclusive_ring_kernel<16>;
     // the attribute is per device: set it on every call (cheap, no synchronisation)
-    MAC_CUDA(cudaFuncSetAttribute(prefill_sink_exclusive_ring_kernel,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, kSxSmemBytes));
+    MAC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  kSxSmemBytes));
     int sms = 148;
     MAC_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
     const int TG = 16 / G;
@@ -638,7 +656,7 @@ extern "C" int mac_b200_prefill_downdate_update_cache(const MacB200PrefillBuildA
     if (slices > max_slices) slices = max_slices;
     if (slices < 1) slices = 1;
     dim3 grid(slices, a.Hkv, p.B);
-    prefill_sink_exclusive_ring_kernel<<<grid, kSxThreads, kSxSmemBytes, stream>>>(a);
+    kernel<<<grid, kSxThreads, kSxSmemBytes, stream>>>(a);
     MAC_CUDA(cudaGetLastError());
     g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
     if (!p.request_length_by_batch || a.ready) {
