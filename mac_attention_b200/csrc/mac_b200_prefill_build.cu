@@ -376,6 +376,21 @@ prefill_sink_exclusive_ring_kernel(const MacB200PrefillBuildArgs a) {
       sx_cp_async16(band_u32 + r * kSxRowBytes + c * 16, bsrc + so, ok ? 16 : 0);
     }
     sx_commit();
+    // LSEs of the two rows whose factors this lane works out later (quad leaders):
+    // fetched now so that their latency hides behind the tensor-core work
+    float l_full[2] = {0.f, 0.f}, l_band[2] = {0.f, 0.f};
+    if (quad == 0) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int r = half ? rhi : rlo;
+        const int tk = i0 + r / G;
+        if (tk < sp.keep) {
+          const size_t li = static_cast<size_t>(sp.base_off + sp.start + tk) * H + kh * G + (r % G);
+          l_full[half] = load_lse(p.src_lse, a.full_lse_dtype, li);
+          l_band[half] = load_lse(a.band_lse, a.band_lse_dtype, li);
+        }
+      }
+    }
     sx_wait<1>();
     __syncwarp();
 
@@ -499,12 +514,8 @@ prefill_sink_exclusive_ring_kernel(const MacB200PrefillBuildArgs a) {
         const int tk = i0 + r / G;
         if (tk >= sp.keep) continue;
         const int h = kh * G + (r % G);
-        const size_t srow = static_cast<size_t>(sp.base_off + sp.start + tk);
         float ret1, t1, s1;
-        downdate_scalars(load_lse(p.src_lse, a.full_lse_dtype, srow * H + h),
-                         __fmul_rn(load_lse(a.band_lse, a.band_lse_dtype, srow * H + h),
-                                   a.band_lse_scale),
-                         ret1, t1, s1);
+        downdate_scalars(l_full[half], __fmul_rn(l_band[half], a.band_lse_scale), ret1, t1, s1);
         int64_t E = pos_base + tk + 1 - a.semantic_pos_ahead;
         if (E < 0) E = 0;
         float ret2 = -INFINITY, fa = 0.f, fb = 0.f, fc = 0.f, empty = 1.f;
