@@ -134,13 +134,16 @@ def ring_slot(past_len: int, capacity: int, pos: int) -> int:
 
 def plant_matches(case: DecodeCase, *, hit_fraction: float, noise: float = 0.1, lag_lo: int = 1,
                   lag_hi: int | None = None, seed: int = 0, borderline_fraction: float = 0.0,
-                  threshold: float = 0.45, state_scale: float = 1.0) -> torch.Tensor:
+                  threshold: float = 0.45, state_scale: float = 1.0,
+                  heads_per_draw: int = 1) -> torch.Tensor:
     """Plant ring entries so that about ``hit_fraction`` of the (request, head)
     pairs find a near-duplicate of their pre-RoPE query at a position drawn
     uniformly from ``[P - lag_hi, P - lag_lo]``.  Planted rows get a finite
     prefix state (random o, finite LSE).  ``borderline_fraction`` of the other
     pairs get a row whose squared distance sits within ~1% of the threshold, on
-    either side.  Returns the bool mask [batch, hq] of planted hits."""
+    either side.  ``heads_per_draw`` > 1 draws hit/miss once per that many
+    consecutive heads (one KV group), the way the reference's synthetic benchmark
+    mode clusters its misses.  Returns the bool mask [batch, hq] of planted hits."""
     g = _gen(seed + 77, "cpu")
     batch, hq, dim = case.q_pre.shape
     cap = case.query_cache.shape[1]
@@ -156,6 +159,8 @@ def plant_matches(case: DecodeCase, *, hit_fraction: float, noise: float = 0.1, 
         hi = min(lag_hi if lag_hi is not None else max_lag, max_lag)
         lo = min(max(lag_lo, 1), hi)
         u = torch.rand(hq, generator=g)
+        if heads_per_draw > 1:
+            u = u[::heads_per_draw].repeat_interleave(heads_per_draw)[:hq]
         lag = torch.randint(lo, hi + 1, (hq,), generator=g)
         ub = torch.rand(hq, generator=g)
         for h in range(hq):
