@@ -135,3 +135,29 @@ def test_sink_exclusive_argument_errors():
     bad["v"] = bad["k"]
     with pytest.raises(RuntimeError, match="divisible"):
         _build(ext.mac_prefill_downdate_update_cache, bad, 32, 8, 4, 16)
+
+
+def test_one_pass_build_replays_from_a_cuda_graph():
+    ext = load_mac_prefill_update_cache_extension()
+    spec = SPECS[0]
+    Hq, S, F, M = spec["Hq"], spec["S"], spec["F"], spec["M"]
+    t = _prompts(spec["lens"], spec["L0s"], Hq, spec["Hkv"], S, F, M, seed=6)
+    t.pop("want_o"), t.pop("want_l")
+    # by-batch lengths: the build leaves request_length alone, so a replay repeats the same write
+    eager = {k: v.cuda() for k, v in t.items()}
+    _build(ext.mac_prefill_downdate_update_cache, eager, M, Hq, S, F)
+    torch.cuda.synchronize()
+    g = {k: v.cuda() for k, v in t.items()}
+    lengths = g["request_length"].clone()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        g["request_length"].copy_(lengths)
+        _build(ext.mac_prefill_downdate_update_cache, g, M, Hq, S, F)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    for name in ("q_cache", "attn_cache", "q_post_cache"):     # bit patterns: the stamp is NaN
+        assert torch.equal(g[name].view(torch.int16), eager[name].view(torch.int16)), name
+    assert torch.equal(g["request_length"], eager["request_length"])
+    assert torch.equal(g["lse_cache"].view(torch.int32), eager["lse_cache"].view(torch.int32))
+    assert ops.query_status() == 0
