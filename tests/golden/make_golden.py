@@ -2,7 +2,7 @@
 
 Run where the reference checkout is mounted (it cannot travel to the GPU box):
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py [--reference <path of the reference checkout>]
 
 What it imports from the reference and never re-implements:
 

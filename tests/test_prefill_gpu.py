@@ -271,3 +271,43 @@ def test_prefill_build_argument_errors():
     call()
     torch.cuda.synchronize()
     assert bool(t["ready"][0]) and not bool(t["ready"][1])
+
+
+def test_prefill_build_matches_the_reference_kernels_in_the_hook_order():
+    """Ring contents against the reference's own CUDA operators (built for sm_100a
+    from the reference sources), called in the order its prefill hook calls them."""
+    from oracle import build_ref
+
+    rdd, rpre = build_ref.load_downdate(), build_ref.load_prefill()
+    if rdd is None or rpre is None:
+        pytest.skip("reference kernels are not built on this box")
+    ext = load_mac_prefill_update_cache_extension()
+    R, M, H, D = 4, 512, 32, 128
+    lens, req_ids, L0 = [2048, 100, 513], [2, 3, 0], [0, 0, 100, 7]
+    t = _build_inputs(R, M, H, D, lens, req_ids, L0, seed=11)
+    ln2 = 0.6931471805599453
+    ref = {k: v.cuda() for k, v in t.items()}
+    band_lse = ref["band_lse"] * ln2
+    rdd.mac_update_then_downdate_bf16_inplace(ref["full_attn"], ref["full_lse"], ref["band_attn"],
+                                              band_lse)
+    rpre.mac_prefill_update_cache(ref["q_cache"], ref["attn_cache"], ref["lse_cache"],
+                                  ref["request_length"], ref["req_ids"], ref["src_q"],
+                                  ref["band_attn"], band_lse, ref["offsets"], ref["lens"], M, H, D,
+                                  ref["q_post_cache"])
+    rpre.mac_mark_persistent_ready(ref["ready"], ref["cache_epoch"], ref["request_epoch"],
+                                   ref["req_ids"])
+    one = {k: v.cuda() for k, v in t.items()}
+    ext.mac_prefill_downdate_update_cache(
+        one["q_cache"], one["attn_cache"], one["lse_cache"], one["request_length"], one["req_ids"],
+        one["src_q"], one["full_attn"], one["full_lse"], one["band_attn"], one["band_lse"],
+        one["offsets"], one["lens"], M, H, D, one["q_post_cache"], band_lse_scale=ln2,
+        ready=one["ready"], cache_epoch=one["cache_epoch"], request_epoch=one["request_epoch"])
+    torch.cuda.synchronize()
+    for name in ("q_cache", "q_post_cache"):
+        assert torch.equal(one[name].view(torch.int16), ref[name].view(torch.int16)), name
+    for name in ("request_length", "ready", "cache_epoch"):
+        assert torch.equal(one[name], ref[name]), name
+    fin = torch.isfinite(ref["lse_cache"])
+    assert torch.equal(torch.isfinite(one["lse_cache"]), fin)
+    assert (one["lse_cache"][fin] - ref["lse_cache"][fin]).abs().max() <= 1e-3   # reference: fast-math exp/log
+    assert O.rel_l2(one["attn_cache"].float().cpu(), ref["attn_cache"].float().cpu()) <= 1e-2
