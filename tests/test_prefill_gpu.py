@@ -311,3 +311,26 @@ def test_prefill_build_matches_the_reference_kernels_in_the_hook_order():
     assert torch.equal(torch.isfinite(one["lse_cache"]), fin)
     assert (one["lse_cache"][fin] - ref["lse_cache"][fin]).abs().max() <= 1e-3   # reference: fast-math exp/log
     assert O.rel_l2(one["attn_cache"].float().cpu(), ref["attn_cache"].float().cpu()) <= 1e-2
+
+
+def test_prefill_build_noop_cases_leave_the_ring_alone():
+    ext = load_mac_prefill_update_cache_extension()
+    t = {k: v.cuda() for k, v in _build_inputs(2, 4, 2, 128, [3], [0], [0, 0], 0).items()}
+    before = {k: t[k].clone() for k in ("q_cache", "attn_cache", "lse_cache", "ready")}
+
+    def call(capacity, **kw):
+        a = dict(t)
+        a.update(kw)
+        ext.mac_prefill_downdate_update_cache(
+            a["q_cache"], a["attn_cache"], a["lse_cache"], a["request_length"], a["req_ids"],
+            a["src_q"], a["full_attn"], a["full_lse"], a["band_attn"], a["band_lse"], a["offsets"],
+            a["lens"], capacity, 2, 128, a["q_post_cache"], ready=a["ready"],
+            cache_epoch=a["cache_epoch"], request_epoch=a["request_epoch"])
+
+    call(0)                                                       # capacity <= 0: the reference's silent no-op
+    call(4, req_ids=t["req_ids"][:0], lens=t["lens"][:0], offsets=t["offsets"][:1])   # empty batch
+    call(4, lens=torch.zeros_like(t["lens"]))                     # zero-length prompt: nothing copied ...
+    torch.cuda.synchronize()
+    for k in ("q_cache", "attn_cache", "lse_cache"):
+        assert torch.equal(before[k].view(torch.uint8), t[k].view(torch.uint8)), k
+    assert bool(t["ready"][0])                                    # ... but the request is marked, as by the reference's mark kernel
