@@ -376,19 +376,15 @@ prefill_sink_exclusive_ring_kernel(const MacB200PrefillBuildArgs a) {
       sx_cp_async16(band_u32 + r * kSxRowBytes + c * 16, bsrc + so, ok ? 16 : 0);
     }
     sx_commit();
-    // LSEs of the two rows whose factors this lane works out later (quad leaders):
+    // LSEs of the row whose factors this lane works out later (lane r < 16 owns MMA row r):
     // fetched now so that their latency hides behind the tensor-core work
-    float l_full[2] = {0.f, 0.f}, l_band[2] = {0.f, 0.f};
-    if (quad == 0) {
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int r = half ? rhi : rlo;
-        const int tk = i0 + r / G;
-        if (tk < sp.keep) {
-          const size_t li = static_cast<size_t>(sp.base_off + sp.start + tk) * H + kh * G + (r % G);
-          l_full[half] = load_lse(p.src_lse, a.full_lse_dtype, li);
-          l_band[half] = load_lse(a.band_lse, a.band_lse_dtype, li);
-        }
+    float l_full = 0.f, l_band = 0.f;
+    {
+      const int tk = i0 + lane / G;
+      if (lane < 16 && tk < sp.keep) {
+        const size_t li = static_cast<size_t>(sp.base_off + sp.start + tk) * H + kh * G + (lane % G);
+        l_full = load_lse(p.src_lse, a.full_lse_dtype, li);
+        l_band = load_lse(a.band_lse, a.band_lse_dtype, li);
       }
     }
     sx_wait<1>();
@@ -458,7 +454,9 @@ prefill_sink_exclusive_ring_kernel(const MacB200PrefillBuildArgs a) {
     // scaled maxima (sm_scale > 0); -inf only when there is no sink key at all
     const float ms_lo = m_lo == -INFINITY ? 0.f : m_lo * scale_log2;
     const float ms_hi = m_hi == -INFINITY ? 0.f : m_hi * scale_log2;
-    float sum_lo = 0.f, sum_hi = 0.f;
+    float sum_lo = 0.f, sum_hi = 0.f;   // fp32 sums of the unrounded weights: the second downdate
+                                        // is sensitive to the denominator when the sink holds
+                                        // nearly all of a row's mass
     uint32_t pa[8][4];
 #pragma unroll
     for (int kb = 0; kb < 8; ++kb) {
@@ -504,23 +502,28 @@ prefill_sink_exclusive_ring_kernel(const MacB200PrefillBuildArgs a) {
       }
     }
 
-    // ---- 3. both downdates folded into three factors per row, by one quad leader:
+    // ---- 3. both downdates folded into three factors per row, lane r < 16 for MMA row r:
     //   state = full * A - band * B - sink_unnormalised * C
     __syncwarp();   // every lane is done with the staged q rows: region A is free
-    if (quad == 0) {
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int r = half ? rhi : rlo;
-        const int tk = i0 + r / G;
-        if (tk >= sp.keep) continue;
+    {
+      // row r's scaled maximum and denominator live in the quad 4 * (r & 7): rows 0..7 in
+      // the "lo" values, rows 8..15 in the "hi" values
+      const int src_lane = (lane & 7) << 2;
+      const float ms_a = __shfl_sync(0xffffffffu, ms_lo, src_lane);
+      const float ms_b = __shfl_sync(0xffffffffu, ms_hi, src_lane);
+      const float su_a = __shfl_sync(0xffffffffu, sum_lo, src_lane);
+      const float su_b = __shfl_sync(0xffffffffu, sum_hi, src_lane);
+      const int r = lane;
+      const int tk = i0 + r / G;
+      if (r < 16 && tk < sp.keep) {
+        const float ms = (r & 8) ? ms_b : ms_a, sum = (r & 8) ? su_b : su_a;
         const int h = kh * G + (r % G);
         float ret1, t1, s1;
-        downdate_scalars(l_full[half], __fmul_rn(l_band[half], a.band_lse_scale), ret1, t1, s1);
+        downdate_scalars(l_full, __fmul_rn(l_band, a.band_lse_scale), ret1, t1, s1);
         int64_t E = pos_base + tk + 1 - a.semantic_pos_ahead;
         if (E < 0) E = 0;
         float ret2 = -INFINITY, fa = 0.f, fb = 0.f, fc = 0.f, empty = 1.f;
         if (E > F) {
-          const float ms = half ? ms_hi : ms_lo, sum = half ? sum_hi : sum_lo;
           const float lse_sink = sum > 0.f ? (ms + log2f(sum)) * 0.6931471805599453f : -INFINITY;
           float t2, s2;
           downdate_scalars(ret1, lse_sink, ret2, t2, s2);
