@@ -216,11 +216,17 @@ prefill_downdate_ring_kernel(const MacB200PrefillBuildArgs a) {
 // CTA = (slice of a request's ring rows, one KV head); 8 independent warps.  A
 // warp tile is 16 MMA rows = 16/G consecutive tokens x the G query heads of the
 // KV head.  Per tile the warp
-//   1. cp.asyncs its q_post, q_pre, full and band rows into its own staging,
+//   1. cp.asyncs its q_post, q_pre, full and band rows into its own staging
+//      and fetches the rows' LSEs (lane r < 16 owns MMA row r),
 //   2. S = Q K^T over the sink keys, softmax (log2 domain), O = P V,
-//   3. works out both downdates' scalars per row,
-//   4. parks the normalised sink state in shared memory and streams
-//      ((full - t1*band)*s1 - t2*sink)*s2 to the ring in 16-byte chunks.
+//   3. folds both downdates into three factors per row, one row per lane:
+//      state = full*A - band*B - sink_unnormalised*C,
+//   4. parks the sink state in shared memory (over the dead q staging) and
+//      streams the rows to the ring in 16-byte chunks.
+// With 246 registers per thread (64 score + 64 output accumulators) only eight
+// warps fit an SM, so the kernel is bound by issue latency rather than by HBM
+// or the tensor pipe; anything the warp does on a few lanes only (the row
+// factors' exp/log chains) costs as much as if all lanes did it.
 constexpr int kSxD = 128;
 constexpr int kSxRowBytes = kSxD * 2;
 constexpr int kSxMaxF = 128;
