@@ -349,16 +349,31 @@ def run_ours(args):
 
     # end to end through the operator with host buffers: H2D of the step's
     # inputs from pinned memory, eager operator call, D2H of the output.
-    host = {k: getattr(case, k).cpu().pin_memory() for k in
-            ("q_post", "q_pre", "req_ids", "past_lens", "out_cache_loc")}
+    # The step's inputs travel as a serving engine would send them: the two query tensors
+    # in one pinned buffer, the two int32 vectors in another, the KV slot vector in a third.
+    import copy
+
+    n_rows = case.q_post.shape[0]
+    e2e_case = copy.copy(case)
+    dev_q = torch.empty((2,) + tuple(case.q_post.shape), dtype=case.q_post.dtype, device=dev)
+    dev_i = torch.empty((2, n_rows), dtype=torch.int32, device=dev)
+    dev_loc = torch.empty_like(case.out_cache_loc)
+    e2e_case.q_post, e2e_case.q_pre = dev_q[0], dev_q[1]
+    e2e_case.req_ids, e2e_case.past_lens = dev_i[0], dev_i[1]
+    e2e_case.out_cache_loc = dev_loc
+    host_q = torch.stack([case.q_post, case.q_pre]).cpu().pin_memory()
+    host_i = torch.stack([case.req_ids[:n_rows], case.past_lens[:n_rows]]).cpu().pin_memory()
+    host_loc = case.out_cache_loc.cpu().pin_memory()
     out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-    h2d = sum(v.numel() * v.element_size() for v in host.values())
+    h2d = sum(v.numel() * v.element_size() for v in (host_q, host_i, host_loc))
     d2h = out_host.numel() * out_host.element_size()
+    launch_e2e = make_launch(ext, e2e_case, ws, scal, out, lse)
 
     def e2e_step():
-        for k, v in host.items():
-            getattr(case, k).copy_(v, non_blocking=True)
-        launch()
+        dev_q.copy_(host_q, non_blocking=True)
+        dev_i.copy_(host_i, non_blocking=True)
+        dev_loc.copy_(host_loc, non_blocking=True)
+        launch_e2e()
         out_host.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
