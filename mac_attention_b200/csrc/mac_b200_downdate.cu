@@ -25,7 +25,7 @@ struct DowndateParams {
   const void* lse1;
   void* lse2;
   int64_t rows;
-  int32_t D, chunks, lanes_per_row, dt1, dt2;
+  int32_t D, chunks, lanes_per_row, unroll, dt1, dt2;
 };
 
 __global__ void __launch_bounds__(kDownThreads)
@@ -38,7 +38,8 @@ downdate_inplace_kernel(const DowndateParams p) {
   const int64_t warps_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
   const int64_t row_bytes = static_cast<int64_t>(p.D) * 2;
 
-  const int rows_per_iter = rows_per_warp * kDownUnroll;   // <= 32: one lane per row for the scalars
+  const int unroll = p.unroll;                             // <= kDownUnroll, and such that
+  const int rows_per_iter = rows_per_warp * unroll;        // <= 32: one lane per row for the scalars
   for (int64_t base = warp_global * rows_per_iter; base < p.rows; base += warps_total * rows_per_iter) {
     // lane r works out the three scalars of row base + r (all lanes busy), the
     // chunk lanes fetch them by shuffle; the row's LSE is replaced right away
@@ -60,7 +61,7 @@ downdate_inplace_kernel(const DowndateParams p) {
 #pragma unroll
       for (int u = 0; u < kDownUnroll; ++u) {
         const int64_t row = base + u * rows_per_warp + lane / lpr;
-        live[u] = row < p.rows && c < p.chunks;
+        live[u] = u < unroll && row < p.rows && c < p.chunks;
         if (live[u]) {
           a[u] = *reinterpret_cast<const uint4*>(p.out1 + row * row_bytes + c * 16);
           b[u] = *reinterpret_cast<const uint4*>(p.out2 + row * row_bytes + c * 16);
@@ -141,12 +142,15 @@ extern "C" int mac_b200_update_then_downdate_bf16_inplace(const void* out1, cons
     int lpr = 1;
     while (lpr < p.chunks && lpr < 32) lpr <<= 1;
     p.lanes_per_row = lpr;
-    const int64_t rows_per_cta = static_cast<int64_t>(kDownThreads / 32) * (32 / lpr) * kDownUnroll;
+    p.unroll = kDownUnroll;
+    while ((32 / lpr) * p.unroll > 32) p.unroll >>= 1;   // narrow rows: fewer rows in flight per lane
+    const int64_t rows_per_cta = static_cast<int64_t>(kDownThreads / 32) * (32 / lpr) * p.unroll;
     int64_t blocks = (rows + rows_per_cta - 1) / rows_per_cta;
     if (blocks > 148 * 32) blocks = 148 * 32;
     downdate_inplace_kernel<<<static_cast<unsigned>(blocks), kDownThreads, 0, stream>>>(p);
   } else {
     p.chunks = 0;
+    p.unroll = 1;
     p.lanes_per_row = 32;
     int64_t blocks = (rows + 7) / 8;
     if (blocks > 148 * 32) blocks = 148 * 32;

@@ -935,7 +935,8 @@ static void build_row_item(void* ctx, int i) {
     downdate_scalars_f(ret, lse_sink, &ret2, &t2, &scale2);
     for (int d = 0; d < D; ++d) {
       const float mid = (bf16_to_f32(full[h * D + d]) - t * bf16_to_f32(band[h * D + d])) * scale;
-      orow[h * D + d] = f32_to_bf16((mid - t2 * (float)(osink[d] / sum)) * scale2);
+      const float sk = sum > 0.0 ? (float)(osink[d] / sum) : 0.f;   /* F == 0: no sink at all */
+      orow[h * D + d] = f32_to_bf16((mid - t2 * sk) * scale2);
     }
     p->lse_cache[dst * H + h] = ret2;
   }

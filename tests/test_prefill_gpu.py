@@ -334,3 +334,64 @@ def test_prefill_build_noop_cases_leave_the_ring_alone():
     for k in ("q_cache", "attn_cache", "lse_cache"):
         assert torch.equal(before[k].view(torch.uint8), t[k].view(torch.uint8)), k
     assert bool(t["ready"][0])                                    # ... but the request is marked, as by the reference's mark kernel
+
+
+@pytest.mark.parametrize("chunk", range(4))
+def test_prefill_build_random_matrix(chunk):
+    """Seeded random geometries of the one-pass build (modes NONE / UNMATCHABLE) against the
+    CPU restatement and, bit for bit, against the separate CUDA operators."""
+    import random
+
+    from mac_attention_b200 import ops
+
+    ext = load_mac_prefill_update_cache_extension()
+    rng = random.Random(300 + chunk)
+    for i in range(15):
+        R = rng.randint(1, 6)
+        M = rng.choice([1, 3, 8, 32, 100, 256])
+        H = rng.choice([1, 3, 8, 32, 40])
+        D = rng.choice([16, 20, 64, 128])
+        B = rng.randint(1, 5)
+        lens = [rng.choice([0, 1, rng.randint(1, 40), rng.randint(1, 2 * M + 3)]) for _ in range(B)]
+        req_ids = [rng.choice([rng.randint(0, R - 1), rng.randint(0, R - 1), -1, R + 2]) for _ in range(B)]
+        # distinct valid request ids (two batch rows writing one ring would race in any implementation)
+        seen = set()
+        for b in range(B):
+            if 0 <= req_ids[b] < R:
+                if req_ids[b] in seen:
+                    req_ids[b] = -1
+                seen.add(req_ids[b])
+        L0 = [rng.choice([0, -3, rng.randint(0, 3 * M)]) for _ in range(R)]
+        unm = rng.random() < 0.4
+        scale = rng.choice([1.0, 0.6931471805599453])
+        tag = f"chunk {chunk} case {i}: R{R} M{M} H{H} D{D} lens{lens} req{req_ids} L0{L0} unm{unm}"
+        t = _build_inputs(R, M, H, D, lens, req_ids, L0, seed=1000 * chunk + i)
+        cpu = {k: v.clone() for k, v in t.items()}
+        O.prefill_build(cpu["q_cache"], cpu["attn_cache"], cpu["lse_cache"], cpu["request_length"],
+                        cpu["req_ids"], cpu["src_q"], cpu["full_attn"], cpu["full_lse"],
+                        cpu["band_attn"], cpu["band_lse"], cpu["offsets"], cpu["lens"], M, H, D,
+                        cpu["q_post_cache"], band_lse_scale=scale, sink_mode=1 if unm else 0,
+                        ready=cpu["ready"], cache_epoch=cpu["cache_epoch"],
+                        request_epoch=cpu["request_epoch"])
+        seq = {k: v.cuda() for k, v in t.items()}
+        _sequential(dict(downdate=ops.mac_update_then_downdate_bf16_inplace,
+                         prefill=ext.mac_prefill_update_cache, mark=ext.mac_mark_persistent_ready),
+                    seq, M, H, D, scale, unm)
+        one = {k: v.cuda() for k, v in t.items()}
+        ext.mac_prefill_downdate_update_cache(
+            one["q_cache"], one["attn_cache"], one["lse_cache"], one["request_length"],
+            one["req_ids"], one["src_q"], one["full_attn"], one["full_lse"], one["band_attn"],
+            one["band_lse"], one["offsets"], one["lens"], M, H, D, one["q_post_cache"],
+            band_lse_scale=scale, sink_mode=1 if unm else 0, ready=one["ready"],
+            cache_epoch=one["cache_epoch"], request_epoch=one["request_epoch"])
+        torch.cuda.synchronize()
+        for name in ("q_cache", "attn_cache", "q_post_cache"):
+            assert torch.equal(one[name].view(torch.int16), seq[name].view(torch.int16)), (name, tag)
+        assert torch.equal(one["lse_cache"].view(torch.int32), seq["lse_cache"].view(torch.int32)), tag
+        for name in ("request_length", "ready", "cache_epoch"):
+            assert torch.equal(one[name].cpu(), cpu[name]), (name, tag)
+            assert torch.equal(one[name], seq[name]), (name, tag)
+        assert torch.equal(one["q_cache"].cpu().view(torch.int16), cpu["q_cache"].view(torch.int16)), tag
+        fin = torch.isfinite(cpu["lse_cache"])
+        assert torch.equal(torch.isfinite(one["lse_cache"]).cpu(), fin), tag
+        assert O.rel_l2(one["attn_cache"].float().cpu(), cpu["attn_cache"].float()) <= 2e-3, tag

@@ -161,3 +161,39 @@ def test_one_pass_build_replays_from_a_cuda_graph():
     assert torch.equal(g["request_length"], eager["request_length"])
     assert torch.equal(g["lse_cache"].view(torch.int32), eager["lse_cache"].view(torch.int32))
     assert ops.query_status() == 0
+
+
+@pytest.mark.parametrize("chunk", range(3))
+def test_sink_exclusive_random_matrix(chunk):
+    """Seeded random prompts (GQA group, sink size, window, ring size, chunked prefill
+    offsets) through the sink-exclusive build against the CPU restatement."""
+    import random
+
+    ext = load_mac_prefill_update_cache_extension()
+    rng = random.Random(700 + chunk)
+    for i in range(8):
+        hkv = rng.choice([1, 2, 4])
+        G = rng.choice([1, 2, 4, 8, 16])
+        S = rng.choice([1, 4, 16, 64])
+        F = rng.choice([0, 1, 16, 20, 64, 128])
+        M = rng.choice([16, 64, 128, 300])
+        B = rng.randint(1, 3)
+        lens = [rng.randint(1, 260) for _ in range(B)]
+        L0s = [rng.choice([0, rng.randint(0, 200)]) for _ in range(B)]
+        tag = f"chunk {chunk} case {i}: hkv{hkv} G{G} S{S} F{F} M{M} lens{lens} L0{L0s}"
+        t = _prompts(lens, L0s, hkv * G, hkv, S, F, M, seed=50 * chunk + i)
+        t.pop("want_o"), t.pop("want_l")
+        cpu = {k: v.clone() for k, v in t.items()}
+        _build(O.prefill_build, cpu, M, hkv * G, S, F)
+        gpu = {k: v.cuda() for k, v in t.items()}
+        _build(ext.mac_prefill_downdate_update_cache, gpu, M, hkv * G, S, F)
+        torch.cuda.synchronize()
+        g = {k: v.cpu() for k, v in gpu.items()}
+        assert torch.equal(g["q_cache"].view(torch.int16), cpu["q_cache"].view(torch.int16)), tag
+        assert torch.equal(g["q_post_cache"].view(torch.int16), cpu["q_post_cache"].view(torch.int16)), tag
+        for name in ("request_length", "ready", "cache_epoch"):
+            assert torch.equal(g[name], cpu[name]), (name, tag)
+        fin = torch.isfinite(cpu["lse_cache"])
+        assert torch.equal(torch.isfinite(g["lse_cache"]), fin), tag
+        assert O.rel_l2(g["attn_cache"].float(), cpu["attn_cache"].float()) <= 2e-2, tag
+    assert ops.query_status() == 0

@@ -151,7 +151,8 @@ def _downdate_inputs(N, H, D, seed):
     return out1, lse1, out2, lse2
 
 
-@pytest.mark.parametrize("N,H,D", [(300, 32, 128), (5, 3, 64), (9, 4, 40), (2, 2, 1024)])
+@pytest.mark.parametrize("N,H,D", [(300, 32, 128), (5, 3, 64), (9, 4, 40), (2, 2, 1024), (70, 5, 16),
+                                   (33, 2, 8), (64, 4, 32)])
 def test_downdate_matches_oracle_and_reference(N, H, D):
     ext = load_mac_merge_downdate_cache_extension()
     out1, lse1, out2, lse2 = _downdate_inputs(N, H, D, 5)
