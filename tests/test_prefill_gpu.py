@@ -395,3 +395,46 @@ def test_prefill_build_random_matrix(chunk):
         fin = torch.isfinite(cpu["lse_cache"])
         assert torch.equal(torch.isfinite(one["lse_cache"]).cpu(), fin), tag
         assert O.rel_l2(one["attn_cache"].float().cpu(), cpu["attn_cache"].float()) <= 2e-3, tag
+
+
+@pytest.mark.parametrize("chunk", range(3))
+def test_prefill_update_cache_random_matrix(chunk):
+    """Seeded random geometries of the plain ring copy against the oracle, bit for bit."""
+    import random
+
+    ext = load_mac_prefill_update_cache_extension()
+    rng = random.Random(20 + chunk)
+    for i in range(15):
+        R, M = rng.randint(1, 6), rng.choice([1, 3, 8, 32, 100, 256])
+        H, D = rng.choice([1, 3, 8, 32, 40]), rng.choice([4, 16, 20, 64, 128])
+        B = rng.randint(1, 5)
+        lens = [rng.choice([0, 1, rng.randint(1, 40), rng.randint(1, 2 * M + 3)]) for _ in range(B)]
+        req_ids, seen = [], set()
+        for _ in range(B):
+            r = rng.choice([rng.randint(0, R - 1), rng.randint(0, R - 1), -1, R + 2])
+            if r in seen:
+                r = -1
+            seen.add(r)
+            req_ids.append(r)
+        by_batch = rng.random() < 0.3
+        L0 = [rng.choice([0, -3, rng.randint(0, 3 * M)]) for _ in range(B if by_batch else R)]
+        if (len(L0) == B) != by_batch:       # R == B makes the operator take the by-batch reading
+            continue
+        with_post = rng.random() < 0.7
+        t = _prefill_inputs(R, M, H, D, lens, req_ids, L0, seed=100 * chunk + i, with_post=with_post)
+        cpu = {k: v.clone() for k, v in t.items()}
+        O.prefill_update_cache(cpu["q_cache"], cpu["attn_cache"], cpu["lse_cache"],
+                               cpu["request_length"], cpu["req_ids"], cpu["src_q"], cpu["src_attn"],
+                               cpu["src_lse"], cpu["offsets"], cpu["lens"], M, H, D, cpu["q_post_cache"])
+        gpu = {k: v.cuda() for k, v in t.items()}
+        ext.mac_prefill_update_cache(gpu["q_cache"], gpu["attn_cache"], gpu["lse_cache"],
+                                     gpu["request_length"], gpu["req_ids"], gpu["src_q"],
+                                     gpu["src_attn"], gpu["src_lse"], gpu["offsets"], gpu["lens"],
+                                     M, H, D, gpu["q_post_cache"])
+        torch.cuda.synchronize()
+        tag = f"chunk {chunk} case {i}: R{R} M{M} H{H} D{D} lens{lens} req{req_ids} L0{L0}"
+        for name in ("q_cache", "attn_cache", "q_post_cache"):
+            if gpu[name].numel():
+                assert torch.equal(gpu[name].cpu().view(torch.int16), cpu[name].view(torch.int16)), (name, tag)
+        assert torch.equal(gpu["request_length"].cpu(), cpu["request_length"]), tag
+        assert torch.equal(gpu["lse_cache"].cpu().view(torch.int32), cpu["lse_cache"].view(torch.int32)), tag

@@ -226,3 +226,68 @@ def test_downdate_then_merge_recovers_the_prefix_state():
     torch.cuda.synchronize()
     assert (lse2.cpu()[0] - l_pre).abs().max() < 2e-2
     assert O.rel_l2(out2.float().cpu()[0], o_pre) < 3e-2
+
+
+@pytest.mark.parametrize("chunk", range(3))
+def test_rope_preserve_random_matrix(chunk):
+    """Seeded random shapes (head counts, head / rotary sizes incl. ones only the scalar path
+    takes, both layouts, index types, fused or separate q/k/v) against the CPU oracle, bit for bit."""
+    import random
+
+    ext = load_mac_decode_rope_preserve_extension()
+    rng = random.Random(40 + chunk)
+    for i in range(12):
+        Hkv = rng.choice([1, 2, 4, 8])
+        Hq = Hkv * rng.choice([1, 2, 4, 8])
+        D = rng.choice([16, 40, 64, 80, 128, 256])
+        rot = rng.choice([D, D // 2, 8])
+        rot -= rot % 2
+        spec = dict(N=rng.randint(1, 70), Hq=Hq, Hkv=Hkv, D=D, rot=rot, neox=rng.random() < 0.5,
+                    pos=rng.choice([torch.int32, torch.int64]),
+                    loc=rng.choice([torch.int32, torch.int64]), fused=rng.random() < 0.7)
+        t = _rope_inputs(spec["N"], Hq, Hkv, D, rot, 2048, 200, 100 * chunk + i, spec["pos"],
+                         spec["loc"], fused_qkv=spec["fused"])
+        gpu = _to_cuda(t, Hq, Hkv, D)
+        q_before = t["q"].clone()
+        O.decode_rope_preserve(t["q"], t["k"], t["v"], t["q_pre"], t["k_buffer"], t["v_buffer"],
+                               t["cache"], t["positions"], t["locs"], D, spec["neox"])
+        _run_rope(ext, gpu, D, spec["neox"])
+        torch.cuda.synchronize()
+        N = spec["N"]
+        tag = f"chunk {chunk} case {i}: {spec}"
+        assert torch.equal(gpu["q_pre"].cpu()[:N].view(N, -1).view(torch.int16),
+                           q_before.contiguous().view(torch.int16)), tag
+        for name in ("q", "k"):
+            assert torch.equal(gpu[name].cpu().contiguous().view(torch.int16),
+                               t[name].contiguous().view(torch.int16)), (name, tag)
+        for name in ("k_buffer", "v_buffer"):
+            assert torch.equal(gpu[name].cpu().view(torch.int16), t[name].view(torch.int16)), (name, tag)
+
+
+@pytest.mark.parametrize("chunk", range(2))
+def test_downdate_random_matrix(chunk):
+    import random
+
+    ext = load_mac_merge_downdate_cache_extension()
+    rng = random.Random(90 + chunk)
+    for i in range(15):
+        N, H = rng.randint(1, 300), rng.choice([1, 2, 3, 8, 32])
+        D = rng.choice([8, 16, 24, 32, 40, 64, 128, 256, 1024])
+        g = torch.Generator().manual_seed(10 * chunk + i)
+        out1 = torch.randn(N, H, D, generator=g).to(torch.bfloat16)
+        out2 = torch.randn(N, H, D, generator=g).to(torch.bfloat16)
+        lse1 = torch.randn(N, H, generator=g) + 4
+        lse2 = lse1 - torch.rand(N, H, generator=g) * 5 - 0.02
+        lse2[0, 0] = lse1[0, 0]
+        if N > 1:
+            lse2[1, 0] = lse1[1, 0] + 2
+        c_out2, c_lse2 = out2.clone(), lse2.clone()
+        O.update_then_downdate(out1, lse1, c_out2, c_lse2)
+        g_out2, g_lse2 = out2.cuda(), lse2.cuda()
+        ext.mac_update_then_downdate_bf16_inplace(out1.cuda(), lse1.cuda(), g_out2, g_lse2)
+        torch.cuda.synchronize()
+        tag = f"chunk {chunk} case {i}: N{N} H{H} D{D}"
+        fin = torch.isfinite(c_lse2)
+        assert torch.equal(torch.isfinite(g_lse2.cpu()), fin), tag
+        assert torch.allclose(g_lse2.cpu()[fin], c_lse2[fin], rtol=1e-5, atol=1e-5), tag
+        assert O.rel_l2(g_out2.float().cpu(), c_out2.float()) <= 2e-3, tag
