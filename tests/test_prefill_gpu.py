@@ -438,3 +438,59 @@ def test_prefill_update_cache_random_matrix(chunk):
                 assert torch.equal(gpu[name].cpu().view(torch.int16), cpu[name].view(torch.int16)), (name, tag)
         assert torch.equal(gpu["request_length"].cpu(), cpu["request_length"]), tag
         assert torch.equal(gpu["lse_cache"].cpu().view(torch.int32), cpu["lse_cache"].view(torch.int32)), tag
+
+
+def test_prefill_build_at_serving_size_equals_the_operator_sequence():
+    """8 prompts of 32768 tokens, Hq 32, D 128, ring 2048 (the serving geometry of the
+    benchmark, an eighth of its batch): the one-pass build leaves bit for bit the ring the
+    separate downdate + copy + mark operators leave, wrap-around and chunk offsets included."""
+    from mac_attention_b200 import ops
+
+    ext = load_mac_prefill_update_cache_extension()
+    B, plen, H, D, M = 8, 32768, 32, 128, 2048
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(12)
+
+    def rnd(*shape):
+        return torch.randn(*shape, device=dev, generator=g)
+
+    src_q = rnd(B * plen, H, D).to(torch.bfloat16)
+    full = rnd(B * plen, H, D).to(torch.bfloat16)
+    band = rnd(B * plen, H, D).to(torch.bfloat16)
+    full_lse = rnd(B * plen, H) + 8
+    band_lse = (full_lse - torch.rand(B * plen, H, device=dev, generator=g) * 4 - 0.1) / 0.6931471805599453
+    req_ids = torch.tensor([5, 2, 7, 0, 3, 6, 1, 4], device=dev, dtype=torch.int32)
+    offsets = (torch.arange(B + 1, device=dev, dtype=torch.int32) * plen).contiguous()
+    lens = torch.full((B,), plen, device=dev, dtype=torch.int32)
+    L0 = torch.tensor([0, 777, 4096, 1, 2047, 100000, 31, 8191], device=dev, dtype=torch.int32)
+
+    def fresh():
+        return dict(q=torch.zeros(B, M, H, D, device=dev, dtype=torch.bfloat16),
+                    a=torch.zeros(B, M, H, D, device=dev, dtype=torch.bfloat16),
+                    l=torch.zeros(B, M, H, device=dev), p=torch.zeros(B, M, H, D, device=dev, dtype=torch.bfloat16),
+                    rl=L0.clone(), ready=torch.zeros(B, device=dev, dtype=torch.bool),
+                    ce=torch.full((B,), -1, device=dev, dtype=torch.int64),
+                    re=torch.arange(B, device=dev, dtype=torch.int64))
+
+    one = fresh()
+    ext.mac_prefill_downdate_update_cache(one["q"], one["a"], one["l"], one["rl"], req_ids, src_q, full,
+                                          full_lse, band, band_lse, offsets, lens, M, H, D, one["p"],
+                                          band_lse_scale=0.6931471805599453, ready=one["ready"],
+                                          cache_epoch=one["ce"], request_epoch=one["re"])
+    seq = fresh()
+    scaled = band_lse * 0.6931471805599453
+    band_work = band.clone()
+    ops.mac_update_then_downdate_bf16_inplace(full, full_lse, band_work, scaled)
+    ext.mac_prefill_update_cache(seq["q"], seq["a"], seq["l"], seq["rl"], req_ids, src_q, band_work,
+                                 scaled, offsets, lens, M, H, D, seq["p"])
+    ext.mac_mark_persistent_ready(seq["ready"], seq["ce"], seq["re"], req_ids)
+    torch.cuda.synchronize()
+    for k in ("q", "a", "p"):
+        assert torch.equal(one[k].view(torch.int16), seq[k].view(torch.int16)), k
+    assert torch.equal(one["l"].view(torch.int32), seq["l"].view(torch.int32))
+    for k in ("rl", "ready", "ce"):
+        assert torch.equal(one[k], seq[k]), k
+    # every ring slot was written: the last 2048 rows of each prompt, rotated by its offset
+    n = 3
+    slot = int((L0[n] + plen - 1) % M)
+    assert torch.equal(one["q"][int(req_ids[n]), slot], src_q[(n + 1) * plen - 1])
