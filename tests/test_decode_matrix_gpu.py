@@ -131,3 +131,28 @@ def test_randomised_matrix_against_the_reference_kernel(chunk):
         assert torch.equal(mine.case.query_cache, theirs.case.query_cache), tag
         a, b = mine.case.attn_cache.float().cpu(), theirs.case.attn_cache.float().cpu()
         assert O.rel_l2(a, b) < 2e-2, tag
+
+
+@pytest.mark.parametrize("F", [0, 16])
+def test_zero_window_is_handled(F):
+    """S = 0 (no trailing window: the ring row covers the whole context, current token
+    included) is not exercised anywhere in the reference, whose band producer would read
+    req_to_token[P]; here the current token always comes from out_cache_loc."""
+    rng = random.Random(77 + F)
+    for i in range(12):
+        spec = _draw(rng)
+        case = synth.make_decode_case(batch=spec["batch"], ctx=0, ctx_list=spec["ctxs"],
+                                      hq=spec["hq"], hkv=spec["hkv"], capacity=spec["capacity"],
+                                      page_size=spec["page"], seed=spec["seed"])
+        # the slot a real request has not filled yet: a wild pool row, so that reading it shows
+        for n in range(spec["batch"]):
+            case.req_to_token[int(case.req_ids[n]), int(case.past_lens[n])] = 0
+        synth.plant_matches(case, hit_fraction=0.6, noise=0.1, seed=spec["seed"] + 1,
+                            lag_hi=spec["capacity"])
+        cfg = O.DecodeConfig(max_context=2048, semantic_pos_ahead=0, front_sink_tokens=F,
+                             match_tile_slots=spec["mts"])
+        cu = run_cuda(case, cfg)
+        orc, orc_case = run_oracle(case, cfg)
+        assert_decisions_equal(cu, orc, spec["batch"])
+        assert_outputs_close(cu, orc, orc_case)
+        assert ops.query_status() == 0
