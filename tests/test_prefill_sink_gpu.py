@@ -75,16 +75,25 @@ def test_sink_exclusive_build_matches_oracle_and_direct_attention(spec):
     assert err.max() <= 6e-2 and err.mean() <= 1e-2, (float(err.max()), float(err.mean()))
 
 
-def test_decode_reuses_a_prefill_written_row_under_front_sink():
-    """Prefill with SINK_EXCLUDE, then one decode step whose pre-RoPE query repeats an
-    earlier prompt position: every head hits that row, and the merged output
-    (sink + reused prefix + band + tail) is full attention."""
+@pytest.mark.parametrize("F", [64, 0])
+def test_decode_reuses_a_prefill_written_row(F):
+    """Prefill through the one-pass build (sink-exclusive rows for F = 64, plain rows for
+    F = 0), then one decode step whose pre-RoPE query repeats an earlier prompt position:
+    every head hits that row, and the merged output (sink + reused prefix + band + tail)
+    is full attention."""
     ext = load_mac_prefill_update_cache_extension()
-    Hq, Hkv, S, F, M, L = 8, 2, 16, 64, 512, 400
+    Hq, Hkv, S, M, L = 8, 2, 16, 512, 400
     t = _prompts([L], [0], Hq, Hkv, S, F, M, seed=9)
     t.pop("want_o"), t.pop("want_l")
     gpu = {k: v.cuda() for k, v in t.items()}
-    _build(ext.mac_prefill_downdate_update_cache, gpu, M, Hq, S, F)
+    if F > 0:
+        _build(ext.mac_prefill_downdate_update_cache, gpu, M, Hq, S, F)
+    else:
+        ext.mac_prefill_downdate_update_cache(
+            gpu["q_cache"], gpu["attn_cache"], gpu["lse_cache"], gpu["request_length"],
+            gpu["req_ids"], gpu["src_q"], gpu["full_attn"], gpu["full_lse"], gpu["band_attn"],
+            gpu["band_lse"], gpu["offsets"], gpu["lens"], M, Hq, 128, gpu["q_post_cache"],
+            ready=gpu["ready"], cache_epoch=gpu["cache_epoch"], request_epoch=gpu["request_epoch"])
     torch.cuda.synchronize()
     assert bool(gpu["ready"][0])
     pstar = 300
