@@ -97,6 +97,19 @@ prefill_ring_copy_kernel(const PrefillParams pp) {
       int d1 = d0 + 1;
       if (d1 >= p.M) d1 -= p.M;
       const size_t s0 = static_cast<size_t>(base_off + start + i), s1 = s0 + 1;
+      // LSE rows of the pair: one float per thread, loaded before the row chunks so that
+      // all of a pass's loads are in flight together
+      float lse_v[2] = {0.f, 0.f};
+      const int lse_n = (two ? 2 : 1) * p.H;
+      const bool lse_small = lse_n <= 2 * static_cast<int>(blockDim.x);
+      if (lse_small) {
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const int idx = threadIdx.x + k * blockDim.x;
+          if (idx < lse_n)
+            lse_v[k] = p.src_lse[(idx >= p.H ? s1 : s0) * p.H + (idx >= p.H ? idx - p.H : idx)];
+        }
+      }
       for (size_t c = threadIdx.x; c < chunks; c += 2 * blockDim.x) {
         const size_t c2 = c + blockDim.x;
         const bool more = c2 < chunks;
@@ -136,8 +149,18 @@ prefill_ring_copy_kernel(const PrefillParams pp) {
           }
         }
       }
-      copy_row(lc + d0 * row_f32, ls + s0 * row_f32, row_f32);
-      if (two) copy_row(lc + d1 * row_f32, ls + s1 * row_f32, row_f32);
+      if (lse_small) {
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const int idx = threadIdx.x + k * blockDim.x;
+          if (idx < lse_n)
+            p.lse_cache[(static_cast<size_t>(req) * p.M + (idx >= p.H ? d1 : d0)) * p.H +
+                        (idx >= p.H ? idx - p.H : idx)] = lse_v[k];
+        }
+      } else {
+        copy_row(lc + d0 * row_f32, ls + s0 * row_f32, row_f32);
+        if (two) copy_row(lc + d1 * row_f32, ls + s1 * row_f32, row_f32);
+      }
     }
     return;
   }
