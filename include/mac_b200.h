@@ -258,7 +258,9 @@ int mac_b200_update_request_state(int32_t* req_len, int32_t* match_req_len,
  *                             E = max(pos + 1 - S, 0), is computed in the kernel
  *                             and subtracted too, so the ring row covers exactly
  *                             [min(F, E), E) as decode-written rows do and is
- *                             matchable at once.  Needs D = 128, F <= 128.
+ *                             matchable at once.  Needs D = 128, F <= 128, H / Hkv in
+ *                             {1, 2, 4, 8, 16}, sm_scale > 0 and 16-byte aligned tensors
+ *                             (else MAC_B200_EUNSUPPORTED / MAC_B200_EINVAL).
  */
 #define MAC_B200_SINK_NONE 0
 #define MAC_B200_SINK_UNMATCHABLE 1
