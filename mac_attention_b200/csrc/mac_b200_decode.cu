@@ -49,9 +49,9 @@ constexpr int kWarpRingBytes = kStages * kStageBytes;    // 24 KB
 constexpr int kRingBytes = kWarps * kWarpRingBytes;      // 192 KB
 constexpr int kMaxGroups = 4096;           // N * Hkv upper bound of one launch
 constexpr int kMaxHq = 128;
-constexpr int kOvhTok = 256;               // cost of opening a segment, in token equivalents
+constexpr int kOvhTok = 256;               // cost of opening a row, in token equivalents (G <= 4)
 constexpr int kMinPieceTok = 768;
-constexpr unsigned kTwoWavePieceTok = 16384;  // second wave of pieces only above this piece size
+constexpr int kMaxWaves = 4;                // most pieces per CTA the arena is sized for
 constexpr unsigned kFuseMaxCost = 8192;       // groups up to this cost are never split over pieces
 constexpr int kCombineRow = kD + 8;        // padded fp32 row of the cross-warp combine buffer
 constexpr int kSmemPerm = kMaxGroups * 2;              // u16 gperm[]
@@ -98,6 +98,8 @@ struct DecodeParams {
   int32_t F;             // front_sink_tokens clamped at 0
   int32_t tm_used;       // ceil(M / match_tile_slots)
   int32_t max_pieces;
+  int32_t force_waves;   // 0: pick by size; 1, 2 or 4: tuning override (MAC_B200_PIECE_WAVES)
+  int32_t ovh_tok;       // cost of opening a row, in token equivalents (kOvhTok unless overridden)
 };
 
 // ------------------------------------------------------------- small helpers
@@ -860,9 +862,9 @@ __device__ void phase_classify(const DecodeParams& p) {
       plan.bad = 0;
       plan.cls = (mode == 0) ? 2 : (eligible ? 1 : 0);
       int cost = 0;
-      if (my_sink > 0) cost += my_sink + kOvhTok;
-      if (band_tok > 0) cost += band_tok + kOvhTok;
-      if (kv_len > new_end) cost += kv_len - new_end + kOvhTok;
+      if (my_sink > 0) cost += my_sink + p.ovh_tok;
+      if (band_tok > 0) cost += band_tok + p.ovh_tok;
+      if (kv_len > new_end) cost += kv_len - new_end + p.ovh_tok;
       plan.cost = cost;
       p.ar.plan[g] = plan;
     }
@@ -956,12 +958,17 @@ __device__ void build_schedule(const DecodeParams& p, Schedule& sc, unsigned lon
   __syncthreads();
   sc.W = static_cast<uint32_t>(ccarry);
   // Wave-quantised piece count: as many pieces as keep a piece above
-  // kMinPieceTok; once there is a piece per CTA, exactly one or two per CTA.
+  // kMinPieceTok; once there is a piece per CTA, exactly one per CTA.
   unsigned pieces = sc.W / kMinPieceTok;
   if (pieces < 1) pieces = 1;
   if (pieces > gridDim.x) {
-    // one wave of pieces, or two when each piece still amortises its fixed cost
-    const unsigned waves = (sc.W / gridDim.x >= 2u * kTwoWavePieceTok) ? 2u : 1u;
+    // One piece per CTA.  Interleaved A/B runs on B200 (1, 2 and 4 waves of pieces with
+    // dynamic tickets) had one wave fastest in all but the very largest steps, where four
+    // waves won by under 1 %: a second piece costs a CTA another row opening and another
+    // set of partials to merge, which outweighs the better tail.  The override stays for
+    // tuning.
+    unsigned waves = 1u;
+    if (p.force_waves > 0) waves = static_cast<unsigned>(p.force_waves);
     pieces = waves * gridDim.x;
   }
   if (pieces > static_cast<unsigned>(p.max_pieces)) pieces = p.max_pieces;
@@ -977,7 +984,8 @@ struct RowGeom {
   uint32_t c;      // cost of the row (0 if empty)
 };
 
-__device__ __forceinline__ void group_rows(const GroupPlan& pl, uint32_t a0, RowGeom (&rows)[3]) {
+__device__ __forceinline__ void group_rows(const GroupPlan& pl, uint32_t a0, int ovh,
+                                           RowGeom (&rows)[3]) {
   rows[0].tok_begin = 0;          rows[0].len = pl.sink_hi;
   rows[1].tok_begin = pl.band_lo; rows[1].len = pl.new_end - pl.band_lo;
   rows[2].tok_begin = pl.new_end; rows[2].len = pl.kv_len - pl.new_end;
@@ -986,7 +994,7 @@ __device__ __forceinline__ void group_rows(const GroupPlan& pl, uint32_t a0, Row
   for (int r = 0; r < 3; ++r) {
     if (rows[r].len < 0) rows[r].len = 0;
     rows[r].a = a;
-    rows[r].c = rows[r].len > 0 ? static_cast<uint32_t>(rows[r].len + kOvhTok) : 0u;
+    rows[r].c = rows[r].len > 0 ? static_cast<uint32_t>(rows[r].len + ovh) : 0u;
     a += rows[r].c;
   }
 }
@@ -994,16 +1002,16 @@ __device__ __forceinline__ void group_rows(const GroupPlan& pl, uint32_t a0, Row
 // Token sub-range of a row that falls into cost interval [x0, x1).  The first
 // kOvhTok cost units of a row stand for the fixed cost of opening it; cut
 // points are rounded down to whole 16-token blocks so neighbours agree.
-__device__ __forceinline__ void segment_tokens(const RowGeom& row, uint32_t x0, uint32_t x1,
-                                               int& lo, int& hi) {
+__device__ __forceinline__ void segment_tokens(const RowGeom& row, int ovh, uint32_t x0,
+                                               uint32_t x1, int& lo, int& hi) {
   const uint32_t end = row.a + row.c;
   int l = 0, h = row.len;
   if (x0 > row.a) {
-    const int rel = static_cast<int>(x0 - row.a) - kOvhTok;
+    const int rel = static_cast<int>(x0 - row.a) - ovh;
     l = rel > 0 ? (rel & ~(kBlkTok - 1)) : 0;
   }
   if (x1 < end) {
-    const int rel = static_cast<int>(x1 - row.a) - kOvhTok;
+    const int rel = static_cast<int>(x1 - row.a) - ovh;
     h = rel > 0 ? (rel & ~(kBlkTok - 1)) : 0;
   }
   if (h > row.len) h = row.len;
@@ -1354,7 +1362,7 @@ __device__ void merge_group(const DecodeParams& p, const Schedule& sc, int v_idx
   const int n = g / a.Hkv, hkv = g - n * a.Hkv;
   const int hq = hkv * G + warp;
   RowGeom rows[3];
-  group_rows(pl, sc.cpre[v_idx], rows);
+  group_rows(pl, sc.cpre[v_idx], p.ovh_tok, rows);
 
   float4 o;
   float lse;
@@ -1491,7 +1499,7 @@ __device__ void phase_attend(const DecodeParams& p, uint8_t* smem) {
         continue;
       }
       RowGeom rows[3];
-      group_rows(pl, sc.cpre[v], rows);
+      group_rows(pl, sc.cpre[v], p.ovh_tok, rows);
       int expected = 0, done_here = 0;
 #pragma unroll 1
       for (int r = 0; r < 3; ++r) {
@@ -1501,7 +1509,7 @@ __device__ void phase_attend(const DecodeParams& p, uint8_t* smem) {
         expected += p_hi - p_lo + 1;
         if (piece < p_lo || piece > p_hi) continue;
         int t0, t1;
-        segment_tokens(rows[r], x0, x1, t0, t1);
+        segment_tokens(rows[r], p.ovh_tok, x0, x1, t0, t1);
         const int slot = piece + 3 * v + r;
         if (slot < p.ar.slots) {
           attend_segment(p, smem, n, hkv, t0, t1, r, slot);
@@ -1566,6 +1574,26 @@ std::mutex g_mu;
 DeviceState g_dev[64];
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Tuning override of the number of piece waves, read at every launch (0 = automatic).
+int piece_waves_override() {
+  const char* e = std::getenv("MAC_B200_PIECE_WAVES");
+  if (!e) return 0;
+  const int v = std::atoi(e);
+  return (v == 1 || v == 2 || v == 4) ? v : 0;
+}
+
+// Cost of opening a row in token equivalents; MAC_B200_OVH_TOK overrides it for tuning.
+// Measured on B200 (one piece per CTA): 256 is the flat optimum for G <= 4 (128 and 192 are
+// 10-30 % slower, 384 is 1-3 % slower), 384 for G = 8 (256 is 3-9 % slower there: a
+// fused small group moves twice the heads).
+int row_overhead_tokens(int G) {
+  const int dflt = G <= 4 ? kOvhTok : kOvhTok + 32 * (G - 4);
+  const char* e = std::getenv("MAC_B200_OVH_TOK");
+  if (!e) return dflt;
+  const int v = std::atoi(e);
+  return (v >= 16 && v <= 4096) ? (v & ~15) : dflt;
+}
 
 struct ArenaLayout {
   size_t ticket, garrive, plan, part_lse, part_o, total;
@@ -1649,7 +1677,7 @@ extern "C" int mac_b200_persistent_decode_bf16(const MacB200DecodeArgs* args, vo
     }
     int grid = ds.sm_count * ds.ctas_per_sm;
     if (a.grid_cap > 0 && a.grid_cap < grid) grid = a.grid_cap;
-    const int max_pieces = 2 * grid;
+    const int max_pieces = kMaxWaves * grid;
     const ArenaLayout L = arena_layout(static_cast<int>(NGll), G, max_pieces);
     if (L.total > ds.arena_bytes) {
       cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
@@ -1677,7 +1705,9 @@ extern "C" int mac_b200_persistent_decode_bf16(const MacB200DecodeArgs* args, vo
   p.NG = static_cast<int>(NGll);
   p.F = a.front_sink_tokens > 0 ? a.front_sink_tokens : 0;
   p.tm_used = (a.M + a.match_tile_slots - 1) / a.match_tile_slots;
-  p.max_pieces = 2 * st.last_grid;
+  p.max_pieces = kMaxWaves * st.last_grid;
+  p.force_waves = piece_waves_override();
+  p.ovh_tok = row_overhead_tokens(G);
   {
     float t = 2.0f * static_cast<float>(a.D);   // mac_decode_persistent.cu:5342, in float
     t = t * (1.0f - a.threshold);
@@ -1806,7 +1836,7 @@ extern "C" int mac_b200_persistent_decode_bf16_noalloc(const MacB200DecodeArgs* 
   }
   int grid = st.sm_count * st.ctas_per_sm;
   if (a.grid_cap > 0 && a.grid_cap < grid) grid = a.grid_cap;
-  const int max_pieces = 2 * grid;
+  const int max_pieces = kMaxWaves * grid;
   const ArenaLayout L = arena_layout(static_cast<int>(NGll), G, max_pieces);
   if (L.total > kNoAllocArenaBytes)
     return fail(MAC_B200_ESIZE,
@@ -1822,6 +1852,8 @@ extern "C" int mac_b200_persistent_decode_bf16_noalloc(const MacB200DecodeArgs* 
   p.F = a.front_sink_tokens > 0 ? a.front_sink_tokens : 0;
   p.tm_used = (a.M + a.match_tile_slots - 1) / a.match_tile_slots;
   p.max_pieces = max_pieces;
+  p.force_waves = piece_waves_override();
+  p.ovh_tok = row_overhead_tokens(G);
   {
     float t = 2.0f * static_cast<float>(a.D);
     t = t * (1.0f - a.threshold);
