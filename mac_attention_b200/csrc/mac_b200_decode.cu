@@ -1836,7 +1836,8 @@ extern "C" int mac_b200_persistent_decode_bf16_noalloc(const MacB200DecodeArgs* 
   }
   int grid = st.sm_count * st.ctas_per_sm;
   if (a.grid_cap > 0 && a.grid_cap < grid) grid = a.grid_cap;
-  const int max_pieces = kMaxWaves * grid;
+  // the fixed block is sized for two pieces per CTA (the kernel clamps a tuning override to it)
+  const int max_pieces = 2 * grid;
   const ArenaLayout L = arena_layout(static_cast<int>(NGll), G, max_pieces);
   if (L.total > kNoAllocArenaBytes)
     return fail(MAC_B200_ESIZE,
