@@ -50,7 +50,7 @@ constexpr int kRingBytes = kWarps * kWarpRingBytes;      // 192 KB
 constexpr int kMaxGroups = 4096;           // N * Hkv upper bound of one launch
 constexpr int kMaxHq = 128;
 constexpr int kOvhTok = 256;               // cost of opening a row, in token equivalents (G <= 4)
-constexpr int kMinPieceTok = 768;
+constexpr int kMinPieceTok = 1536;          // smallest streaming piece worth its fixed cost
 constexpr int kMaxWaves = 4;                // most pieces per CTA the arena is sized for
 constexpr unsigned kFuseMaxCost = 8192;       // groups up to this cost are never split over pieces
 constexpr int kCombineRow = kD + 8;        // padded fp32 row of the cross-warp combine buffer
@@ -100,6 +100,8 @@ struct DecodeParams {
   int32_t max_pieces;
   int32_t force_waves;   // 0: pick by size; 1, 2 or 4: tuning override (MAC_B200_PIECE_WAVES)
   int32_t ovh_tok;       // cost of opening a row, in token equivalents (kOvhTok unless overridden)
+  int32_t min_piece;     // smallest piece worth its fixed cost (kMinPieceTok unless overridden)
+  int32_t fuse_max;      // groups up to this cost are never split (kFuseMaxCost unless overridden)
 };
 
 // ------------------------------------------------------------- small helpers
@@ -948,18 +950,29 @@ __device__ void build_schedule(const DecodeParams& p, Schedule& sc, unsigned lon
   for (int base = 0; base < NG; base += kThreads) {
     const int v_idx = base + tid;
     unsigned long long c = 0;
-    if (v_idx < NG) c = static_cast<unsigned long long>(__ldcg(&p.ar.plan[sc.gperm[v_idx]].cost));
+    if (v_idx < NG) {
+      c = static_cast<unsigned long long>(__ldcg(&p.ar.plan[sc.gperm[v_idx]].cost));
+      // bits 40.. count the groups small enough to be finished in one fused pass
+      if (c > 0 && c <= static_cast<unsigned long long>(p.fuse_max)) c |= 1ull << 40;
+    }
     unsigned long long t;
     const unsigned long long ex = block_scan_excl(c, scan_sm, t) + ccarry;
     ccarry += t;
-    if (v_idx < NG) sc.cpre[v_idx] = static_cast<uint32_t>(ex);
+    if (v_idx < NG) sc.cpre[v_idx] = static_cast<uint32_t>(ex & 0xffffffffffull);
   }
+  const unsigned n_small = static_cast<unsigned>(ccarry >> 40);
+  ccarry &= 0xffffffffffull;
   if (tid == 0) sc.cpre[NG] = static_cast<uint32_t>(ccarry);
   __syncthreads();
   sc.W = static_cast<uint32_t>(ccarry);
   // Wave-quantised piece count: as many pieces as keep a piece above
   // kMinPieceTok; once there is a piece per CTA, exactly one per CTA.
-  unsigned pieces = sc.W / kMinPieceTok;
+  // ... but never fewer pieces than there are small groups (up to one per half such
+  // piece): those are latency-bound and want a CTA each, whatever their cost adds up to.
+  unsigned pieces = sc.W / static_cast<unsigned>(p.min_piece);
+  unsigned small_pieces = 2u * sc.W / static_cast<unsigned>(p.min_piece);
+  if (small_pieces > n_small) small_pieces = n_small;
+  if (pieces < small_pieces) pieces = small_pieces;
   if (pieces < 1) pieces = 1;
   if (pieces > gridDim.x) {
     // One piece per CTA.  Interleaved A/B runs on B200 (1, 2 and 4 waves of pieces with
@@ -1494,7 +1507,7 @@ __device__ void phase_attend(const DecodeParams& p, uint8_t* smem) {
       // A small group is never split: it belongs to the piece that holds its
       // first cost unit and is finished there in one fused pass.
       const uint32_t gcost = sc.cpre[v + 1] - sc.cpre[v];
-      if (gcost <= kFuseMaxCost && gcost <= 2u * sc.ps) {
+      if (gcost <= static_cast<uint32_t>(p.fuse_max) && gcost <= 2u * sc.ps) {
         if (sc.cpre[v] >= x0) attend_group_fused(p, smem, n, hkv, pl);
         continue;
       }
@@ -1581,6 +1594,14 @@ int piece_waves_override() {
   if (!e) return 0;
   const int v = std::atoi(e);
   return (v == 1 || v == 2 || v == 4) ? v : 0;
+}
+
+// Tuning overrides read at every launch.
+int env_int_or(const char* name, int dflt, int lo, int hi) {
+  const char* e = std::getenv(name);
+  if (!e) return dflt;
+  const int v = std::atoi(e);
+  return (v >= lo && v <= hi) ? v : dflt;
 }
 
 // Cost of opening a row in token equivalents; MAC_B200_OVH_TOK overrides it for tuning.
@@ -1708,6 +1729,8 @@ extern "C" int mac_b200_persistent_decode_bf16(const MacB200DecodeArgs* args, vo
   p.max_pieces = kMaxWaves * st.last_grid;
   p.force_waves = piece_waves_override();
   p.ovh_tok = row_overhead_tokens(G);
+  p.min_piece = env_int_or("MAC_B200_MIN_PIECE", kMinPieceTok, 64, 1 << 20);
+  p.fuse_max = env_int_or("MAC_B200_FUSE_MAX", static_cast<int>(kFuseMaxCost), 0, 1 << 24);
   {
     float t = 2.0f * static_cast<float>(a.D);   // mac_decode_persistent.cu:5342, in float
     t = t * (1.0f - a.threshold);
@@ -1855,6 +1878,8 @@ extern "C" int mac_b200_persistent_decode_bf16_noalloc(const MacB200DecodeArgs* 
   p.max_pieces = max_pieces;
   p.force_waves = piece_waves_override();
   p.ovh_tok = row_overhead_tokens(G);
+  p.min_piece = env_int_or("MAC_B200_MIN_PIECE", kMinPieceTok, 64, 1 << 20);
+  p.fuse_max = env_int_or("MAC_B200_FUSE_MAX", static_cast<int>(kFuseMaxCost), 0, 1 << 24);
   {
     float t = 2.0f * static_cast<float>(a.D);
     t = t * (1.0f - a.threshold);
