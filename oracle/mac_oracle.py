@@ -184,6 +184,42 @@ def decode_step(q_post, q_pre, k_buffer, v_buffer, req_to_token, req_ids, past_l
     return res
 
 
+def decide(q_pre, req_ids, past_lens, query_cache, lse_cache, cfg: DecodeConfig, *, hkv: int,
+           req_to_token_shape, cache_ready=None, cache_epoch=None, request_epoch=None):
+    """Per-head match decisions only (scan, threshold, synthetic override, front-sink
+    demotion; no attention), for shapes whose K/V would not fit the host: returns
+    ``(hit, match_slot, match_pos)`` int32 ``[N, Hq]``."""
+    for t in (q_pre, req_ids, past_lens, query_cache, lse_cache):
+        assert t.device.type == "cpu" and t.is_contiguous()
+    N, Hq, D = q_pre.shape
+    R, M = query_cache.shape[:2]
+    a = _abi.MacB200DecodeArgs()
+    a.N, a.Hq, a.Hkv, a.D, a.M, a.R = N, Hq, hkv, D, M, R
+    a.req_to_token_rows, a.req_to_token_stride = req_to_token_shape
+    a.ws_batch = N
+    a.max_match_tiles = (M + cfg.match_tile_slots - 1) // cfg.match_tile_slots
+    for name in ("max_context", "tile_tokens", "match_tile_slots", "semantic_pos_ahead",
+                 "front_sink_tokens", "gen_min_limit", "lookback_right", "candidate_mode",
+                 "threshold", "sm_scale", "debug_enabled", "bench_mode", "bench_hit_rate",
+                 "bench_hit_rate_std", "bench_skip_ratio", "bench_skip_ratio_std",
+                 "bench_match_lag_mean", "bench_match_lag_std", "bench_seed", "bench_miss_mask",
+                 "bench_layer_id", "mixed_group_fallback", "bench_exact_quota"):
+        setattr(a, name, getattr(cfg, name))
+    a.q_pre, a.req_ids, a.past_lens = _p(q_pre), _p(req_ids), _p(past_lens)
+    a.query_cache, a.lse_cache = _p(query_cache), _p(lse_cache)
+    keep = None
+    if cache_ready is not None and cache_ready.numel() > 0:
+        keep = cache_ready.view(torch.uint8) if cache_ready.dtype == torch.bool else cache_ready
+        a.cache_ready = _p(keep)
+        if cache_epoch is not None and request_epoch is not None and cache_epoch.numel() > 0:
+            a.cache_epoch, a.request_epoch = _p(cache_epoch), _p(request_epoch)
+    hit = torch.zeros(N, Hq, dtype=torch.int32)
+    mslot = torch.zeros(N, Hq, dtype=torch.int32)
+    mpos = torch.zeros(N, Hq, dtype=torch.int32)
+    lib().mac_oracle_decide(C.byref(a), _p(hit), _p(mslot), _p(mpos))
+    return hit, mslot, mpos
+
+
 def prefill_update_cache(q_cache, attn_cache, lse_cache, request_length, req_ids, src_q, src_attn,
                          src_lse, offsets, lens, capacity, num_heads, head_dim,
                          q_post_cache=None) -> None:

@@ -477,3 +477,41 @@ def test_decisions_identical_to_reference_cuda_kernel():
         theirs = run_cuda(case, cfg, ext=ref, poison=False)
         for idx in (3, 4, 5, 6, 7, 8, 9, 15):
             assert torch.equal(mine.ws[idx], theirs.ws[idx]), f"bench workspace[{idx}] differs"
+
+
+def test_decisions_at_serving_size_match_the_oracle():
+    """16 requests at context 126976 with a 2048-slot ring (the benchmark's geometry, a
+    quarter of its batch): planted matches per KV group plus rows within 1 % of the
+    threshold on either side.  The K/V pool (8.6 GB) stays on the GPU; the CPU oracle
+    restates the decisions alone from the ring and the queries."""
+    batch, ctx, hq, hkv, M = 16, 126976, 32, 8, 2048
+    case = synth.make_decode_case(batch=batch, ctx=ctx, hq=hq, hkv=hkv, capacity=M, page_size=16,
+                                  seed=12, device="cuda")
+    planted = synth.plant_matches(case, hit_fraction=0.7, noise=0.1, borderline_fraction=0.6,
+                                  seed=4, lag_lo=1, lag_hi=M, heads_per_draw=hq // hkv)
+    cfg = O.DecodeConfig(max_context=131072)
+    ext = load_mac_persistent_decode_extension()
+    ws = make_decode_workspace(batch, hq, hkv, M, cfg.max_context, cfg.tile_tokens,
+                               cfg.match_tile_slots, cfg.semantic_pos_ahead, 0)
+    out = torch.empty_like(case.q_post)
+    lse = torch.empty(batch, hq, device="cuda")
+    ring_before = case.query_cache.cpu()
+    lse_before = case.lse_cache.cpu()
+    e = torch.empty(0)
+    ext.mac_persistent_decode_bf16(case.q_post, case.q_pre, case.k, case.v, case.req_to_token,
+                                   case.req_ids, case.past_lens, case.out_cache_loc,
+                                   case.query_cache, case.attn_cache, case.lse_cache, out, lse, *ws,
+                                   *cfg.scalar_args(), case.query_cache, e, e, e)
+    torch.cuda.synchronize()
+    hit, mslot, mpos = O.decide(case.q_pre.cpu(), case.req_ids.cpu(), case.past_lens.cpu(),
+                                ring_before, lse_before, cfg, hkv=hkv,
+                                req_to_token_shape=tuple(case.req_to_token.shape))
+    got_hit = ws[3][:batch].cpu()
+    assert torch.equal(got_hit, hit)
+    sel = hit.bool()
+    assert torch.equal(ws[4][:batch].cpu()[sel], mslot[sel])
+    assert torch.equal(ws[5][:batch].cpu()[sel], mpos[sel])
+    assert planted.sum() > 0 and bool((got_hit.bool() | ~planted).all())   # every planted head hits
+    assert int(got_hit.sum()) > int(planted.sum())                         # and some borderline rows do
+    assert torch.isfinite(out.float()).all()
+    _status_clean()
