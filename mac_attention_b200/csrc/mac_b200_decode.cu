@@ -1363,107 +1363,106 @@ __device__ __forceinline__ void write_output(const MacB200DecodeArgs& a, int n, 
   if (lane == 0 && a.optional_lse) a.optional_lse[ho] = ok ? lse : -INFINITY;
 }
 
-// State of one row of a group from the np >= 2 partials its pieces left in the arena
-// (slots slot0 .. slot0 + np - 1), for the head this warp owns; lane owns 4 dims.  Two
-// passes so that the loads do not wait on one another: every LSE first (a lane per
-// piece), then the weighted rows two at a time.  A long context on a small batch spans
-// dozens of pieces; walking them one dependent load after the other was a tail of tens
-// of microseconds.  Out of line, scalar arguments only: the streaming kernel's register
-// allocation must not feel it.
-struct RowState {
-  float4 o;
-  float lse;
-};
-__device__ __noinline__ RowState merge_row_partials(const float* part_lse, const float* part_o,
-                                                    long long slot0, int np, int G, int head) {
-  const int lane = threadIdx.x & 31;
-  RowState rs;
-  rs.o = make_float4(0.f, 0.f, 0.f, 0.f);
-  rs.lse = -INFINITY;
-  float mx = -INFINITY;
-  for (int b = lane; b < np; b += 32) {
-    const float l2 = __ldcg(part_lse + (slot0 + b) * 8 + head);
-    if (isfinite(l2)) mx = fmaxf(mx, l2);
-  }
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-  if (mx == -INFINITY) return rs;
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  float den = 0.f;
-  for (int base = 0; base < np; base += 32) {
-    float w_mine = 0.f;
-    if (base + lane < np) {
-      const float l2 = __ldcg(part_lse + (slot0 + base + lane) * 8 + head);
-      if (isfinite(l2)) w_mine = expf(l2 - mx);
-    }
-    den += w_mine;
-    const int cnt = min(32, np - base);
-    for (int j0 = 0; j0 < cnt; j0 += 2) {
-      float w[2];
-      float4 o2[2];
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        w[u] = __shfl_sync(0xffffffffu, w_mine, (j0 + u) & 31);
-        if (j0 + u >= cnt) w[u] = 0.f;
-        if (w[u] != 0.f)   // warp-uniform
-          o2[u] = __ldcg(reinterpret_cast<const float4*>(
-              part_o + ((slot0 + base + j0 + u) * G + head) * kD + lane * 4));
-      }
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        if (w[u] != 0.f) {
-          acc.x = fmaf(w[u], o2[u].x, acc.x); acc.y = fmaf(w[u], o2[u].y, acc.y);
-          acc.z = fmaf(w[u], o2[u].z, acc.z); acc.w = fmaf(w[u], o2[u].w, acc.w);
-        }
-      }
-    }
-  }
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) den += __shfl_xor_sync(0xffffffffu, den, off);
-  const float inv = 1.0f / den;   // den >= 1: the piece that holds the maximum has weight 1
-  rs.o = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
-  rs.lse = mx + logf(den);
-  return rs;
-}
+// Runs in the CTA that retired the group's last segment (all 256 threads): prefix
+// state (+) band partials -> ring row; (+) sink (+) tail partials -> output.  Warp h < G
+// owns head h, lane owns 4 dims.  Order of operations: DEC.cu:4346-4365, 4485-4520.
+//
+// A row that spans several pieces left one partial per piece in the arena.  A long
+// context on a small batch spans dozens; loading them one after the other (each load
+// an L2 round trip) was a tail of tens of microseconds.  So the partial rows of up to
+// kMergeChunk pieces at a time are copied into the idle K/V ring in shared memory by
+// the whole CTA (cp.async: as many loads in flight as there are rows), and each head's
+// warp then accumulates them from shared memory with softmax weights taken from all of
+// the row's LSEs at once.
+constexpr int kMergeChunk = 32;
+constexpr int kMergeStagedMin = 6;   // rows with fewer partials are merged by direct loads
+static_assert(kMergeChunk * 8 * kRowBytes * 2 <= kRingBytes, "merge staging must fit the ring");
 
-// Runs in the CTA that retired the group's last segment: prefix state (+) band
-// partials -> ring row; (+) sink (+) tail partials -> output.  Warp h owns
-// head h, lane owns 4 dims.  Order of operations: DEC.cu:4346-4365, 4485-4520.
-__device__ void merge_group(const DecodeParams& p, const Schedule& sc, int v_idx, int g,
-                            const GroupPlan& pl) {
+__device__ void merge_group(const DecodeParams& p, uint8_t* smem, const Schedule& sc, int v_idx,
+                            int g, const GroupPlan& pl) {
   const MacB200DecodeArgs& a = p.a;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (warp >= p.G) return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int G = p.G;
+  const bool active = warp < G;
   const int n = g / a.Hkv, hkv = g - n * a.Hkv;
-  const int hq = hkv * G + warp;
+  const int hq = hkv * G + (active ? warp : 0);
   RowGeom rows[3];
   group_rows(pl, sc.cpre[v_idx], p.ovh_tok, rows);
 
-  float4 o;
-  float lse;
-  load_prefix_state(a, n, hq, o, lse);
-  auto merge_row = [&](int r) {
+  float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+  float lse = -INFINITY;
+  if (active) load_prefix_state(a, n, hq, o, lse);
+  const uint32_t stage_u32 = smem_u32(smem);
+  auto merge_row = [&](int r) {     // control flow is uniform over the CTA
     if (rows[r].c == 0) return;
     int p_lo, p_hi;
     row_piece_span(rows[r], sc.ps, p_lo, p_hi);
+    const int np = p_hi - p_lo + 1;
     const int64_t slot0 = static_cast<int64_t>(p_lo) + 3 * v_idx + r;
-    if (p_hi == p_lo) {
-      const float l2 = __ldcg(p.ar.part_lse + slot0 * 8 + warp);
-      if (!isfinite(l2)) return;
-      const float4 o2 = __ldcg(reinterpret_cast<const float4*>(
-          p.ar.part_o + (slot0 * G + warp) * kD + lane * 4));
-      merge_state(o, lse, o2, l2);
+    if (np < kMergeStagedMin) {   // a few partials: straight loads, no barrier
+      if (active) {
+        for (int b = 0; b < np; ++b) {
+          const float l2 = __ldcg(p.ar.part_lse + (slot0 + b) * 8 + warp);
+          if (!isfinite(l2)) continue;
+          const float4 o2 = __ldcg(reinterpret_cast<const float4*>(
+              p.ar.part_o + ((slot0 + b) * G + warp) * kD + lane * 4));
+          merge_state(o, lse, o2, l2);
+        }
+      }
       return;
     }
-    const RowState rs = merge_row_partials(p.ar.part_lse, p.ar.part_o, slot0, p_hi - p_lo + 1, G, warp);
-    merge_state(o, lse, rs.o, rs.lse);
+    float mx = -INFINITY;
+    if (active) {
+      for (int b = lane; b < np; b += 32) {
+        const float l2 = __ldcg(p.ar.part_lse + (slot0 + b) * 8 + warp);
+        if (isfinite(l2)) mx = fmaxf(mx, l2);
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    }
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float den = 0.f;
+    const int units_per_piece = G * (kRowBytes * 2 / 16);   // 16-byte units of one piece's G fp32 rows
+    for (int base = 0; base < np; base += kMergeChunk) {
+      const int cnt = min(kMergeChunk, np - base);
+      const char* src = reinterpret_cast<const char*>(p.ar.part_o + (slot0 + base) * G * kD);
+      for (int u = tid; u < cnt * units_per_piece; u += kThreads)
+        cp_async16(stage_u32 + u * 16, src + static_cast<size_t>(u) * 16, 16);
+      cp_async_commit();
+      float w_mine = 0.f;
+      if (active && lane < cnt && mx != -INFINITY) {
+        const float l2 = __ldcg(p.ar.part_lse + (slot0 + base + lane) * 8 + warp);
+        if (isfinite(l2)) w_mine = expf(l2 - mx);
+      }
+      den += w_mine;
+      cp_async_wait<0>();
+      __syncthreads();
+      if (active) {
+        const float4* rowp = reinterpret_cast<const float4*>(smem) + warp * 32 + lane;
+        for (int j = 0; j < cnt; ++j) {
+          const float w = __shfl_sync(0xffffffffu, w_mine, j);
+          if (w != 0.f) {   // warp-uniform
+            const float4 v = rowp[j * G * 32];
+            acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y);
+            acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
+          }
+        }
+      }
+      __syncthreads();   // the next chunk overwrites the staging
+    }
+    if (active && mx != -INFINITY) {
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) den += __shfl_xor_sync(0xffffffffu, den, off);
+      const float inv = 1.0f / den;   // den >= 1: the piece that holds the maximum has weight 1
+      merge_state(o, lse, make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv),
+                  mx + logf(den));
+    }
   };
   merge_row(1);
-  write_ring_row(a, n, hq, o, lse);
+  if (active) write_ring_row(a, n, hq, o, lse);
   merge_row(0);
   merge_row(2);
-  write_output(a, n, hq, o, lse);
+  if (active) write_output(a, n, hq, o, lse);
 }
 
 // A group whose three rows all fall inside one piece is finished by this CTA
@@ -1608,7 +1607,7 @@ __device__ void phase_attend(const DecodeParams& p, uint8_t* smem) {
       __syncthreads();
       if (sh_last) {
         __threadfence();
-        merge_group(p, sc, v, g, pl);
+        merge_group(p, smem, sc, v, g, pl);
       }
     }
   }
