@@ -515,3 +515,22 @@ def test_decisions_at_serving_size_match_the_oracle():
     assert int(got_hit.sum()) > int(planted.sum())                         # and some borderline rows do
     assert torch.isfinite(out.float()).all()
     _status_clean()
+
+
+@pytest.mark.parametrize("hq,hkv", [(16, 2), (8, 2), (8, 8)], ids=["gqa8", "gqa4", "mha"])
+def test_long_context_few_groups_outputs_match_oracle(hq, hkv):
+    """Two requests with tens of thousands of tokens and only a handful of KV groups: every
+    full-attention group is cut into dozens of pieces, so its partials take the staged
+    (shared-memory) merge.  Outputs, ring rows and LSEs against the CPU oracle."""
+    case = synth.make_decode_case(batch=2, ctx=0, ctx_list=[40000, 23000], hq=hq, hkv=hkv,
+                                  capacity=256, page_size=16, seed=21)
+    synth.plant_matches(case, hit_fraction=0.4, noise=0.1, seed=8, lag_hi=200,
+                        heads_per_draw=hq // hkv)
+    cfg = O.DecodeConfig(max_context=65536, semantic_pos_ahead=256)
+    cu = run_cuda(case, cfg)
+    orc, orc_case = run_oracle(case, cfg)
+    assert_decisions_equal(cu, orc, 2)
+    assert_outputs_close(cu, orc, orc_case)
+    assert int(cu.ws[22][0]) >= 40          # pieces: far more than groups
+    assert 0 < int(orc.head_hit.sum()) < orc.head_hit.numel()
+    _status_clean()
