@@ -1371,12 +1371,14 @@ __device__ __forceinline__ void write_output(const MacB200DecodeArgs& a, int n, 
 // context on a small batch spans dozens; loading them one after the other (each load
 // an L2 round trip) was a tail of tens of microseconds.  So the partial rows of up to
 // kMergeChunk pieces at a time are copied into the idle K/V ring in shared memory by
-// the whole CTA (cp.async: as many loads in flight as there are rows), and each head's
+// the whole CTA (cp.async, double-buffered: as many loads in flight as there are rows), and each head's
 // warp then accumulates them from shared memory with softmax weights taken from all of
 // the row's LSEs at once.
 constexpr int kMergeChunk = 32;
 constexpr int kMergeStagedMin = 6;   // rows with fewer partials are merged by direct loads
-static_assert(kMergeChunk * 8 * kRowBytes * 2 <= kRingBytes, "merge staging must fit the ring");
+static_assert(2 * kMergeChunk * 4 * kRowBytes * 2 <= kRingBytes &&
+                  2 * (kMergeChunk / 2) * 8 * kRowBytes * 2 <= kRingBytes,
+              "two merge staging buffers must fit the ring");
 
 __device__ void merge_group(const DecodeParams& p, uint8_t* smem, const Schedule& sc, int v_idx,
                             int g, const GroupPlan& pl) {
@@ -1423,22 +1425,34 @@ __device__ void merge_group(const DecodeParams& p, uint8_t* smem, const Schedule
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float den = 0.f;
     const int units_per_piece = G * (kRowBytes * 2 / 16);   // 16-byte units of one piece's G fp32 rows
-    for (int base = 0; base < np; base += kMergeChunk) {
-      const int cnt = min(kMergeChunk, np - base);
+    // two staging buffers of `chunk` pieces each (64 KB apiece): the next chunk is in
+    // flight while this one is accumulated
+    const int chunk = G <= 4 ? kMergeChunk : kMergeChunk / 2;
+    const uint32_t buf_bytes = static_cast<uint32_t>(chunk) * units_per_piece * 16;
+    auto stage = [&](int base, int which) {
+      const int cnt = min(chunk, np - base);
       const char* src = reinterpret_cast<const char*>(p.ar.part_o + (slot0 + base) * G * kD);
       for (int u = tid; u < cnt * units_per_piece; u += kThreads)
-        cp_async16(stage_u32 + u * 16, src + static_cast<size_t>(u) * 16, 16);
+        cp_async16(stage_u32 + which * buf_bytes + u * 16, src + static_cast<size_t>(u) * 16, 16);
       cp_async_commit();
+    };
+    stage(0, 0);
+    int which = 0;
+    for (int base = 0; base < np; base += chunk, which ^= 1) {
+      const int cnt = min(chunk, np - base);
+      const bool more = base + chunk < np;
+      if (more) stage(base + chunk, which ^ 1);
       float w_mine = 0.f;
       if (active && lane < cnt && mx != -INFINITY) {
         const float l2 = __ldcg(p.ar.part_lse + (slot0 + base + lane) * 8 + warp);
         if (isfinite(l2)) w_mine = expf(l2 - mx);
       }
       den += w_mine;
-      cp_async_wait<0>();
+      if (more) cp_async_wait<1>(); else cp_async_wait<0>();
       __syncthreads();
       if (active) {
-        const float4* rowp = reinterpret_cast<const float4*>(smem) + warp * 32 + lane;
+        const float4* rowp =
+            reinterpret_cast<const float4*>(smem + which * buf_bytes) + warp * 32 + lane;
         for (int j = 0; j < cnt; ++j) {
           const float w = __shfl_sync(0xffffffffu, w_mine, j);
           if (w != 0.f) {   // warp-uniform
@@ -1448,7 +1462,7 @@ __device__ void merge_group(const DecodeParams& p, uint8_t* smem, const Schedule
           }
         }
       }
-      __syncthreads();   // the next chunk overwrites the staging
+      __syncthreads();   // this buffer is refilled two chunks from now
     }
     if (active && mx != -INFINITY) {
 #pragma unroll
