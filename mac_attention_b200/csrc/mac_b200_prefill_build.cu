@@ -11,6 +11,8 @@
 // the rows bound for the ring are downdated on their way into it: each
 // (row, head) state is read once from the full-prefix and band tensors and
 // written once, to the ring.  The band tensors are left as they were.
+#include <cstdlib>
+
 #include "mac_b200_common.h"
 #include "mac_b200_state_math.cuh"
 
@@ -671,9 +673,26 @@ extern "C" int mac_b200_prefill_downdate_update_cache(const MacB200PrefillBuildA
     const int TG = 16 / G;
     const int max_tiles = ((p.M < 1 ? 1 : p.M) + TG - 1) / TG;
     const int pairs = p.B * a.Hkv;
-    int slices = (4 * sms + pairs - 1) / pairs;               // about four CTAs per SM in total
+    // Slices per (request, KV head): between three and eight CTAs per SM in all, and among
+    // those the count that leaves the last wave fullest (fewest slices on a tie: every CTA
+    // reloads the sink K/V).  MAC_B200_SINK_SLICES overrides it for tuning.
     const int max_slices = (max_tiles + kSxWarps - 1) / kSxWarps;
-    if (slices > max_slices) slices = max_slices;
+    int lo = (3 * sms + pairs - 1) / pairs, hi = (8 * sms + pairs - 1) / pairs;
+    if (lo < 1) lo = 1;
+    if (hi > max_slices) hi = max_slices;
+    if (lo > hi) lo = hi;
+    int slices = lo;
+    double best = -1.0;
+    for (int sl = lo; sl <= hi; ++sl) {
+      const long long total = static_cast<long long>(sl) * pairs;
+      const long long waves = (total + sms - 1) / sms;
+      const double eff = static_cast<double>(total) / static_cast<double>(waves * sms);
+      if (eff > best + 1e-9) { best = eff; slices = sl; }
+    }
+    if (const char* e = std::getenv("MAC_B200_SINK_SLICES")) {
+      const int v = std::atoi(e);
+      if (v >= 1 && v <= max_slices) slices = v;
+    }
     if (slices < 1) slices = 1;
     dim3 grid(slices, a.Hkv, p.B);
     kernel<<<grid, kSxThreads, kSxSmemBytes, stream>>>(a);
