@@ -158,3 +158,41 @@ def test_zero_window_is_handled(F):
         assert_decisions_equal(cu, orc, spec["batch"])
         assert_outputs_close(cu, orc, orc_case)
         assert ops.query_status() == 0
+
+
+@pytest.mark.parametrize("chunk", range(3))
+def test_randomised_parity_matrix_medium_contexts(chunk):
+    """Contexts of thousands to tens of thousands of tokens on one to four requests: rows
+    are cut into many pieces, so split-KV partials, the direct and the staged group merge,
+    fused small groups and mixed groups all meet in one step."""
+    rng = random.Random(9000 + chunk + 100000 * SEED_BASE)
+    for i in range(10):
+        spec = _draw(rng)
+        spec["batch"] = rng.randint(1, 4)
+        spec["ctxs"] = [rng.choice([rng.randint(3000, 9000), rng.randint(9000, 40000), rng.randint(50, 900)])
+                        for _ in range(spec["batch"])]
+        spec["capacity"] = rng.choice([64, 256, 512])
+        case = synth.make_decode_case(batch=spec["batch"], ctx=0, ctx_list=spec["ctxs"],
+                                      hq=spec["hq"], hkv=spec["hkv"], capacity=spec["capacity"],
+                                      page_size=spec["page"], seed=spec["seed"])
+        synth.plant_matches(case, hit_fraction=spec["hit"], noise=0.1,
+                            borderline_fraction=spec["borderline"], seed=spec["seed"] + 1,
+                            lag_hi=spec["capacity"], threshold=spec["threshold"])
+        if spec["gate"]:
+            synth.add_readiness_gate(case, not_ready_fraction=0.3, stale_fraction=0.2,
+                                     seed=spec["seed"] + 2)
+        cfg = O.DecodeConfig(max_context=65536, semantic_pos_ahead=spec["S"],
+                             front_sink_tokens=spec["F"], match_tile_slots=spec["mts"],
+                             threshold=spec["threshold"], bench_mode=spec["bench"],
+                             bench_hit_rate=spec["hit"],
+                             bench_match_lag_mean=float(min(64, spec["capacity"])),
+                             bench_seed=spec["seed"] % 97)
+        tag = f"chunk {chunk} case {i}: {spec}"
+        try:
+            cu = run_cuda(case, cfg)
+            orc, orc_case = run_oracle(case, cfg)
+            assert_decisions_equal(cu, orc, spec["batch"])
+            assert_outputs_close(cu, orc, orc_case)
+        except AssertionError as exc:
+            raise AssertionError(f"{tag}\n{exc}") from exc
+        assert ops.query_status() == 0, tag
