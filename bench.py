@@ -511,8 +511,12 @@ def run_reference_arm(args):
         "value": cb["value"], "unit": "us", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": cb["value"] / 1e3, "higher_is_better": False,
         "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-        "config": {"workload": f"GQA-{args.hq // args.hkv} MAC decode step, Hq{args.hq}/Hkv{args.hkv}"
-                               f"/D128, batch {args.batch}, context {args.ctx}, hit {args.hit}"},
+        "config": {
+            "workload": f"GQA-{args.hq // args.hkv} MAC decode step, Hq{args.hq}/Hkv{args.hkv}/D128, "
+                        f"batch {args.batch} per GPU, context {args.ctx}, per-head hit fraction {args.hit} "
+                        f"(reference synthetic_head decisions, lag {LAG}), ring M={args.capacity}, "
+                        f"S={SEM}, F={args.front_sink}, paged KV page {args.page_size}",
+            "batch": args.batch, "context": args.ctx, "hit_fraction": args.hit},
         "cpu_baseline": cb,
         "e2e": {"value": cb["value"], "unit": "us", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
