@@ -96,3 +96,31 @@ def test_kv_head_shards_reassemble_the_unsharded_step():
     assert torch.equal(sharding.gather_heads(rings, dim=2), full_case.attn_cache)
     with pytest.raises(ValueError):
         sharding.head_slices(16, 4, 3, 0)
+
+
+def test_one_pass_prefill_build_host_checks_need_no_device():
+    """No-op paths return before touching the device; wrong placements and shapes raise the
+    operator's messages from the host-side checks."""
+    import pytest
+
+    from mac_attention_b200 import load_mac_prefill_update_cache_extension
+
+    ext = load_mac_prefill_update_cache_extension()
+    assert hasattr(ext, "mac_prefill_downdate_update_cache")
+    R, M, H, D, rows = 2, 4, 2, 128, 3
+    t = dict(q=torch.zeros(R, M, H, D, dtype=torch.bfloat16), a=torch.zeros(R, M, H, D, dtype=torch.bfloat16),
+             l=torch.zeros(R, M, H), rl=torch.zeros(R, dtype=torch.int32),
+             ids=torch.zeros(1, dtype=torch.int32), sq=torch.zeros(rows, H, D, dtype=torch.bfloat16),
+             fl=torch.zeros(rows, H), off=torch.tensor([0, rows], dtype=torch.int32),
+             ln=torch.tensor([rows], dtype=torch.int32))
+
+    def call(capacity=M, ids=None):
+        ext.mac_prefill_downdate_update_cache(t["q"], t["a"], t["l"], t["rl"],
+                                              t["ids"] if ids is None else ids, t["sq"], t["sq"],
+                                              t["fl"], t["sq"], t["fl"], t["off"], t["ln"],
+                                              capacity, H, D, None)
+
+    call(capacity=0)                                      # silent no-op, as the reference's copy
+    call(ids=torch.zeros(0, dtype=torch.int32))           # empty batch
+    with pytest.raises(RuntimeError, match="must be CUDA"):
+        call()
