@@ -211,9 +211,9 @@ prefill_downdate_ring_kernel(const MacB200PrefillBuildArgs a) {
 // It is a small dense problem -- 16 query rows x F <= 128 keys x D = 128 per
 // warp tile -- done here on the tensor cores (mma.sync m16n8k16, bf16 in, fp32
 // accumulate) straight from shared memory, inside the pass that also streams
-// the row through the two downdates into the ring.  The kernel stays bound by
-// the HBM stream of the rows, the sink K/V of a (request, KV head) are read
-// once per CTA.
+// the row through the two downdates into the ring.  Its HBM traffic is the
+// stream of the rows alone; the sink K/V of a (request, KV head) are read once
+// per CTA.
 //
 // CTA = (slice of a request's ring rows, one KV head); 8 independent warps.  A
 // warp tile is 16 MMA rows = 16/G consecutive tokens x the G query heads of the
