@@ -1,17 +1,24 @@
 #!/usr/bin/env python3
 """Benchmark of the fused MAC decode step (one JSON line on stdout).
 
-Metric: microseconds per decode step under CUDA-graph replay, with the
-algorithmic HBM GB/s it corresponds to, on the reference's headline workload:
-GQA-4 (Hq 32 / Hkv 8 / D 128), bf16 paged KV (page 16), batch 64, context
-126976, ring capacity 2048, semantic_pos_ahead 256, per-query-head hit fraction
-0.9 chosen by the reference's own synthetic decision hash (its published curves
-were measured the same way), match lag 64.  Inputs are seeded synthetic tensors
-of those shapes (``mac_attention_b200/synth.py``).
+Metric: microseconds per decode step under CUDA-graph replay, with the HBM GB/s
+it corresponds to, on the reference's headline workload: GQA-4 (Hq 32 / Hkv 8 /
+D 128), bf16 paged KV (page 16), batch 64, context 126976, ring capacity 2048,
+semantic_pos_ahead 256, per-query-head hit fraction 0.9 chosen by the
+reference's own synthetic decision hash (its published curves were measured the
+same way), match lag 64.  Inputs are seeded synthetic tensors of those shapes
+(``mac_attention_b200/synth.py``).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W]           this library
-    python bench.py --impl reference ...                           CPU baseline arm
-    python bench.py --sweep ...                                    hit/batch/context table
+    python bench.py [--gpus N] [--steps K] [--warmup W]     this library
+    python bench.py --impl reference ...                     the reference's own CUDA kernel
+    python bench.py --sweep ...                              hit/batch/context table
+    python bench.py --config4 ...                            mixed serving step + prefill rows
+
+The line of this library also carries: ``parity`` (the timed tensors checked
+against the CPU oracle on a sample of requests), ``gpu_baselines`` (FlashInfer
+full decode with and without tensor cores and the reference kernel on the same
+tensors), ``config3`` (the Llama-70B attention shape split by KV head over the
+N ranks), ``cpu_baseline`` and ``real_scan``.
 
 With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank
 owns its own requests, KV pool and ring (the path shards by request with no
@@ -38,6 +45,7 @@ LAG = 64
 # dram__bytes_read+write / bytes requested by the kernel, from the ncu captures
 # summarised under profiles/ (small cases, scaled by the units processed)
 NCU_TRAFFIC_RATIO = 1.02
+METRIC = "us_per_decode_step_cuda_graph_replay"
 
 
 def parse_args():
@@ -55,11 +63,15 @@ def parse_args():
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--capacity", type=int, default=CAPACITY)
     ap.add_argument("--bench-mode", type=int, default=1)
-    ap.add_argument("--sweep", action="store_true", help="write the hit/batch/context table")
-    ap.add_argument("--sweep-out", default=str(ROOT / "gpurun_out" / "sweep.json"))
-    ap.add_argument("--baselines", default="", help="comma list for --sweep: flashinfer,refkernel")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--cpu-sample-requests", type=int, default=4)
+    ap.add_argument("--sweep", action="store_true", help="print the hit/batch/context table")
+    ap.add_argument("--sweep-out", default=None, help="also write the sweep rows to this file")
+    ap.add_argument("--baselines", default="",
+                    help="comma list for --sweep/--config4: flashinfer,flashinfer_tc,refkernel")
+    ap.add_argument("--no-cpu-baseline", action="store_true",
+                    help="skip the oracle legs (parity sample and cpu_baseline)")
+    ap.add_argument("--no-gpu-baselines", action="store_true")
+    ap.add_argument("--no-config3", action="store_true")
+    ap.add_argument("--parity-requests", type=int, default=6)
     ap.add_argument("--shard", default="request", choices=["request", "kv_head"])
     ap.add_argument("--config4", action="store_true",
                     help="mixed serving step with readiness gating + prefill ring build timing")
@@ -67,18 +79,39 @@ def parse_args():
                     help="with --config4: run every row, or only the prefill ring-build rows")
     ap.add_argument("--prompt-len", type=int, default=32768,
                     help="with --config4: prompt length of the prefill ring-build rows")
-    ap.add_argument("--config4-out", default=str(ROOT / "gpurun_out" / "config4.json"))
+    ap.add_argument("--config4-out", default=None, help="also write the config-4 rows to this file")
     return ap.parse_args()
 
 
 # --------------------------------------------------------------------------- workload
-def alg_bytes(ws, batch, hq, hkv, F, capacity, past_lens, eligible=True):
-    """Algorithmic bytes of one step from the decision arrays the kernel reports:
-    K/V rows actually needed (512 B per token and KV head), the ring scan (full
-    256 B rows of every candidate slot), reused prefix states, ring write,
-    output, queries and the page-table entries."""
-    import torch
+def workload_config(args, world, hq=None, hkv=None, shard=None):
+    """What is measured, in the same words for every arm of the benchmark."""
+    hq = args.hq if hq is None else hq
+    hkv = args.hkv if hkv is None else hkv
+    shard = args.shard if shard is None else shard
+    return {
+        "workload": f"GQA-{hq // hkv} MAC decode step, Hq{hq}/Hkv{hkv}/D128, "
+                    f"batch {args.batch} per GPU, context {args.ctx}, per-head hit fraction {args.hit} "
+                    f"(reference synthetic_head decisions, lag {LAG}), ring M={args.capacity}, "
+                    f"S={SEM}, F={args.front_sink}, paged KV page {args.page_size}",
+        "batch": args.batch, "context": args.ctx, "hit_fraction": args.hit,
+        "hq": hq, "hkv": hkv, "ring_capacity": args.capacity, "front_sink": args.front_sink,
+        "page_size": args.page_size,
+        "sharding": f"{shard} x{world}, no collective in attention",
+        "l2": "inputs larger than L2 (K/V + ring streamed per step >> 126 MB)",
+    }
 
+
+def alg_bytes(ws, batch, hq, hkv, F, capacity, past_lens, eligible=True):
+    """Bytes of one step from the decision arrays the kernel reports: K/V rows
+    actually needed (512 B per token and KV head), the ring scan, reused prefix
+    states, ring write, output, queries and the page-table entries.
+
+    ``total`` counts full 256 B ring rows for every scanned slot (the convention
+    of the reference's own accounting); ``requested`` counts what this kernel
+    asks the memory system for: the 128 B probe half of every row (the second
+    half is fetched only for rows that survive the probe, a handful per step).
+    ``per_row`` is ``requested`` split by batch row."""
     from mac_attention_b200 import workspace as W
 
     head_hit = ws[W.HEAD_HIT][:batch].cpu()
@@ -86,28 +119,33 @@ def alg_bytes(ws, batch, hq, hkv, F, capacity, past_lens, eligible=True):
     new_end = ws[W.HEAD_NEW_END][:batch].cpu()
     mode = ws[W.GROUP_MODE][:batch].cpu()
     G = hq // hkv
-    kv = 0
-    pt = 0
+    kv = pt = scan = 0
+    per_row = []
     for n in range(batch):
         P = int(past_lens[n])
         kv_len = P + 1
         ne = int(new_end[n, 0])
-        distinct = 0
+        distinct = row_kv = 0
         for g in range(hkv):
             if int(mode[n, g]) != 0:
                 t = kv_len
             else:
                 lo = int(head_rect[n, g * G:(g + 1) * G].min())
                 t = min(F, lo) + (ne - lo) + (kv_len - ne)
-            kv += t * 512
+            row_kv += t * 512
             distinct = max(distinct, t)
+        row_scan = min(capacity, P) * hq * 256 if eligible else 0
+        row_small = int(head_hit[n].sum()) * 260 + hq * (516 + 256 + 512) + 4 * distinct
+        kv += row_kv
         pt += 4 * distinct
-    scan = sum(min(capacity, int(p)) for p in past_lens) * hq * 256 if eligible else 0
+        scan += row_scan
+        per_row.append(row_kv + row_scan // 2 + row_small)
     hits = int(head_hit.sum())
     heads = batch * hq
     total = kv + scan + hits * 260 + heads * 516 + heads * 256 + heads * 512 + pt
-    return dict(total=total, kv=kv, scan=scan, hit_heads=hits,
-                non_hit_groups=int((mode != 0).sum()), full_groups=int((mode == 1).sum()))
+    return dict(total=total, requested=total - scan // 2, kv=kv, scan=scan, hit_heads=hits,
+                per_row=per_row, non_hit_groups=int((mode != 0).sum()),
+                full_groups=int((mode == 1).sum()))
 
 
 class ClockSampler:
@@ -189,15 +227,16 @@ def make_launch(ext, case, ws, scal, out, lse):
     return launch
 
 
-def scalars(args, hit, debug=0):
+def scalars(args, hit, debug=0, front_sink=None):
     """The operator's 21 scalars in positional order (reference benchmark defaults)."""
-    return (MAX_CONTEXT, TILE, MTS, SEM, args.front_sink, 0, 0, 0, 0.45, 1.0 / math.sqrt(DIM),
+    F = args.front_sink if front_sink is None else front_sink
+    return (MAX_CONTEXT, TILE, MTS, SEM, F, 0, 0, 0, 0.45, 1.0 / math.sqrt(DIM),
             debug, args.bench_mode, hit, 0.0, -1.0, 0.0, float(LAG), 0.0, 1, -1, 0)
 
 
 def time_graph(launch, steps, warmup, barrier=None):
     """Mean ms per replay of a CUDA graph holding one step, CUDA events on the
-    capturing stream's replay stream."""
+    stream the graph is replayed on."""
     import torch
 
     for _ in range(3):
@@ -221,6 +260,66 @@ def time_graph(launch, steps, warmup, barrier=None):
     if barrier:
         barrier()
     return t0.elapsed_time(t1) / steps, graph
+
+
+class HostStep:
+    """One step's host-side inputs the way a serving engine would send them: the
+    two query tensors and the three per-row integer vectors packed into ONE
+    pinned buffer, uploaded with one copy into a device buffer whose typed
+    views are what the operator is called with."""
+
+    def __init__(self, case, device):
+        import copy
+
+        import torch
+
+        n = case.q_post.shape[0]
+        parts = [("q_post", case.q_post), ("q_pre", case.q_pre), ("req_ids", case.req_ids[:n]),
+                 ("past_lens", case.past_lens[:n]), ("out_cache_loc", case.out_cache_loc[:n])]
+        off, layout = 0, []
+        for name, t in parts:
+            nbytes = t.numel() * t.element_size()
+            layout.append((name, t, off, nbytes))
+            off = (off + nbytes + 255) // 256 * 256
+        self.host = torch.empty(off, dtype=torch.uint8).pin_memory()
+        self.dev = torch.empty(off, dtype=torch.uint8, device=device)
+        self.case = copy.copy(case)
+        self.h2d_bytes = off
+        for name, t, o, nbytes in layout:
+            self.host[o:o + nbytes].copy_(t.contiguous().view(torch.uint8).reshape(-1).cpu())
+            setattr(self.case, name, self.dev[o:o + nbytes].view(t.dtype).view(t.shape))
+
+    def upload(self):
+        self.dev.copy_(self.host, non_blocking=True)
+
+
+def time_e2e(ext, case, ws, scal, out, lse, dev, n_steps, barrier, count_launches=None):
+    """The step through the operator with HOST buffers: one pinned H2D copy of
+    the step's inputs, the eager operator call, the output copied back to
+    pinned host memory, a stream synchronise; host wall clock per step."""
+    import torch
+
+    hs = HostStep(case, dev)
+    out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    launch = make_launch(ext, hs.case, ws, scal, out, lse)
+    stream = torch.cuda.current_stream()
+
+    def step():
+        hs.upload()
+        launch()
+        out_host.copy_(out, non_blocking=True)
+        stream.synchronize()
+
+    for _ in range(3):
+        step()
+    barrier()
+    before = count_launches() if count_launches else 0
+    w0 = time.perf_counter()
+    for _ in range(n_steps):
+        step()
+    ms = (time.perf_counter() - w0) * 1e3 / n_steps
+    launches = (count_launches() - before) if count_launches else None
+    return ms, hs.h2d_bytes, out_host.numel() * out_host.element_size(), launches
 
 
 def time_real_scan(args, ext, case, ws, out, lse, dev):
@@ -266,10 +365,252 @@ def time_real_scan(args, ext, case, ws, out, lse, dev):
     return {"us": ms * 1e3, "includes": "3 ring-slot restore copies per step",
             "planted_hit_heads": int(planted.sum()), "hit_heads": int(hits.sum()),
             "decisions_match_planted": bool(torch.equal(hits, planted)),
-            "alg_gbs": ab["total"] / (ms * 1e-3) / 1e9, "non_hit_groups": ab["non_hit_groups"]}
+            "requested_gbs": ab["requested"] / (ms * 1e-3) / 1e9,
+            "non_hit_groups": ab["non_hit_groups"]}
 
 
-def run_ours(args):
+# --------------------------------------------------------------------------- parity on the timed tensors
+def parity_sample(args, case, ws, out, lse, per_row_bytes, hq, hkv, front_sink, max_rows):
+    """Checks the step that was just timed against the CPU oracle on a sample of
+    its requests: the SAME tensors, copied to the host.  The sample holds rows of
+    every kind the step has (a request with a full-attention group, one with a
+    mixed group, all-hit requests); their K/V rows are gathered through the page
+    table into a compact host pool, their ring rows are taken whole, and the
+    oracle runs with the full batch's row indices (the synthetic decision hash
+    depends on them) restricted to the sampled rows.  Returns the parity record
+    and the oracle's wall time with the share of the step's bytes it covered."""
+    import torch
+
+    from mac_attention_b200 import workspace as W
+    from oracle import mac_oracle as O
+
+    N = case.q_post.shape[0]
+    M = case.query_cache.shape[1]
+    mode = ws[W.GROUP_MODE][:N].cpu()
+    kinds = {"full": [], "mixed": [], "hit": []}
+    for n in range(N):
+        row = mode[n]
+        kinds["mixed" if bool((row == 2).any()) else "full" if bool((row == 1).any()) else "hit"].append(n)
+    rows = []
+    quota = max(1, max_rows // 3)
+    for k in ("full", "mixed", "hit"):
+        rows += kinds[k][:quota]
+    for k in ("hit", "full", "mixed"):           # fill up from whatever is left
+        for n in kinds[k][quota:]:
+            if len(rows) < max_rows:
+                rows.append(n)
+    rows = sorted(rows)[:max_rows]
+    dev = case.q_post.device
+    P = case.past_lens.cpu().tolist()
+    req = case.req_ids.cpu().tolist()
+    stride = max(P[n] + 1 for n in rows)
+    r2t_sub = torch.zeros(len(rows), stride, dtype=torch.int32)
+    req_sub = torch.zeros(N, dtype=torch.int32)
+    ocl_sub = torch.zeros(N, dtype=case.out_cache_loc.dtype)
+    k_parts, v_parts = [], []
+    base = 0
+    for i, n in enumerate(rows):
+        toks = torch.cat([case.req_to_token[req[n], :P[n]].long(),
+                          case.out_cache_loc[n:n + 1].long()])
+        k_parts.append(case.k.index_select(0, toks).cpu())
+        v_parts.append(case.v.index_select(0, toks).cpu())
+        r2t_sub[i, :P[n]] = torch.arange(base, base + P[n], dtype=torch.int32)
+        ocl_sub[n] = base + P[n]
+        req_sub[n] = i
+        base += P[n] + 1
+    sel = torch.tensor([req[n] for n in rows], device=dev)
+    gpu_ring = [t.index_select(0, sel).cpu() for t in (case.query_cache, case.attn_cache, case.lse_cache)]
+    qc, ac, lc = (t.clone() for t in gpu_ring)
+    mask = torch.zeros(N, dtype=torch.uint8)
+    mask[rows] = 1
+    cfg = O.DecodeConfig(max_context=MAX_CONTEXT, tile_tokens=TILE, match_tile_slots=MTS,
+                         semantic_pos_ahead=SEM, front_sink_tokens=front_sink,
+                         bench_mode=args.bench_mode, bench_hit_rate=args.hit,
+                         bench_match_lag_mean=float(LAG), bench_seed=1)
+    k_sub, v_sub = torch.cat(k_parts), torch.cat(v_parts)
+    del k_parts, v_parts
+    t0 = time.perf_counter()
+    res = O.decode_step(case.q_post.cpu(), case.q_pre.cpu(), k_sub, v_sub, r2t_sub, req_sub,
+                        case.past_lens.cpu()[:N].contiguous(), ocl_sub, qc, ac, lc, cfg,
+                        row_mask=mask)
+    oracle_s = time.perf_counter() - t0
+    ridx = torch.tensor(rows)
+    pairs = [(W.HEAD_HIT, res.head_hit), (W.HEAD_MATCH_SLOT, res.head_match_slot),
+             (W.HEAD_MATCH_POS, res.head_match_pos), (W.HEAD_PREFIX_END, res.head_prefix_end),
+             (W.HEAD_RECT_START, res.head_rect_start), (W.HEAD_NEW_END, res.head_new_end),
+             (W.GROUP_RECT_BEGIN, res.group_rect_begin), (W.GROUP_MODE, res.group_mode)]
+    decisions_equal = all(torch.equal(ws[i][:N].cpu()[ridx], ref[ridx]) for i, ref in pairs)
+    got_out = out.float().cpu()[ridx]
+    out_err = O.rel_l2(got_out, res.out_f32[ridx])
+    slot = torch.tensor([P[n] % M for n in rows])
+    ar = torch.arange(len(rows))
+    ring_q_equal = bool(torch.equal(gpu_ring[0][ar, slot], qc[ar, slot]))
+    ring_err = O.rel_l2(gpu_ring[1][ar, slot].float(), res.ring_o_f32[ridx])
+    l_gpu, l_ref = lse.cpu()[ridx], res.lse[ridx]
+    fin = torch.isfinite(l_ref)
+    lse_err = float((l_gpu[fin] - l_ref[fin]).abs().max()) if bool(fin.any()) else 0.0
+    rl_gpu, rl_ref = gpu_ring[2][ar, slot], lc[ar, slot]
+    rfin = torch.isfinite(rl_ref)
+    ring_lse_err = float((rl_gpu[rfin] - rl_ref[rfin]).abs().max()) if bool(rfin.any()) else 0.0
+    parity = {
+        "checked_against": "CPU oracle (oracle/mac_oracle.c) on the timed tensors copied to the host",
+        "requests_checked": len(rows), "rows": rows,
+        "rows_with_full_group": sum(n in kinds["full"] for n in rows),
+        "rows_with_mixed_group": sum(n in kinds["mixed"] for n in rows),
+        "all_hit_rows": sum(n in kinds["hit"] for n in rows),
+        "decisions_equal": bool(decisions_equal), "out_rel_l2": out_err,
+        "ring_query_rows_equal": ring_q_equal, "ring_rel_l2": ring_err,
+        "lse_max_abs": lse_err, "ring_lse_max_abs": ring_lse_err,
+        "finite_pattern_equal": bool(torch.equal(torch.isfinite(l_gpu), fin)
+                                     and torch.equal(torch.isfinite(rl_gpu), rfin)),
+        "tolerance": {"out_rel_l2": 1e-2, "ring_rel_l2": 1e-2, "lse_max_abs": 2e-2},
+    }
+    parity["ok"] = bool(decisions_equal and ring_q_equal and parity["finite_pattern_equal"]
+                        and out_err <= 1e-2 and ring_err <= 1e-2 and lse_err <= 2e-2
+                        and ring_lse_err <= 2e-2)
+    share = sum(per_row_bytes[n] for n in rows) / max(1, sum(per_row_bytes))
+    return parity, oracle_s, share
+
+
+def cpu_baseline_from_sample(parity, oracle_s, share, args):
+    """``cpu_baseline`` of the main line: the oracle's time on the parity sample,
+    scaled to the whole step by the share of the step's bytes the sample holds."""
+    from oracle import mac_oracle as O
+
+    return {"value": oracle_s / max(share, 1e-9) * 1e6, "unit": "us",
+            "cores": O.lib().mac_oracle_num_threads(), "kind": "port",
+            "sample": f"{parity['requests_checked']} of {args.batch} requests of the timed step "
+                      f"(rows {parity['rows']}: {parity['rows_with_full_group']} with a full-attention "
+                      f"group, {parity['rows_with_mixed_group']} with a mixed group, "
+                      f"{parity['all_hit_rows']} all-hit) = {share * 100:.1f} % of the step's bytes, "
+                      f"{oracle_s:.3f} s on the host cores, scaled by bytes"}
+
+
+def cpu_port_arm(args, steps, warmup):
+    """The CPU restatement of the path (oracle port) timed on the host cores on
+    the first requests of a step of the same shape; used only when the
+    reference's CUDA kernel is not available to ``--impl reference``."""
+    import torch  # noqa: F401
+
+    from mac_attention_b200 import synth
+    from oracle import mac_oracle as O
+
+    ns = max(1, min(4, args.batch))
+    case = synth.make_decode_case(batch=ns, ctx=args.ctx, hq=args.hq, hkv=args.hkv,
+                                  capacity=args.capacity, page_size=args.page_size, seed=1000,
+                                  device="cpu")
+    cfg = O.DecodeConfig(max_context=MAX_CONTEXT, tile_tokens=TILE, match_tile_slots=MTS,
+                         semantic_pos_ahead=SEM, front_sink_tokens=args.front_sink,
+                         bench_mode=args.bench_mode, bench_hit_rate=args.hit,
+                         bench_match_lag_mean=float(LAG), bench_seed=1)
+    times = []
+    for i in range(warmup + steps):
+        c = case.clone() if i == 0 else case
+        t0 = time.perf_counter()
+        O.decode_step(c.q_post, c.q_pre, c.k, c.v, c.req_to_token, c.req_ids, c.past_lens,
+                      c.out_cache_loc, c.query_cache, c.attn_cache, c.lse_cache, cfg)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    per_sample = sum(times) / len(times)
+    scale = args.batch / ns
+    return {"value": per_sample * scale * 1e6, "unit": "us", "cores": O.lib().mac_oracle_num_threads(),
+            "kind": "port", "extrapolated": True, "factor": scale,
+            "sample": f"{ns} of {args.batch} requests (all heads, full context {args.ctx}, hit "
+                      f"{args.hit}), {per_sample:.3f} s per sample step, scaled x{scale:g}"}
+
+
+# --------------------------------------------------------------------------- same-box GPU baselines
+def gpu_baselines(args, case, ws, scal, out, lse, hq, hkv, budget_s=240.0):
+    """FlashInfer full decode (CUDA-core and tensor-core decode paths) and the
+    reference's own kernel (built for sm_100a from its source) on the tensors of
+    the timed step.  An arm that cannot run reports why instead of a number."""
+    import torch
+
+    res = {}
+    t_start = time.perf_counter()
+    steps = max(5, min(args.steps, 20))
+    for key, tc in (("flashinfer_us", False), ("flashinfer_tc_us", True)):
+        if time.perf_counter() - t_start > budget_s:
+            res[key] = "unavailable on this box: time budget of the baseline leg used up"
+            continue
+        try:
+            ms, fi_out = bench_flashinfer(case, hq, hkv, args.page_size, steps, 3, use_tensor_cores=tc)
+            res[key] = ms * 1e3
+            del fi_out
+        except Exception as exc:  # noqa: BLE001
+            res[key] = f"unavailable on this box: {type(exc).__name__}: {str(exc)[:160]}"
+        torch.cuda.empty_cache()
+    nums = [v for v in (res.get("flashinfer_us"), res.get("flashinfer_tc_us")) if isinstance(v, float)]
+    res["flashinfer_best_us"] = min(nums) if nums else None
+    try:
+        from oracle import build_ref
+
+        ref_ext = build_ref.load_decode()
+        if ref_ext is None:
+            res["refkernel_us"] = "unavailable on this box: oracle/_ref holds no prebuilt reference kernel"
+        else:
+            keep = [t.clone() for t in (out, lse)]
+            ms, _ = time_graph(make_launch(ref_ext, case, ws, scal, out, lse), steps, 3)
+            res["refkernel_us"] = ms * 1e3
+            out.copy_(keep[0]); lse.copy_(keep[1])
+    except Exception as exc:  # noqa: BLE001
+        res["refkernel_us"] = f"unavailable on this box: {type(exc).__name__}: {str(exc)[:160]}"
+    res["what"] = ("same tensors as the timed step; FlashInfer BatchDecodeWithPagedKVCacheWrapper "
+                   "(page 16, plan once, graph replay) with use_tensor_cores False / True; "
+                   "refkernel = the reference's mac_persistent_decode_bf16 built for sm_100a")
+    return res
+
+
+# --------------------------------------------------------------------------- config 3
+def config3_leg(args, dev, rank, world, dist, ext, peak_gbs):
+    """BASELINE config 3: the Llama-3.1-70B attention shape (Hq 64 / Hkv 8, batch
+    64, context 126976, hit 0.9) split by KV head over the ranks; every rank owns
+    its KV-head slice of the pool and of the ring, no collective.  Strong
+    scaling: the aggregate work is fixed."""
+    import torch
+
+    from mac_attention_b200 import make_decode_workspace, sharding
+
+    hq_all, hkv_all, batch, ctx, hit = 64, 8, 64, 126976, 0.9
+    if hkv_all % world != 0:
+        return {"skipped": f"Hkv {hkv_all} does not split over {world} ranks"}
+    q_sl, kv_sl = sharding.head_slices(hq_all, hkv_all, world, rank)
+    hq, hkv = q_sl.stop - q_sl.start, kv_sl.stop - kv_sl.start
+    case = build_case(args, dev, 3000 + rank, batch, ctx, hq, hkv)
+    ws = make_decode_workspace(batch, hq, hkv, args.capacity, MAX_CONTEXT, TILE, MTS, SEM, 0,
+                               device=dev, partial_dtype=torch.bfloat16)
+    out = torch.empty_like(case.q_post)
+    lse = torch.empty(batch, hq, device=dev)
+    scal = scalars(args, hit, front_sink=0)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    ms, _ = time_graph(make_launch(ext, case, ws, scal, out, lse), args.steps, args.warmup, barrier)
+    ab = alg_bytes(ws, batch, hq, hkv, 0, args.capacity, case.past_lens.cpu().tolist())
+    t = torch.tensor([ms, float(ab["requested"]), float(ab["total"])], device=dev, dtype=torch.float64)
+    tmax = t.clone()
+    if dist is not None:
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    ms_max = float(tmax[0])
+    req_all, alg_all = float(t[1]), float(t[2])
+    del case, ws, out, lse
+    torch.cuda.empty_cache()
+    return {"workload": f"Hq{hq_all}/Hkv{hkv_all}/D128 split by KV head over {world} GPU(s), batch "
+                        f"{batch}, context {ctx}, hit {hit}, ring M={args.capacity}",
+            "us": ms_max * 1e3, "scaling": "strong", "hq_per_rank": hq, "hkv_per_rank": hkv,
+            "requested_gbs_aggregate": req_all / (ms_max * 1e-3) / 1e9,
+            "alg_gbs_aggregate": alg_all / (ms_max * 1e-3) / 1e9,
+            "frac": req_all / (ms_max * 1e-3) / 1e9 / (peak_gbs * world),
+            "frac_of": "requested bytes / (measured copy bandwidth x ranks)",
+            "non_hit_groups_rank0": ab["non_hit_groups"]}
+
+
+# --------------------------------------------------------------------------- this library's arm
+def dist_setup():
     import torch
 
     rank = int(os.environ.get("RANK", "0"))
@@ -286,9 +627,33 @@ def run_ours(args):
         sys.stdout.flush()
         saved_stdout = os.dup(1)
         os.dup2(2, 1)
-
         dist = dist_mod
         dist.init_process_group("nccl", device_id=dev)
+    return rank, local_rank, world, dev, dist, saved_stdout
+
+
+def dist_finish(dist, saved_stdout):
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if saved_stdout is not None:
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        os.close(saved_stdout)
+
+
+def measured_peak():
+    pk = ROOT / "MEASURED_PEAKS.json"
+    if pk.exists():
+        return float(json.loads(pk.read_text()).get("hbm_gbs", 6650.0)), \
+            "MEASURED_PEAKS.json hbm_gbs (of measured)"
+    return 6650.0, "6650 GB/s (of fallback)"
+
+
+def run_ours(args):
+    import torch
+
+    rank, local_rank, world, dev, dist, saved_stdout = dist_setup()
 
     from mac_attention_b200 import load_mac_persistent_decode_extension, make_decode_workspace
     from mac_attention_b200 import ops, sharding
@@ -319,16 +684,31 @@ def run_ours(args):
     with ClockSampler(local_rank) as clk:
         ms, graph = time_graph(launch, args.steps, args.warmup, barrier)
     clocks = clk.summary()
+    if profiler_range:   # the side legs below are not part of the launch list
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_max = float(t)
     ab = alg_bytes(ws, batch, hq, hkv, args.front_sink, args.capacity,
                    case.past_lens.cpu().tolist())
-    bytes_all = torch.tensor([float(ab["total"])], device=dev, dtype=torch.float64)
+    bytes_all = torch.tensor([float(ab["requested"]), float(ab["total"])], device=dev,
+                             dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(bytes_all, op=dist.ReduceOp.SUM)
     status = ops.query_status(dev)
+
+    # the timed tensors against the CPU oracle (rank 0), which also gives the CPU baseline
+    parity = cpu_base = None
+    if rank == 0 and not args.no_cpu_baseline:
+        try:
+            parity, oracle_s, share = parity_sample(args, case, ws, out, lse, ab["per_row"], hq, hkv,
+                                                    args.front_sink, args.parity_requests)
+            cpu_base = cpu_baseline_from_sample(parity, oracle_s, share, args)
+        except Exception as exc:  # reported, never fatal for the main line
+            parity = {"ok": False, "error": f"{type(exc).__name__}: {exc}"[:300]}
+    barrier()
 
     # the same step with decisions from the REAL match scan (synthetic-decision mode
     # off): ring rows planted so that about the same fraction of KV groups hit at the
@@ -336,79 +716,39 @@ def run_ours(args):
     # the row written by one replay is a distance-0 match for the next
     real_scan = None
     if world == 1 and args.bench_mode != 0:
-        if profiler_range:   # a side measurement with its own set-up copies: not in the launch list
-            torch.cuda.synchronize()
-            torch.cuda.profiler.stop()
         try:
             real_scan = time_real_scan(args, ext, case, ws, out, lse, dev)
         except Exception as exc:  # reported, never fatal for the main line
             real_scan = {"error": f"{type(exc).__name__}: {exc}"[:200]}
-        if profiler_range:
-            torch.cuda.synchronize()
-            torch.cuda.profiler.start()
 
-    # end to end through the operator with host buffers: H2D of the step's
-    # inputs from pinned memory, eager operator call, D2H of the output.
-    # The step's inputs travel as a serving engine would send them: the two query tensors
-    # in one pinned buffer, the two int32 vectors in another, the KV slot vector in a third.
-    import copy
-
-    n_rows = case.q_post.shape[0]
-    e2e_case = copy.copy(case)
-    dev_q = torch.empty((2,) + tuple(case.q_post.shape), dtype=case.q_post.dtype, device=dev)
-    dev_i = torch.empty((2, n_rows), dtype=torch.int32, device=dev)
-    dev_loc = torch.empty_like(case.out_cache_loc)
-    e2e_case.q_post, e2e_case.q_pre = dev_q[0], dev_q[1]
-    e2e_case.req_ids, e2e_case.past_lens = dev_i[0], dev_i[1]
-    e2e_case.out_cache_loc = dev_loc
-    host_q = torch.stack([case.q_post, case.q_pre]).cpu().pin_memory()
-    host_i = torch.stack([case.req_ids[:n_rows], case.past_lens[:n_rows]]).cpu().pin_memory()
-    host_loc = case.out_cache_loc.cpu().pin_memory()
-    out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-    h2d = sum(v.numel() * v.element_size() for v in (host_q, host_i, host_loc))
-    d2h = out_host.numel() * out_host.element_size()
-    launch_e2e = make_launch(ext, e2e_case, ws, scal, out, lse)
-
-    def e2e_step():
-        dev_q.copy_(host_q, non_blocking=True)
-        dev_i.copy_(host_i, non_blocking=True)
-        dev_loc.copy_(host_loc, non_blocking=True)
-        launch_e2e()
-        out_host.copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-
-    for _ in range(3):
-        e2e_step()
-    barrier()
     n_e2e = max(5, min(args.steps, 50))
-    launches_before = ops.launch_info(dev)["kernel_launches"]
-    w0 = time.perf_counter()
-    for _ in range(n_e2e):
-        e2e_step()
-    e2e_ms = (time.perf_counter() - w0) * 1e3 / n_e2e
-    launches_e2e = ops.launch_info(dev)["kernel_launches"] - launches_before
+    e2e_ms, h2d, d2h, launches_e2e = time_e2e(
+        ext, case, ws, scal, out, lse, dev, n_e2e, barrier,
+        count_launches=lambda: ops.launch_info(dev)["kernel_launches"])
     te = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_ms = float(te)
-    if profiler_range:
-        torch.cuda.synchronize()
-        torch.cuda.profiler.stop()
+
+    baselines = None
+    if world == 1 and not args.no_gpu_baselines:
+        baselines = gpu_baselines(args, case, ws, scal, out, lse, hq, hkv)
 
     info = ops.launch_info(dev)
-    peaks = {}
-    pk = ROOT / "MEASURED_PEAKS.json"
-    if pk.exists():
-        peaks = json.loads(pk.read_text())
-    peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
-    achieved = ab["total"] / (ms * 1e-3) / 1e9
-    # The scan fetches only the first 128 B of a ring row unless the row is a
-    # near match, so the bytes the kernel asks for are the algorithmic ones minus
-    # half of the scan; DRAM traffic measured by ncu on smaller captures is 1.02x
-    # the requested bytes and grows in proportion to them (profiles/).
-    requested = ab["total"] - ab["scan"] // 2
+    peak_gbs, peak_source = measured_peak()
+    del case, ws, graph, launch
+    torch.cuda.empty_cache()
+    config3 = None
+    if not args.no_config3 and args.shard == "request":
+        try:
+            config3 = config3_leg(args, dev, rank, world, dist, ext, peak_gbs)
+        except Exception as exc:  # reported, never fatal for the main line
+            config3 = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+
+    requested = ab["requested"]
+    achieved = requested / (ms * 1e-3) / 1e9
     line = {
-        "metric": "us_per_decode_step_cuda_graph_replay",
+        "metric": METRIC,
         "value": ms_max * 1e3,
         "unit": "us",
         "n_gpus": world,
@@ -420,114 +760,137 @@ def run_ours(args):
         "vs_baseline": None,
         "dtype": "bf16",
         "data": "synthetic",
-        "config": {
-            "workload": f"GQA-{args.hq // args.hkv} MAC decode step, Hq{args.hq}/Hkv{args.hkv}/D128, "
-                        f"batch {batch} per GPU, context {args.ctx}, per-head hit fraction {args.hit} "
-                        f"(reference synthetic_head decisions, lag {LAG}), ring M={args.capacity}, "
-                        f"S={SEM}, F={args.front_sink}, paged KV page {args.page_size}",
-            "batch": batch, "context": args.ctx, "hit_fraction": args.hit,
-            "sharding": f"{args.shard} x{world}, no collective in attention",
-            "l2": "inputs larger than L2 (K/V + ring streamed per step >> 126 MB)",
-            "non_hit_groups": ab["non_hit_groups"], "full_attention_groups": ab["full_groups"],
-            "grid": info["last_grid"], "regs": info["regs_per_thread"],
-        },
-        "hbm_gbs": bytes_all.item() / (ms_max * 1e-3) / 1e9,
+        "config": workload_config(args, world),
+        "non_hit_groups": ab["non_hit_groups"], "full_attention_groups": ab["full_groups"],
+        "grid": info["last_grid"], "regs": info["regs_per_thread"],
+        "hbm_gbs": float(bytes_all[0]) / (ms_max * 1e-3) / 1e9,
+        "hbm_gbs_full_row_convention": float(bytes_all[1]) / (ms_max * 1e-3) / 1e9,
         "request_steps_per_s": world * batch / (ms_max * 1e-3),
         "e2e": {"value": e2e_ms * 1e3, "unit": "us", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h},
+                "d2h_bytes_per_step": d2h, "h2d_copies_per_step": 1},
         "gpu_launches": args.steps,
         "gpu_launches_e2e_region": int(launches_e2e),
         "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"],
                    "reasons": clocks["reasons"]},
+        # achieved = bytes this kernel asks the memory system for (K/V rows, the
+        # 128-byte probe half of every scanned ring row, states, outputs) per
+        # launch / CUDA-event time of one launch; DRAM traffic measured by ncu
+        # on smaller captures is 1.02x that and grows in proportion (profiles/).
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
                      "frac": achieved / peak_gbs, "traffic": int(requested * NCU_TRAFFIC_RATIO),
+                     "traffic_gbs": requested * NCU_TRAFFIC_RATIO / (ms * 1e-3) / 1e9,
                      "requested_bytes_per_launch": requested,
-                     "requested_gbs": requested / (ms * 1e-3) / 1e9,
                      "kernel": "mac_decode_persistent_kernel",
-                     "alg_bytes_per_launch": ab["total"], "kv_bytes": ab["kv"],
-                     "scan_bytes": ab["scan"],
-                     "peak_source": "MEASURED_PEAKS.json hbm_gbs (of measured)" if peaks
-                     else "6650 GB/s (of fallback)"},
+                     "alg_bytes_full_row_convention": ab["total"],
+                     "alg_gbs_full_row_convention": ab["total"] / (ms * 1e-3) / 1e9,
+                     "kv_bytes": ab["kv"], "scan_bytes_full_rows": ab["scan"],
+                     "peak_source": peak_source},
+        "parity": parity,
+        "gpu_baselines": baselines,
+        "config3": config3,
         "device_status": status, "real_scan": real_scan,
     }
-    if rank == 0 and not args.no_cpu_baseline and world == 1:
-        line["cpu_baseline"] = cpu_baseline(args, steps=2, warmup=1)
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
-    if saved_stdout is not None:
-        sys.stdout.flush()
-        os.dup2(saved_stdout, 1)
-        os.close(saved_stdout)
+    if cpu_base is not None:
+        line["cpu_baseline"] = cpu_base
+    dist_finish(dist, saved_stdout)
     if rank == 0:
         print(json.dumps(line), flush=True)
 
 
-# --------------------------------------------------------------------------- CPU arm
-def cpu_baseline(args, steps, warmup):
-    """The CPU restatement of the reference path (oracle port) timed on the host
-    cores on a bounded sample of the workload: the first few requests of the
-    batch, all heads, same context and hit fraction; scaled to the full batch."""
+# --------------------------------------------------------------------------- reference arm
+def run_reference_arm(args):
+    """``--impl reference``: the reference's own decode kernel, compiled for
+    sm_100a from its unmodified source by ``oracle/build_ref.py`` (prebuilt into
+    ``oracle/_ref``), through its own operator on the same workload, timed the
+    same way (graph replay, CUDA events, max over ranks; ``e2e`` with the same
+    host copies).  The reference has no CPU implementation of the path; when
+    its kernel cannot be loaded the CPU oracle port is timed instead and the
+    line says so."""
     import torch
 
-    from mac_attention_b200 import synth
-    from oracle import mac_oracle as O
+    from oracle import build_ref
 
-    ns = max(1, min(args.cpu_sample_requests, args.batch))
-    case = synth.make_decode_case(batch=ns, ctx=args.ctx, hq=args.hq, hkv=args.hkv,
-                                  capacity=args.capacity, page_size=args.page_size, seed=1000,
-                                  device="cpu")
-    cfg = O.DecodeConfig(max_context=MAX_CONTEXT, tile_tokens=TILE, match_tile_slots=MTS,
-                         semantic_pos_ahead=SEM, front_sink_tokens=args.front_sink,
-                         bench_mode=args.bench_mode, bench_hit_rate=args.hit,
-                         bench_match_lag_mean=float(LAG), bench_seed=1)
-    times = []
-    for i in range(warmup + steps):
-        c = case.clone() if i == 0 else case
-        t0 = time.perf_counter()
-        O.decode_step(c.q_post, c.q_pre, c.k, c.v, c.req_to_token, c.req_ids, c.past_lens,
-                      c.out_cache_loc, c.query_cache, c.attn_cache, c.lse_cache, cfg)
-        dt = time.perf_counter() - t0
-        if i >= warmup:
-            times.append(dt)
-    per_sample = sum(times) / len(times)
-    scale = args.batch / ns
-    return {"value": per_sample * scale * 1e6, "unit": "us", "cores": O.lib().mac_oracle_num_threads(),
-            "kind": "port",
-            "sample": f"{ns} of {args.batch} requests (all heads, full context {args.ctx}, hit "
-                      f"{args.hit}), {per_sample:.3f} s per sample step, scaled x{scale:g}"}
-
-
-def run_reference_arm(args):
-    """``--impl reference``: the reference has no CPU implementation of the whole
-    path (its kernel is CUDA only), so this arm times the CPU oracle port on
-    the host cores.  Under torchrun only rank 0 works."""
-    if int(os.environ.get("RANK", "0")) != 0:
+    ref_ext = None
+    why = ""
+    try:
+        ref_ext = build_ref.load_decode()
+        if ref_ext is None:
+            why = "oracle/_ref holds no prebuilt reference kernel"
+    except Exception as exc:  # noqa: BLE001
+        why = f"{type(exc).__name__}: {str(exc)[:160]}"
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if ref_ext is None or not torch.cuda.is_available():
+        if int(os.environ.get("RANK", "0")) != 0:
+            return
+        cb = cpu_port_arm(args, steps=max(1, min(args.steps, 5)), warmup=1)
+        line = {
+            "impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "us",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": cb["value"] / 1e3, "higher_is_better": False, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+            "config": workload_config(args, world), "extrapolated": True,
+            "reference_kind": f"CPU oracle port (reference kernel unavailable: {why})",
+            "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": "us", "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": 0},
+            "gpu_launches": 0,
+        }
+        print(json.dumps(line), flush=True)
         return
-    cb = cpu_baseline(args, steps=max(1, args.steps), warmup=max(0, args.warmup))
+
+    rank, local_rank, world, dev, dist, saved_stdout = dist_setup()
+    from mac_attention_b200 import make_decode_workspace
+
+    hq, hkv, batch = args.hq, args.hkv, args.batch
+    case = build_case(args, dev, 1000 + rank, batch, args.ctx, hq, hkv)
+    ws = make_decode_workspace(batch, hq, hkv, args.capacity, MAX_CONTEXT, TILE, MTS, SEM,
+                               args.front_sink, device=dev, partial_dtype=torch.bfloat16)
+    out = torch.empty_like(case.q_post)
+    lse = torch.empty(batch, hq, device=dev)
+    scal = scalars(args, args.hit)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    with ClockSampler(local_rank) as clk:
+        ms, graph = time_graph(make_launch(ref_ext, case, ws, scal, out, lse), args.steps,
+                               args.warmup, barrier)
+    clocks = clk.summary()
+    ab = alg_bytes(ws, batch, hq, hkv, args.front_sink, args.capacity, case.past_lens.cpu().tolist())
+    e2e_ms, h2d, d2h, _ = time_e2e(ref_ext, case, ws, scal, out, lse, dev,
+                                   max(5, min(args.steps, 50)), barrier)
+    t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max, e2e_max = float(t[0]), float(t[1])
+    peak_gbs, peak_source = measured_peak()
     line = {
-        "impl": "reference",
-        "metric": "us_per_decode_step_cuda_graph_replay",
-        "value": cb["value"], "unit": "us", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": cb["value"] / 1e3, "higher_is_better": False,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-        "config": {
-            "workload": f"GQA-{args.hq // args.hkv} MAC decode step, Hq{args.hq}/Hkv{args.hkv}/D128, "
-                        f"batch {args.batch} per GPU, context {args.ctx}, per-head hit fraction {args.hit} "
-                        f"(reference synthetic_head decisions, lag {LAG}), ring M={args.capacity}, "
-                        f"S={SEM}, F={args.front_sink}, paged KV page {args.page_size}",
-            "batch": args.batch, "context": args.ctx, "hit_fraction": args.hit},
-        "cpu_baseline": cb,
-        "e2e": {"value": cb["value"], "unit": "us", "h2d_bytes_per_step": 0,
-                "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
+        "impl": "reference", "metric": METRIC, "value": ms_max * 1e3, "unit": "us",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_max, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic", "config": workload_config(args, world),
+        "reference_kind": "the reference's mac_persistent_decode_bf16 CUDA kernel, built for sm_100a "
+                          "from its unmodified source (oracle/_ref), its own operator and workspace",
+        "non_hit_groups": ab["non_hit_groups"], "full_attention_groups": ab["full_groups"],
+        "hbm_gbs_full_row_convention": ab["total"] / (ms * 1e-3) / 1e9,
+        "e2e": {"value": e2e_max * 1e3, "unit": "us", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "h2d_copies_per_step": 1},
+        "gpu_launches": args.steps,
+        "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"],
+                   "reasons": clocks["reasons"]},
+        "peak": peak_gbs, "peak_source": peak_source,
     }
-    print(json.dumps(line))
+    dist_finish(dist, saved_stdout)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
 
 
 # --------------------------------------------------------------------------- sweep
-def bench_flashinfer(case, hq, hkv, page_size, steps, warmup):
-    """FlashInfer full decode over the same paged KV (plan once, capture run, time replay)."""
+def bench_flashinfer(case, hq, hkv, page_size, steps, warmup, use_tensor_cores=False):
+    """FlashInfer full decode over the same paged KV (plan once, capture run, time replay).
+    ``use_tensor_cores`` selects its tensor-core decode path (the prefill template run on
+    decode queries) instead of the CUDA-core decode kernel the reference's harness uses."""
     import torch
     import flashinfer
 
@@ -550,7 +913,8 @@ def bench_flashinfer(case, hq, hkv, page_size, steps, warmup):
     vc = case.v.view(-1, page_size, hkv, DIM)
     wsb = torch.empty(256 << 20, device=dev, dtype=torch.uint8)
     wrapper = flashinfer.decode.BatchDecodeWithPagedKVCacheWrapper(
-        wsb, kv_layout="NHD", use_cuda_graph=True, paged_kv_indptr_buffer=indptr,
+        wsb, kv_layout="NHD", use_cuda_graph=True, use_tensor_cores=use_tensor_cores,
+        paged_kv_indptr_buffer=indptr,
         paged_kv_indices_buffer=indices, paged_kv_last_page_len_buffer=last)
     wrapper.plan(indptr, indices, last, hq, hkv, DIM, page_size, q_data_type=torch.bfloat16,
                  kv_data_type=torch.bfloat16, sm_scale=1.0 / math.sqrt(DIM))
@@ -592,13 +956,19 @@ def run_sweep(args):
                                    SEM, args.front_sink, device=dev, partial_dtype=torch.bfloat16)
         out = torch.empty_like(case.q_post)
         lse = torch.empty(batch, args.hq, device=dev)
-        fi_ms = None
-        if "flashinfer" in baselines:
+        fi_ms = fi_tc_ms = None
+        for name, tc in (("flashinfer", False), ("flashinfer_tc", True)):
+            if name not in baselines:
+                continue
             try:
-                fi_ms, _ = bench_flashinfer(case, args.hq, args.hkv, args.page_size, args.steps,
-                                            args.warmup)
+                v, _ = bench_flashinfer(case, args.hq, args.hkv, args.page_size, args.steps,
+                                        args.warmup, use_tensor_cores=tc)
             except Exception as exc:  # noqa: BLE001
-                fi_ms = f"unavailable on this box: {type(exc).__name__}: {str(exc)[:200]}"
+                v = f"unavailable on this box: {type(exc).__name__}: {str(exc)[:200]}"
+            if tc:
+                fi_tc_ms = v
+            else:
+                fi_ms = v
         for hit in hits:
             scal = scalars(args, hit)
             ms, _ = time_graph(make_launch(ext, case, ws, scal, out, lse), args.steps, args.warmup)
@@ -609,11 +979,13 @@ def run_sweep(args):
             torch.cuda.synchronize()
             ph = ws[29].cpu().tolist()
             row = dict(batch=batch, ctx=ctx, hit=hit, mac_us=ms * 1e3,
+                       requested_gbs=ab["requested"] / (ms * 1e-3) / 1e9,
                        phase_us=dict(scan=(ph[1] - ph[0]) / 1e3, classify=(ph[2] - ph[1]) / 1e3,
                                      attend_cta0=(ph[3] - ph[2]) / 1e3),
                        alg_gbs=ab["total"] / (ms * 1e-3) / 1e9, kv_gb=ab["kv"] / 1e9,
                        non_hit_groups=ab["non_hit_groups"], full_groups=ab["full_groups"],
-                       flashinfer_us=(fi_ms * 1e3 if isinstance(fi_ms, float) else fi_ms))
+                       flashinfer_us=(fi_ms * 1e3 if isinstance(fi_ms, float) else fi_ms),
+                       flashinfer_tc_us=(fi_tc_ms * 1e3 if isinstance(fi_tc_ms, float) else fi_tc_ms))
             if ref_ext is not None:
                 try:
                     rms, _ = time_graph(make_launch(ref_ext, case, ws, scal, out, lse), args.steps,
@@ -625,10 +997,11 @@ def run_sweep(args):
             print(json.dumps(row), flush=True)
         del case, ws
         torch.cuda.empty_cache()
-    Path(args.sweep_out).parent.mkdir(parents=True, exist_ok=True)
-    Path(args.sweep_out).write_text(json.dumps(dict(rows=rows, status=ops.query_status(dev),
-                                                    hq=args.hq, hkv=args.hkv,
-                                                    front_sink=args.front_sink), indent=1))
+    if args.sweep_out:
+        Path(args.sweep_out).parent.mkdir(parents=True, exist_ok=True)
+        Path(args.sweep_out).write_text(json.dumps(dict(rows=rows, status=ops.query_status(dev),
+                                                        hq=args.hq, hkv=args.hkv,
+                                                        front_sink=args.front_sink), indent=1))
 
 
 def run_config4(args):
@@ -794,9 +1167,7 @@ def run_config4(args):
     torch.cuda.empty_cache()
 
     if args.config4_part == "prefill":
-        Path(args.config4_out).parent.mkdir(parents=True, exist_ok=True)
-        Path(args.config4_out).write_text(json.dumps(dict(rows=rows, status=ops.query_status(dev)),
-                                                     indent=1))
+        write_config4(args, rows, ops.query_status(dev))
         return
     # the producer of the prefill rows: downdate of the last M rows of every prompt
     from mac_attention_b200 import (load_mac_decode_rope_preserve_extension,
@@ -859,9 +1230,14 @@ def run_config4(args):
                      alg_gbs=rbytes / (rms * 1e-3) / 1e9, alg_bytes=rbytes,
                      refkernel_us=ref_us.get("rope")))
     print(json.dumps(rows[-1]), flush=True)
-    Path(args.config4_out).parent.mkdir(parents=True, exist_ok=True)
-    Path(args.config4_out).write_text(json.dumps(dict(rows=rows, status=ops.query_status(dev)),
-                                                 indent=1))
+    write_config4(args, rows, ops.query_status(dev))
+
+
+def write_config4(args, rows, status):
+    if args.config4_out:
+        Path(args.config4_out).parent.mkdir(parents=True, exist_ok=True)
+        Path(args.config4_out).write_text(json.dumps(dict(rows=rows, status=status), indent=1))
+
 
 
 def main():

@@ -20,6 +20,18 @@ int fail(int code, const char* fmt, ...) {
   return code;
 }
 
+int device_sm_count(int device) {
+  static std::atomic<int> cached[64];
+  if (device < 0 || device >= 64) return 148;
+  int v = cached[device].load(std::memory_order_relaxed);
+  if (v <= 0) {
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || v <= 0)
+      v = 148;   // B200; only used to cap grids
+    cached[device].store(v, std::memory_order_relaxed);
+  }
+  return v;
+}
+
 }  // namespace mac_b200
 
 extern "C" const char* mac_b200_last_error(void) { return mac_b200::error_buffer(); }

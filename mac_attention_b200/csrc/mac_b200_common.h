@@ -24,6 +24,13 @@ inline int cuda_fail(cudaError_t err, const char* what) {
               cudaGetErrorName(err));
 }
 
+// Reads and clears the sticky status bits of the prefill ring-build kernels on
+// the current device (the caller has synchronised the device).
+int take_prefill_build_status(unsigned* bits);
+
+// Multiprocessor count of a device, looked up once per device.
+int device_sm_count(int device);
+
 // Kernels launched by this process through the library (all entry points).
 extern std::atomic<int64_t> g_kernel_launches;
 

@@ -1712,16 +1712,11 @@ ArenaLayout arena_layout(int NG, int G, int max_pieces) {
   return L;
 }
 
-}  // namespace
-}  // namespace mac_b200
-
-using namespace mac_b200;
-
-extern "C" int mac_b200_persistent_decode_bf16(const MacB200DecodeArgs* args, void* stream_v) {
-  MAC_REQUIRE(args != nullptr, "decode args must not be null");
-  const MacB200DecodeArgs& a = *args;
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  // Shape rules of the reference launcher (mac_decode_persistent.cu:5080-5153).
+// Checks shared by the decode entry points: the shape rules of the reference
+// launcher (mac_decode_persistent.cu:5080-5153) and this build's limits.
+// Returns MAC_B200_OK with *empty = true for an empty batch.
+int validate_decode_args(const MacB200DecodeArgs& a, bool* empty) {
+  *empty = false;
   MAC_REQUIRE(a.D == kD, "persistent decode supports D=128 only");
   MAC_REQUIRE(a.Hkv > 0 && a.Hq > 0 && a.Hq % a.Hkv == 0, "Hq must be divisible by Hkv");
   const int G = a.Hq / a.Hkv;
@@ -1734,7 +1729,8 @@ extern "C" int mac_b200_persistent_decode_bf16(const MacB200DecodeArgs* args, vo
   MAC_REQUIRE(a.ws_batch >= a.N, "decision workspaces are smaller than the batch");
   MAC_REQUIRE(a.bench_mode == 0 || a.bench_mode == 1 || a.bench_mode == 2,
               "unsupported synthetic MAC bench mode");
-  MAC_REQUIRE(a.phase_cycles_count >= 6 && a.phase_cycles, "phase_cycles must have at least 6 elements");
+  MAC_REQUIRE(a.phase_cycles_count >= 6 && a.phase_cycles,
+              "phase_cycles must have at least 6 elements");
   MAC_REQUIRE(a.q_post && a.q_pre && a.k_buffer && a.v_buffer && a.req_to_token && a.req_ids &&
                   a.past_lens && a.out_cache_loc && a.query_cache && a.attn_cache && a.lse_cache &&
                   a.out,
@@ -1745,13 +1741,124 @@ extern "C" int mac_b200_persistent_decode_bf16(const MacB200DecodeArgs* args, vo
                   a.group_tail_begin && a.group_tail_end && a.group_tail_tiles && a.group_mode &&
                   a.task_counts,
               "workspace tensors must not be null");
-  if (a.N == 0) return MAC_B200_OK;
+  if (a.N == 0) {
+    *empty = true;
+    return MAC_B200_OK;
+  }
   if (a.Hq > kMaxHq)
     return fail(MAC_B200_EUNSUPPORTED, "Hq=%d exceeds this build's limit of %d", a.Hq, kMaxHq);
   const long long NGll = static_cast<long long>(a.N) * a.Hkv;
   if (NGll > kMaxGroups)
     return fail(MAC_B200_EUNSUPPORTED, "N*Hkv=%lld exceeds this build's limit of %d", NGll,
                 kMaxGroups);
+  return MAC_B200_OK;
+}
+
+// Kernel parameters of a validated step on a grid of `grid` CTAs whose scratch
+// block starts at `arena` and is laid out for `max_pieces` pieces.
+DecodeParams make_decode_params(const MacB200DecodeArgs& a, void* arena, int max_pieces) {
+  DecodeParams p;
+  p.a = a;
+  p.G = a.Hq / a.Hkv;
+  p.NG = a.N * a.Hkv;
+  p.F = a.front_sink_tokens > 0 ? a.front_sink_tokens : 0;
+  p.tm_used = (a.M + a.match_tile_slots - 1) / a.match_tile_slots;
+  p.max_pieces = max_pieces;
+  p.force_waves = piece_waves_override();
+  p.ovh_tok = row_overhead_tokens(p.G);
+  p.min_piece = env_int_or("MAC_B200_MIN_PIECE", kMinPieceTok, 64, 1 << 20);
+  p.fuse_max = env_int_or("MAC_B200_FUSE_MAX", static_cast<int>(kFuseMaxCost), 0, 1 << 24);
+  {
+    float t = 2.0f * static_cast<float>(a.D);   // mac_decode_persistent.cu:5342, in float
+    t = t * (1.0f - a.threshold);
+    t = t * (1.0f - a.threshold);
+    p.thr_dist = t;
+  }
+  p.scale_log2 = a.sm_scale * kLog2e;
+  const ArenaLayout L = arena_layout(p.NG, p.G, max_pieces);
+  char* base = static_cast<char*>(arena);
+  p.ar.ticket = reinterpret_cast<uint32_t*>(base + L.ticket);
+  p.ar.garrive = reinterpret_cast<int32_t*>(base + L.garrive);
+  p.ar.plan = reinterpret_cast<GroupPlan*>(base + L.plan);
+  p.ar.part_lse = reinterpret_cast<float*>(base + L.part_lse);
+  p.ar.part_o = reinterpret_cast<float*>(base + L.part_o);
+  p.ar.slots = L.slots;
+  return p;
+}
+
+// One-time facts of the decode kernel on a device (the device is current).
+int query_kernel_facts(int device, int* sm_count, int* ctas_per_sm, int* regs) {
+  int coop = 0;
+  MAC_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device));
+  if (!coop) return fail(MAC_B200_EUNSUPPORTED, "device does not support cooperative launch");
+  MAC_CUDA(cudaFuncSetAttribute(mac_decode_persistent_kernel,
+                                cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+  MAC_CUDA(cudaDeviceGetAttribute(sm_count, cudaDevAttrMultiProcessorCount, device));
+  MAC_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(ctas_per_sm, mac_decode_persistent_kernel,
+                                                         kThreads, kSmemBytes));
+  if (*ctas_per_sm < 1) return fail(MAC_B200_ECUDA, "decode kernel has zero occupancy");
+  cudaFuncAttributes fa{};
+  MAC_CUDA(cudaFuncGetAttributes(&fa, mac_decode_persistent_kernel));
+  *regs = fa.numRegs;
+  return MAC_B200_OK;
+}
+
+// Decode launches of one device share its barrier words and scratch, so two of
+// them must never run at the same time.  Launches on one stream are ordered by
+// the stream; a launch on ANOTHER stream while the previous one has not
+// finished is refused instead of being left to race.  (Not checked while a
+// stream is being captured: a graph's launches run when it is replayed.)
+struct InFlight {
+  cudaEvent_t done = nullptr;
+  cudaStream_t stream = nullptr;
+  bool recorded = false;
+};
+std::mutex g_inflight_mu;
+InFlight g_inflight[64];
+
+int launch_decode(int device, const DecodeParams& p, int grid, cudaStream_t stream) {
+  cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+  MAC_CUDA(cudaStreamIsCapturing(stream, &cs));
+  const bool capturing = cs != cudaStreamCaptureStatusNone;
+  std::lock_guard<std::mutex> lock(g_inflight_mu);
+  InFlight& f = g_inflight[device];
+  if (!capturing && f.recorded && f.stream != stream) {
+    const cudaError_t q = cudaEventQuery(f.done);
+    if (q == cudaErrorNotReady)
+      return fail(MAC_B200_EINVAL,
+                  "a decode step is still running on another stream of this device; decode "
+                  "launches share per-device scratch and must not overlap (order them with an "
+                  "event or use one stream)");
+    if (q != cudaSuccess) return cuda_fail(q, "cudaEventQuery");
+  }
+  DecodeParams params = p;
+  void* kargs[] = {&params};
+  MAC_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(mac_decode_persistent_kernel),
+                                       dim3(grid), dim3(kThreads), kargs, kSmemBytes, stream));
+  g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+  if (!capturing) {
+    if (f.done == nullptr) MAC_CUDA(cudaEventCreateWithFlags(&f.done, cudaEventDisableTiming));
+    MAC_CUDA(cudaEventRecord(f.done, stream));
+    f.stream = stream;
+    f.recorded = true;
+  }
+  return MAC_B200_OK;
+}
+
+}  // namespace
+}  // namespace mac_b200
+
+using namespace mac_b200;
+
+extern "C" int mac_b200_persistent_decode_bf16(const MacB200DecodeArgs* args, void* stream_v) {
+  MAC_REQUIRE(args != nullptr, "decode args must not be null");
+  const MacB200DecodeArgs& a = *args;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  bool empty = false;
+  if (const int rc = validate_decode_args(a, &empty)) return rc;
+  if (empty) return MAC_B200_OK;
+  const int G = a.Hq / a.Hkv;
+  const int NG = a.N * a.Hkv;
 
   int device = 0;
   MAC_CUDA(cudaGetDevice(&device));
@@ -1761,24 +1868,14 @@ extern "C" int mac_b200_persistent_decode_bf16(const MacB200DecodeArgs* args, vo
     std::lock_guard<std::mutex> lock(g_mu);
     DeviceState& ds = g_dev[device];
     if (!ds.ready) {
-      int coop = 0;
-      MAC_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device));
-      if (!coop) return fail(MAC_B200_EUNSUPPORTED, "device does not support cooperative launch");
-      MAC_CUDA(cudaFuncSetAttribute(mac_decode_persistent_kernel,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-      MAC_CUDA(cudaDeviceGetAttribute(&ds.sm_count, cudaDevAttrMultiProcessorCount, device));
-      MAC_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(
-          &ds.ctas_per_sm, mac_decode_persistent_kernel, kThreads, kSmemBytes));
-      if (ds.ctas_per_sm < 1) return fail(MAC_B200_ECUDA, "decode kernel has zero occupancy");
-      cudaFuncAttributes fa{};
-      MAC_CUDA(cudaFuncGetAttributes(&fa, mac_decode_persistent_kernel));
-      ds.regs = fa.numRegs;
+      if (const int rc = query_kernel_facts(device, &ds.sm_count, &ds.ctas_per_sm, &ds.regs))
+        return rc;
       ds.ready = true;
     }
     int grid = ds.sm_count * ds.ctas_per_sm;
     if (a.grid_cap > 0 && a.grid_cap < grid) grid = a.grid_cap;
     const int max_pieces = kMaxWaves * grid;
-    const ArenaLayout L = arena_layout(static_cast<int>(NGll), G, max_pieces);
+    const ArenaLayout L = arena_layout(NG, G, max_pieces);
     if (L.total > ds.arena_bytes) {
       cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
       MAC_CUDA(cudaStreamIsCapturing(stream, &cs));
@@ -1798,49 +1895,8 @@ extern "C" int mac_b200_persistent_decode_bf16(const MacB200DecodeArgs* args, vo
     ds.last_grid = grid;
     st = ds;
   }
-
-  DecodeParams p;
-  p.a = a;
-  p.G = G;
-  p.NG = static_cast<int>(NGll);
-  p.F = a.front_sink_tokens > 0 ? a.front_sink_tokens : 0;
-  p.tm_used = (a.M + a.match_tile_slots - 1) / a.match_tile_slots;
-  p.max_pieces = kMaxWaves * st.last_grid;
-  p.force_waves = piece_waves_override();
-  p.ovh_tok = row_overhead_tokens(G);
-  p.min_piece = env_int_or("MAC_B200_MIN_PIECE", kMinPieceTok, 64, 1 << 20);
-  p.fuse_max = env_int_or("MAC_B200_FUSE_MAX", static_cast<int>(kFuseMaxCost), 0, 1 << 24);
-  {
-    float t = 2.0f * static_cast<float>(a.D);   // mac_decode_persistent.cu:5342, in float
-    t = t * (1.0f - a.threshold);
-    t = t * (1.0f - a.threshold);
-    p.thr_dist = t;
-  }
-  p.scale_log2 = a.sm_scale * kLog2e;
-  const ArenaLayout L = arena_layout(p.NG, G, p.max_pieces);
-  char* base = static_cast<char*>(st.arena);
-  p.ar.ticket = reinterpret_cast<uint32_t*>(base + L.ticket);
-  p.ar.garrive = reinterpret_cast<int32_t*>(base + L.garrive);
-  p.ar.plan = reinterpret_cast<GroupPlan*>(base + L.plan);
-  p.ar.part_lse = reinterpret_cast<float*>(base + L.part_lse);
-  p.ar.part_o = reinterpret_cast<float*>(base + L.part_o);
-  p.ar.slots = L.slots;
-
-  void* kargs[] = {&p};
-  static const bool plain = [] {
-    const char* e = std::getenv("MAC_B200_PLAIN_LAUNCH");
-    return e && std::atoi(e) != 0;
-  }();
-  if (plain) {
-    mac_decode_persistent_kernel<<<st.last_grid, kThreads, kSmemBytes, stream>>>(p);
-    MAC_CUDA(cudaGetLastError());
-  } else {
-    MAC_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(mac_decode_persistent_kernel),
-                                         dim3(st.last_grid), dim3(kThreads), kargs, kSmemBytes,
-                                         stream));
-  }
-  g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
-  return MAC_B200_OK;
+  const DecodeParams p = make_decode_params(a, st.arena, kMaxWaves * st.last_grid);
+  return launch_decode(device, p, st.last_grid, stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -1875,37 +1931,11 @@ extern "C" int mac_b200_persistent_decode_bf16_noalloc(const MacB200DecodeArgs* 
   MAC_REQUIRE(args != nullptr, "decode args must not be null");
   const MacB200DecodeArgs& a = *args;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  MAC_REQUIRE(a.D == kD, "persistent decode supports D=128 only");
-  MAC_REQUIRE(a.Hkv > 0 && a.Hq > 0 && a.Hq % a.Hkv == 0, "Hq must be divisible by Hkv");
+  bool empty = false;
+  if (const int rc = validate_decode_args(a, &empty)) return rc;
+  if (empty) return MAC_B200_OK;
   const int G = a.Hq / a.Hkv;
-  MAC_REQUIRE(G > 0 && G <= 8, "unsupported GQA group size");
-  MAC_REQUIRE(a.N >= 0, "negative batch");
-  MAC_REQUIRE(a.M > 0 && a.R > 0, "ring tensors must not be empty");
-  MAC_REQUIRE(a.match_tile_slots > 0, "match_tile_slots must be positive");
-  MAC_REQUIRE(a.max_match_tiles >= (a.M + a.match_tile_slots - 1) / a.match_tile_slots,
-              "match workspace too small");
-  MAC_REQUIRE(a.ws_batch >= a.N, "decision workspaces are smaller than the batch");
-  MAC_REQUIRE(a.bench_mode == 0 || a.bench_mode == 1 || a.bench_mode == 2,
-              "unsupported synthetic MAC bench mode");
-  MAC_REQUIRE(a.phase_cycles_count >= 6 && a.phase_cycles,
-              "phase_cycles must have at least 6 elements");
-  MAC_REQUIRE(a.q_post && a.q_pre && a.k_buffer && a.v_buffer && a.req_to_token && a.req_ids &&
-                  a.past_lens && a.out_cache_loc && a.query_cache && a.attn_cache && a.lse_cache &&
-                  a.out,
-              "input/output tensors must not be null");
-  MAC_REQUIRE(a.match_dist && a.match_pos && a.match_slot && a.head_hit && a.head_match_slot &&
-                  a.head_match_pos && a.head_prefix_end && a.head_rect_start && a.head_new_end &&
-                  a.group_rect_begin && a.group_rect_end && a.group_rect_tiles &&
-                  a.group_tail_begin && a.group_tail_end && a.group_tail_tiles && a.group_mode &&
-                  a.task_counts,
-              "workspace tensors must not be null");
-  if (a.N == 0) return MAC_B200_OK;
-  if (a.Hq > kMaxHq)
-    return fail(MAC_B200_EUNSUPPORTED, "Hq=%d exceeds this build's limit of %d", a.Hq, kMaxHq);
   const long long NGll = static_cast<long long>(a.N) * a.Hkv;
-  if (NGll > kMaxGroups)
-    return fail(MAC_B200_EUNSUPPORTED, "N*Hkv=%lld exceeds this build's limit of %d", NGll,
-                kMaxGroups);
 
   int device = 0;
   MAC_CUDA(cudaGetDevice(&device));
@@ -1919,15 +1949,8 @@ extern "C" int mac_b200_persistent_decode_bf16_noalloc(const MacB200DecodeArgs* 
       // attributes, occupancy, and the device address of the fixed block.  In
       // host code the array's name is only a handle for the runtime; the
       // address a kernel can use comes from cudaGetSymbolAddress.
-      int coop = 0;
-      MAC_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device));
-      if (!coop) return fail(MAC_B200_EUNSUPPORTED, "device does not support cooperative launch");
-      MAC_CUDA(cudaFuncSetAttribute(mac_decode_persistent_kernel,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-      MAC_CUDA(cudaDeviceGetAttribute(&ds.sm_count, cudaDevAttrMultiProcessorCount, device));
-      MAC_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(
-          &ds.ctas_per_sm, mac_decode_persistent_kernel, kThreads, kSmemBytes));
-      if (ds.ctas_per_sm < 1) return fail(MAC_B200_ECUDA, "decode kernel has zero occupancy");
+      int regs = 0;
+      if (const int rc = query_kernel_facts(device, &ds.sm_count, &ds.ctas_per_sm, &regs)) return rc;
       void* sym = nullptr;
       MAC_CUDA(cudaGetSymbolAddress(&sym, g_noalloc_arena));
       if (sym == nullptr) return fail(MAC_B200_ECUDA, "fixed scratch block has no device address");
@@ -1947,41 +1970,12 @@ extern "C" int mac_b200_persistent_decode_bf16_noalloc(const MacB200DecodeArgs* 
                 "group) but the fixed block holds %zu; use mac_b200_persistent_decode_bf16 or a "
                 "smaller batch",
                 L.total, NGll, G, kNoAllocArenaBytes);
-
-  DecodeParams p;
-  p.a = a;
-  p.G = G;
-  p.NG = static_cast<int>(NGll);
-  p.F = a.front_sink_tokens > 0 ? a.front_sink_tokens : 0;
-  p.tm_used = (a.M + a.match_tile_slots - 1) / a.match_tile_slots;
-  p.max_pieces = max_pieces;
-  p.force_waves = piece_waves_override();
-  p.ovh_tok = row_overhead_tokens(G);
-  p.min_piece = env_int_or("MAC_B200_MIN_PIECE", kMinPieceTok, 64, 1 << 20);
-  p.fuse_max = env_int_or("MAC_B200_FUSE_MAX", static_cast<int>(kFuseMaxCost), 0, 1 << 24);
-  {
-    float t = 2.0f * static_cast<float>(a.D);
-    t = t * (1.0f - a.threshold);
-    t = t * (1.0f - a.threshold);
-    p.thr_dist = t;
-  }
-  p.scale_log2 = a.sm_scale * kLog2e;
-  char* base = static_cast<char*>(st.arena);
-  p.ar.ticket = reinterpret_cast<uint32_t*>(base + L.ticket);
-  p.ar.garrive = reinterpret_cast<int32_t*>(base + L.garrive);
-  p.ar.plan = reinterpret_cast<GroupPlan*>(base + L.plan);
-  p.ar.part_lse = reinterpret_cast<float*>(base + L.part_lse);
-  p.ar.part_o = reinterpret_cast<float*>(base + L.part_o);
-  p.ar.slots = L.slots;
   // The block keeps whatever the previous call left in it.  The words that
   // must start at zero (piece ticket, per-group arrival counters) are cleared
   // by the kernel's first phase before any CTA reads them; everything else is
   // written before it is read within one launch.
-  void* kargs[] = {&p};
-  MAC_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(mac_decode_persistent_kernel),
-                                       dim3(grid), dim3(kThreads), kargs, kSmemBytes, stream));
-  g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
-  return MAC_B200_OK;
+  const DecodeParams p = make_decode_params(a, st.arena, max_pieces);
+  return launch_decode(device, p, grid, stream);
 }
 
 extern "C" int mac_b200_query_status(uint32_t* status_out, void* stream_v) {
@@ -1990,7 +1984,9 @@ extern "C" int mac_b200_query_status(uint32_t* status_out, void* stream_v) {
   MAC_CUDA(cudaStreamSynchronize(stream));
   unsigned v = 0;
   MAC_CUDA(cudaMemcpyFromSymbol(&v, g_status, sizeof(v)));
-  *status_out = v;
+  unsigned build_bits = 0;
+  if (const int rc = take_prefill_build_status(&build_bits)) return rc;
+  *status_out = v | build_bits;
   if (v != 0) {
     const unsigned zero = 0;
     MAC_CUDA(cudaDeviceSynchronize());

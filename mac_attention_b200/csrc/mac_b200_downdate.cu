@@ -136,6 +136,9 @@ extern "C" int mac_b200_update_then_downdate_bf16_inplace(const void* out1, cons
   p.D = D;
   p.dt1 = lse1_dtype;
   p.dt2 = lse2_dtype;
+  int device = 0;
+  MAC_CUDA(cudaGetDevice(&device));
+  const int64_t max_blocks = static_cast<int64_t>(device_sm_count(device)) * 32;
   const bool vec = D % 8 == 0 && ((reinterpret_cast<uintptr_t>(out1) | reinterpret_cast<uintptr_t>(out2)) & 15u) == 0;
   if (vec) {
     p.chunks = D / 8;
@@ -146,14 +149,14 @@ extern "C" int mac_b200_update_then_downdate_bf16_inplace(const void* out1, cons
     while ((32 / lpr) * p.unroll > 32) p.unroll >>= 1;   // narrow rows: fewer rows in flight per lane
     const int64_t rows_per_cta = static_cast<int64_t>(kDownThreads / 32) * (32 / lpr) * p.unroll;
     int64_t blocks = (rows + rows_per_cta - 1) / rows_per_cta;
-    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (blocks > max_blocks) blocks = max_blocks;
     downdate_inplace_kernel<<<static_cast<unsigned>(blocks), kDownThreads, 0, stream>>>(p);
   } else {
     p.chunks = 0;
     p.unroll = 1;
     p.lanes_per_row = 32;
     int64_t blocks = (rows + 7) / 8;
-    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (blocks > max_blocks) blocks = max_blocks;
     downdate_inplace_scalar_kernel<<<static_cast<unsigned>(blocks), kDownThreads, 0, stream>>>(p);
   }
   MAC_CUDA(cudaGetLastError());

@@ -281,6 +281,16 @@ __device__ __forceinline__ float sx_ex2(float x) {
   return y;
 }
 
+// Sticky status bits raised by the kernels of this file (read and cleared
+// through mac_b200_query_status together with the decode kernel's word).
+__device__ unsigned g_build_status = 0;
+
+// A request whose id has no row in req_to_token cannot have its sink attention
+// computed: its ring rows are not built and it is not marked ready.
+__device__ __forceinline__ bool sink_request_out_of_table(const MacB200PrefillBuildArgs& a, int req) {
+  return a.sink_mode == MAC_B200_SINK_EXCLUDE && req >= a.req_to_token_rows;
+}
+
 // grid = (slices, Hkv, B); G = query heads per KV head
 template <int G>
 __global__ void __launch_bounds__(kSxThreads, 1)
@@ -290,7 +300,10 @@ prefill_sink_exclusive_ring_kernel(const MacB200PrefillBuildArgs a) {
   const MacB200PrefillArgs& p = a.ring;
   const RowSpan sp = row_span(p, blockIdx.z);
   if (!sp.ok) return;
-  if (sp.req >= a.req_to_token_rows) return;
+  if (sink_request_out_of_table(a, sp.req)) {
+    if (threadIdx.x == 0) atomicOr(&g_build_status, MAC_B200_STATUS_BAD_REQUEST);
+    return;
+  }
   const int H = p.H, Hkv = a.Hkv;
   const int kh = blockIdx.y;
   const int F = a.front_sink_tokens;
@@ -311,6 +324,8 @@ prefill_sink_exclusive_ring_kernel(const MacB200PrefillBuildArgs a) {
       int64_t tok = -1;
       if (j < F && j < a.req_to_token_stride) tok = table[j];
       const bool ok = tok >= 0 && tok < a.kv_tokens;
+      if (j < F && !ok && c == 0)   // a sink position without a valid pool row reads as zeros
+        atomicOr(&g_build_status, MAC_B200_STATUS_BAD_REQUEST);
       const int64_t off = (ok ? tok : 0) * tok_stride + c * 16;
       const uint32_t dst = j * kSxRowBytes + ((c ^ (j & 7)) << 4);
       sx_cp_async16(sx_smem_u32(ks) + dst, kb + off, ok ? 16 : 0);
@@ -596,6 +611,7 @@ __global__ void prefill_build_finish_kernel(const MacB200PrefillBuildArgs a) {
   if (b >= p.B) return;
   const int req = p.req_ids[b];
   if (req < 0 || req >= p.R) return;
+  if (sink_request_out_of_table(a, req)) return;   // rows were not built: not ready, length kept
   if (a.ready) {
     a.cache_epoch[req] = a.request_epoch[req];
     a.ready[req] = 1;
@@ -609,6 +625,18 @@ __global__ void prefill_build_finish_kernel(const MacB200PrefillBuildArgs a) {
 }
 
 }  // namespace
+
+int take_prefill_build_status(unsigned* bits) {
+  unsigned v = 0;
+  MAC_CUDA(cudaMemcpyFromSymbol(&v, g_build_status, sizeof(v)));
+  if (v != 0) {
+    const unsigned zero = 0;
+    MAC_CUDA(cudaMemcpyToSymbol(g_build_status, &zero, sizeof(zero)));
+  }
+  *bits = v;
+  return MAC_B200_OK;
+}
+
 }  // namespace mac_b200
 
 using namespace mac_b200;
@@ -668,8 +696,7 @@ extern "C" int mac_b200_prefill_downdate_update_cache(const MacB200PrefillBuildA
     // the attribute is per device: set it on every call (cheap, no synchronisation)
     MAC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   kSxSmemBytes));
-    int sms = 148;
-    MAC_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    const int sms = device_sm_count(device);
     const int TG = 16 / G;
     const int max_tiles = ((p.M < 1 ? 1 : p.M) + TG - 1) / TG;
     const int pairs = p.B * a.Hkv;

@@ -251,7 +251,10 @@ extern "C" int mac_b200_decode_rope_preserve_q_bf16(const MacB200RopeArgs* args,
     const int64_t total = a.N * (static_cast<int64_t>(a.Hq + a.Hkv) * (D - R / 2) +
                                  static_cast<int64_t>(a.Hkv) * D);
     int64_t blocks = (total + kRopeThreads - 1) / kRopeThreads;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    int device = 0;
+    MAC_CUDA(cudaGetDevice(&device));
+    const int64_t max_blocks = static_cast<int64_t>(device_sm_count(device)) * 16;
+    if (blocks > max_blocks) blocks = max_blocks;
     if (blocks < 1) blocks = 1;
     rope_preserve_scalar_kernel<<<static_cast<unsigned>(blocks), kRopeThreads, 0, stream>>>(a);
   }

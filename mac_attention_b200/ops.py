@@ -289,14 +289,15 @@ _ARG_CACHE_ON = os.environ.get("MAC_B200_NO_ARG_CACHE", "0") != "1"
 
 
 def _decode_key(args):
-    """Identity of a call for the marshalling cache: every tensor's address, the
-    shapes the struct is derived from, and all scalars.  A repeat of the same
-    call (serving loops and graph warm-ups pass the same buffers every step)
-    reuses the checked argument struct instead of re-validating ~50 tensors."""
-    ptrs = tuple(0 if args[i] is None else args[i].data_ptr() for i in _TENSOR_ARGS)
-    return (ptrs, args[43:64], tuple(args[0].shape), tuple(args[2].shape[:2]),
-            tuple(args[4].shape), tuple(args[8].shape[:2]), tuple(args[13].shape),
-            args[42].numel(), args[12].numel(), args[7].dtype, args[0].device)
+    """Identity of a call for the marshalling cache: address, shape, dtype and
+    contiguity of EVERY tensor argument plus all scalars.  A caching allocator
+    can hand the same address to a tensor of another shape or dtype, so the
+    address alone does not identify a buffer.  A repeat of the same call
+    (serving loops and graph warm-ups pass the same buffers every step) reuses
+    the checked argument struct instead of re-validating ~50 tensors."""
+    ident = tuple(None if t is None else (t.data_ptr(), t.shape, t.dtype, t.is_contiguous())
+                  for t in (args[i] for i in _TENSOR_ARGS))
+    return (ident, args[43:64], args[0].device)
 
 
 def _decode_entry(entry_name, args) -> None:

@@ -525,8 +525,15 @@ static void attend_item(void* ctx, int idx) {
  * receive the un-rounded output and ring state for tolerance checks.
  * Returns the number of rows skipped as malformed (those rows get zeros).
  */
-ORACLE_API int mac_oracle_decode_step(const MacB200DecodeArgs* a, float* out_f32,
-                                      float* ring_o_f32) {
+/*
+ * row_mask (optional, [N] bytes): rows whose byte is 0 are left out of the step
+ * entirely (no decisions, no attention, zero outputs, not counted anywhere)
+ * while N and the row indices of the other rows stay what they are -- the
+ * synthetic-decision hash depends on both.  Lets a test check a sample of a
+ * large batch without holding every request's K/V on the host.
+ */
+ORACLE_API int mac_oracle_decode_step_rows(const MacB200DecodeArgs* a, float* out_f32,
+                                           float* ring_o_f32, const uint8_t* row_mask) {
   const int N = a->N, Hq = a->Hq, Hkv = a->Hkv, D = a->D, M = a->M;
   if (D != 128 || Hkv <= 0 || Hq % Hkv != 0) return -1;
   const int G = Hq / Hkv;
@@ -539,6 +546,10 @@ ORACLE_API int mac_oracle_decode_step(const MacB200DecodeArgs* a, float* out_f32
   int nonhit = 0, full = 0;
 
   for (int n = 0; n < N; ++n) {
+    if (row_mask && !row_mask[n]) {
+      bad[n] = 2; /* left out on request */
+      continue;
+    }
     bad[n] = request_bad(a, n);
     bad_rows += bad[n];
   }
@@ -651,6 +662,11 @@ ORACLE_API int mac_oracle_decode_step(const MacB200DecodeArgs* a, float* out_f32
   free(gmode);
   free(bad);
   return bad_rows;
+}
+
+ORACLE_API int mac_oracle_decode_step(const MacB200DecodeArgs* a, float* out_f32,
+                                      float* ring_o_f32) {
+  return mac_oracle_decode_step_rows(a, out_f32, ring_o_f32, NULL);
 }
 
 /* Decisions only (no attention): for large-shape decision parity. */

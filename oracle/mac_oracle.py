@@ -38,6 +38,9 @@ def lib() -> C.CDLL:
         _lib = C.CDLL(str(LIB))
         _lib.mac_oracle_decode_step.restype = C.c_int
         _lib.mac_oracle_decode_step.argtypes = [C.POINTER(_abi.MacB200DecodeArgs), C.c_void_p, C.c_void_p]
+        _lib.mac_oracle_decode_step_rows.restype = C.c_int
+        _lib.mac_oracle_decode_step_rows.argtypes = [C.POINTER(_abi.MacB200DecodeArgs), C.c_void_p,
+                                                     C.c_void_p, C.c_void_p]
         _lib.mac_oracle_decide.restype = C.c_int
         _lib.mac_oracle_decide.argtypes = [C.POINTER(_abi.MacB200DecodeArgs), C.c_void_p, C.c_void_p, C.c_void_p]
         _lib.mac_oracle_prefill_update_cache.restype = C.c_int
@@ -126,8 +129,11 @@ def _p(t):
 
 def decode_step(q_post, q_pre, k_buffer, v_buffer, req_to_token, req_ids, past_lens,
                 out_cache_loc, query_cache, attn_cache, lse_cache, cfg: DecodeConfig,
-                cache_ready=None, cache_epoch=None, request_epoch=None) -> DecodeResult:
-    """One MAC decode step on the CPU; the three ring tensors are updated in place."""
+                cache_ready=None, cache_epoch=None, request_epoch=None,
+                row_mask=None) -> DecodeResult:
+    """One MAC decode step on the CPU; the three ring tensors are updated in place.
+    ``row_mask`` (uint8 ``[N]``): rows with 0 are left out of the step while the batch
+    size and the other rows' indices stay (the synthetic-decision hash uses both)."""
     for t in (q_post, q_pre, k_buffer, v_buffer, req_to_token, req_ids, past_lens, out_cache_loc,
               query_cache, attn_cache, lse_cache):
         assert t.device.type == "cpu" and t.is_contiguous()
@@ -178,7 +184,10 @@ def decode_step(q_post, q_pre, k_buffer, v_buffer, req_to_token, req_ids, past_l
         a.cache_ready = _p(ready_u8)
         if cache_epoch is not None and request_epoch is not None and cache_epoch.numel() > 0:
             a.cache_epoch, a.request_epoch = _p(cache_epoch), _p(request_epoch)
-    res.bad_rows = lib().mac_oracle_decode_step(C.byref(a), _p(res.out_f32), _p(res.ring_o_f32))
+    if row_mask is not None:
+        assert row_mask.dtype == torch.uint8 and row_mask.numel() == N and row_mask.is_contiguous()
+    res.bad_rows = lib().mac_oracle_decode_step_rows(C.byref(a), _p(res.out_f32),
+                                                     _p(res.ring_o_f32), _p(row_mask))
     if res.bad_rows < 0:
         raise RuntimeError("oracle rejected the shapes")
     return res

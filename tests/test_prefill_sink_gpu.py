@@ -146,6 +146,37 @@ def test_sink_exclusive_argument_errors():
         _build(ext.mac_prefill_downdate_update_cache, bad, 32, 8, 4, 16)
 
 
+def test_request_without_a_page_table_row_is_reported_and_left_unbuilt():
+    """A request id that is a valid ring row but has no row in ``req_to_token`` cannot get
+    its sink attention: its ring rows stay as they were, it is NOT marked ready, its length
+    is not bumped, and the sticky status word reports a bad request.  The other request of
+    the batch is built as usual.  (The access is guarded; nothing faults.)"""
+    ext = load_mac_prefill_update_cache_extension()
+    Hq, Hkv, S, F, M = 8, 2, 8, 32, 64
+    t = _prompts([70, 50], [0, 0], Hq, Hkv, S, F, M, seed=9)
+    t.pop("want_o"), t.pop("want_l")
+    # three ring rows, two page-table rows; the second prompt claims ring row 2
+    for name in ("q_cache", "attn_cache", "lse_cache", "q_post_cache"):
+        t[name] = torch.cat([t[name], t[name][:1].clone()])
+    t["ready"] = torch.zeros(3, dtype=torch.bool)
+    t["cache_epoch"] = torch.full((3,), -1, dtype=torch.int64)
+    t["request_epoch"] = torch.arange(3, dtype=torch.int64) + 2
+    t["request_length"] = torch.zeros(3, dtype=torch.int32)
+    t["req_ids"] = torch.tensor([0, 2], dtype=torch.int32)
+    gpu = {k: v.cuda() for k, v in t.items()}
+    assert ops.query_status() == 0
+    _build(ext.mac_prefill_downdate_update_cache, gpu, M, Hq, S, F)
+    torch.cuda.synchronize()
+    status = ops.query_status()
+    assert status & 0x2, status                       # MAC_B200_STATUS_BAD_REQUEST
+    assert ops.query_status() == 0                    # read clears it
+    assert gpu["ready"].cpu().tolist() == [True, False, False]
+    assert gpu["request_length"].cpu().tolist() == [70, 0, 0]
+    assert torch.equal(gpu["q_cache"][2].cpu(), t["q_cache"][2])
+    assert torch.equal(gpu["attn_cache"][2].cpu(), t["attn_cache"][2])
+    assert not torch.equal(gpu["q_cache"][0].cpu(), t["q_cache"][0])     # request 0 was built
+
+
 def test_one_pass_build_replays_from_a_cuda_graph():
     ext = load_mac_prefill_update_cache_extension()
     spec = SPECS[0]

@@ -58,6 +58,40 @@ def test_noalloc_entry_matches_allocating_entry_twice_in_a_row():
     assert ops.query_status() == 0
 
 
+def test_noalloc_entry_leaves_free_device_memory_unchanged():
+    """The point of the entry: the driver hands out no device memory for it.  Free memory
+    as the driver reports it is the same before and after a call (the inputs are made
+    first, and the first call on the device -- which looks up the block's address -- is
+    made before the measurement)."""
+    ext = load_mac_persistent_decode_extension()
+    cfg = O.DecodeConfig(max_context=4096, semantic_pos_ahead=128)
+    case = synth.make_decode_case(batch=3, ctx=0, ctx_list=[2500, 700, 3300], hq=32, hkv=8,
+                                  capacity=256, seed=41)
+    c = case.to("cuda").clone()
+    ws = make_decode_workspace(3, 32, 8, 256, cfg.max_context, cfg.tile_tokens,
+                               cfg.match_tile_slots, cfg.semantic_pos_ahead)
+    out = torch.empty_like(c.q_post)
+    lse = torch.empty(3, 32, device="cuda")
+    e = torch.empty(0)
+
+    def call():
+        ext.mac_persistent_decode_bf16_noalloc(
+            c.q_post, c.q_pre, c.k, c.v, c.req_to_token, c.req_ids, c.past_lens, c.out_cache_loc,
+            c.query_cache, c.attn_cache, c.lse_cache, out, lse, *ws, *cfg.scalar_args(),
+            c.query_cache, e, e, e)
+        torch.cuda.synchronize()
+
+    call()                                   # set-up call
+    free_before, _ = torch.cuda.mem_get_info()
+    reserved_before = torch.cuda.memory_reserved()
+    call()
+    call()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    assert torch.cuda.memory_reserved() == reserved_before
+    assert ops.query_status() == 0
+
+
 def test_noalloc_entry_refuses_steps_beyond_its_fixed_block():
     ext = load_mac_persistent_decode_extension()
     cfg = O.DecodeConfig(max_context=256, semantic_pos_ahead=16)
