@@ -48,6 +48,7 @@ extern "C" {
 #define MAC_B200_STATUS_BARRIER_TIMEOUT 0x1u /* a bounded grid-barrier wait ran out         */
 #define MAC_B200_STATUS_BAD_REQUEST 0x2u     /* req id / length outside the tables; row zeroed */
 #define MAC_B200_STATUS_SCHED_OVERFLOW 0x4u  /* internal schedule exceeded its arena         */
+#define MAC_B200_STATUS_COPY_TIMEOUT 0x8u    /* a bounded wait on a bulk copy ran out          */
 
 /*
  * Arguments of one fused MAC decode step.

@@ -24,6 +24,7 @@
 // Semantics follow the reference kernel
 // attention/src/mac_attention/integrations/sglang/csrc/mac_decode_persistent.cu
 // (cited as DEC.cu below); structure, scheduling and data flow are new.
+#include <cuda.h>
 #include <cuda_bf16.h>
 
 #include <climits>
@@ -58,6 +59,9 @@ constexpr int kSmemPerm = kMaxGroups * 2;              // u16 gperm[]
 constexpr int kSmemPrefix = (kMaxGroups + 1) * 4;      // u32 cost prefix
 constexpr int kSmemMisc = 1024;
 constexpr int kSmemBytes = kRingBytes + kSmemPerm + kSmemPrefix + 12 + kSmemMisc;
+// mbarrier words of the bulk-copy scan (64-byte aligned, inside the kSmemMisc tail)
+constexpr int kSmemBars = (kRingBytes + kSmemPerm + kSmemPrefix + 12 + 63) / 64 * 64;
+static_assert(kSmemBars + 64 <= kSmemBytes, "mbarrier words must fit the tail");
 constexpr unsigned long long kBarrierLimitNs = 2000000000ull;  // a grid-barrier wait gives up after 2 s
 constexpr float kLog2e = 1.4426950408889634074f;
 constexpr float kLn2 = 0.6931471805599453094f;
@@ -102,6 +106,7 @@ struct DecodeParams {
   int32_t ovh_tok;       // cost of opening a row, in token equivalents (kOvhTok unless overridden)
   int32_t min_piece;     // smallest piece worth its fixed cost (kMinPieceTok unless overridden)
   int32_t fuse_max;      // groups up to this cost are never split (kFuseMaxCost unless overridden)
+  int32_t scan_mode;     // 0: per-thread cp.async staging; 1 / 2: bulk tensor copies, 64 B / 128 B probe
 };
 
 // ------------------------------------------------------------- small helpers
@@ -661,6 +666,452 @@ __device__ void phase_match_scan(const DecodeParams& p, uint8_t* smem) {
       }
       __syncthreads();
     }
+  }
+}
+
+
+// ------------------------------------------------- phase A, bulk-copy variant
+// The same match scan with the ring rows brought in by the copy engine instead
+// of by per-thread cp.async: the ring is viewed as a 2-D tensor [R*M*Hq rows,
+// 128 bf16] and ONE elected thread issues a tiled bulk copy
+// (cp.async.bulk.tensor.2d, completion on an mbarrier) of the probe columns of
+// 256 consecutive rows -- one row per thread.  The rows of a (request, match
+// tile) are consecutive in that view, so a tile is a handful of such boxes.
+// The other 255 threads issue no address arithmetic and no copy instructions
+// at all; each evaluates the probe of its own row straight from shared memory
+// (swizzled by the copy engine, so the 256 row reads are bank-conflict free).
+//
+//  * Probe width kChunks * 16 bytes (64 B = dims 0..31, or 128 B = dims 0..63):
+//    the partial distance over a prefix of the dims is a lower bound of the
+//    full one whatever the prefix, and it is formed per 16-byte chunk in packed
+//    bf16 exactly as in the cp.async variant (same error bound, same widened
+//    threshold), the chunk sums added in fp32.
+//  * A row that passes the probe is re-read whole from global memory by its
+//    thread and its exact distance formed in the reference's order
+//    (DEC.cu:1062-1069, 343-349): sixteen 8-dim sums of sequential FMAs, then
+//    pairwise at chunk distance 8, 4, 2, 1.  The per-(tile, head) minimum with
+//    the (distance, older position) order is kept by a 64-bit atomicMin in
+//    shared memory on (distance bits << 32 | position): distances are
+//    non-negative, so their bit patterns order like the values, NaNs order
+//    above +inf and never win.
+//  * Every wait on a copy is bounded (wall time); on expiry the CTA records
+//    MAC_B200_STATUS_COPY_TIMEOUT, waits (bounded again) for the copies it still
+//    has in flight and the kernel returns.
+constexpr int kTmaBoxRows = 256;
+constexpr unsigned long long kCopyWaitLimitNs = 2000000000ull;
+constexpr unsigned long long kCopyDrainLimitNs = 50000000ull;
+constexpr unsigned long long kNoMatchKey = (0x7f800000ull << 32) | 0x7fffffffull;   // (+inf, INT_MAX)
+
+struct BoxTile {
+  int n, tile, P, cbeg, cend, s_begin, nrows, tail, off_lo, off_hi, nbox, row0;
+};
+static_assert(sizeof(BoxTile) == 48, "three int4 loads");
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      " selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
+                                                  unsigned long long limit_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns_u64();
+  unsigned polls = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++polls & 63u) == 0u && global_ns_u64() - t0 > limit_ns) return false;
+  }
+  return true;
+}
+__device__ __forceinline__ void bulk_tensor_load_2d(uint32_t dst, const CUtensorMap* map, int x,
+                                                    int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, "
+      "%3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+// Exact distance of one ring row (global memory) to one query row, reference
+// summation order; updates the per-(tile, head) minimum.
+__device__ __noinline__ void scan_exact_row(const char* row, const char* qrow, int pos,
+                                            unsigned long long* best) {
+  float sum[16];
+#pragma unroll
+  for (int c = 0; c < 16; ++c) {
+    const uint4 rv = ld_stream16(row + c * 16);
+    const uint4 qv = __ldg(reinterpret_cast<const uint4*>(qrow + c * 16));
+    float qf[8];
+    unpack8(qv, qf);
+    sum[c] = scan_dist8(qf, rv);
+  }
+#pragma unroll
+  for (int c = 0; c < 8; ++c) sum[c] = __fadd_rn(sum[c], sum[c + 8]);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) sum[c] = __fadd_rn(sum[c], sum[c + 4]);
+  sum[0] = __fadd_rn(sum[0], sum[2]);
+  sum[1] = __fadd_rn(sum[1], sum[3]);
+  const float d = __fadd_rn(sum[0], sum[1]);
+  const unsigned long long key =
+      (static_cast<unsigned long long>(__float_as_uint(d)) << 32) | static_cast<unsigned>(pos);
+  atomicMin(best, key);
+}
+
+template <int kChunks>
+__device__ bool phase_match_scan_bulk(const DecodeParams& p, const CUtensorMap* ring_map,
+                                      uint8_t* smem) {
+  constexpr int kProbeBytes = kChunks * 16;
+  constexpr int kBoxBytes = kTmaBoxRows * kProbeBytes;
+  constexpr int kStagesB = kChunks == 4 ? 8 : 5;
+  static_assert(kStagesB * kBoxBytes + 1024 + kScanRoundTiles * 48 <= kRingBytes, "scan stages must fit");
+  static_assert(2 * kMaxHq * 8 <= kSmemPerm, "best-match words must fit");
+  const MacB200DecodeArgs& a = p.a;
+  const int tid = threadIdx.x;
+  if (blockIdx.x == 0) {
+    if (tid < 9) a.task_counts[tid] = 0;
+    if (tid == 9) *p.ar.ticket = 0u;
+  }
+  for (int g = blockIdx.x * kThreads + tid; g < p.NG; g += gridDim.x * kThreads)
+    p.ar.garrive[g] = 0;
+
+  const int Hq = a.Hq, M = a.M, Tm = a.max_match_tiles;
+  const int total_tiles = a.N * Tm;
+  const int my_tiles = static_cast<int>(blockIdx.x) < total_tiles
+                           ? (total_tiles - static_cast<int>(blockIdx.x) +
+                              static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x)
+                           : 0;
+  const uint32_t base_u32 = smem_u32(smem);
+  const uint32_t pad = (1024u - (base_u32 & 1023u)) & 1023u;
+  uint8_t* stage0 = smem + pad;
+  const uint32_t stage0_u32 = base_u32 + pad;
+  BoxTile* tinfo = reinterpret_cast<BoxTile*>(stage0 + kStagesB * kBoxBytes);
+  unsigned long long* best = reinterpret_cast<unsigned long long*>(smem + kRingBytes);  // [2][kMaxHq]
+  const uint32_t bars_u32 = smem_u32(smem + kSmemBars);
+  const float thr_probe = p.thr_dist * 1.0625f;   // see the probe's error bound in scan_probe8's user
+  const bool fixed_head = (kTmaBoxRows % Hq) == 0;   // a thread then keeps one head for every box
+  const char* ring = static_cast<const char*>(a.query_cache);
+  const char* qsrc = static_cast<const char*>(a.q_pre);
+  const int swz = kChunks == 4 ? ((tid >> 1) & 3) : (tid & 7);
+  const uint8_t* my_row = stage0 + tid * kProbeBytes;
+
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < kStagesB; ++s) mbar_init(bars_u32 + s * 8, 1);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  for (int i = tid; i < 2 * kMaxHq; i += kThreads) best[i] = kNoMatchKey;
+  __syncthreads();
+
+  unsigned seq_base = 0;   // boxes consumed in earlier rounds (stage and parity carry over)
+  bool failed = false;
+  for (int r0 = 0; r0 < my_tiles && !failed; r0 += kScanRoundTiles) {
+    const int rt = min(kScanRoundTiles, my_tiles - r0);
+    if (tid < rt) {
+      ScanCursor c;
+      scan_load_tile(a, blockIdx.x + (r0 + tid) * gridDim.x, c);
+      BoxTile t;
+      t.n = c.n; t.tile = c.tile; t.P = c.P; t.cbeg = c.cbeg; t.cend = c.cend;
+      t.s_begin = c.s_begin; t.nrows = (c.s_end - c.s_begin) * Hq;
+      t.tail = c.tail; t.off_lo = c.off_lo; t.off_hi = c.off_hi;
+      t.row0 = (c.req * M + c.s_begin) * Hq;
+      bool any = false;
+      if (c.elig)
+        for (int s = c.s_begin; s < c.s_end; ++s) {
+          const int pos = scan_slot_pos(c, s);
+          any = any || (pos >= c.cbeg && pos < c.cend);
+        }
+      t.nbox = any ? (t.nrows + kTmaBoxRows - 1) / kTmaBoxRows : 0;
+      tinfo[tid] = t;
+    }
+    __syncthreads();
+    int nact = 0;
+    for (int k = 0; k < rt; ++k) nact += tinfo[k].nbox;
+    // tiles without a candidate row report "no match" (the classifier reads every tile)
+    for (int k = 0; k < rt; ++k) {
+      if (tinfo[k].nbox != 0 || tid >= Hq) continue;
+      const int64_t off = (static_cast<int64_t>(tinfo[k].n) * Hq + tid) * Tm + tinfo[k].tile;
+      a.match_dist[off] = INFINITY;
+      a.match_pos[off] = INT_MAX;
+      a.match_slot[off] = -1;
+    }
+    // producer cursor (thread 0) and consumer cursor (every thread) over the active boxes
+    int pk = 0, pb = -1, ck = 0, cb = -1;
+    auto advance = [&](int& k, int& b) {
+      ++b;
+      while (k < rt && b >= tinfo[k].nbox) { ++k; b = 0; }
+    };
+    unsigned issued = 0;
+    auto issue = [&](unsigned i) {   // thread 0: box pk/pb into stage (seq_base + i) % kStagesB
+      const unsigned sq = seq_base + i;
+      const uint32_t bar = bars_u32 + (sq % kStagesB) * 8;
+      mbar_expect_tx(bar, kBoxBytes);
+      bulk_tensor_load_2d(stage0_u32 + (sq % kStagesB) * kBoxBytes, ring_map, 0,
+                          tinfo[pk].row0 + pb * kTmaBoxRows, bar);
+    };
+    if (tid == 0) {
+      advance(pk, pb);
+      while (issued < static_cast<unsigned>(min(kStagesB, nact))) {
+        issue(issued);
+        ++issued;
+        advance(pk, pb);
+      }
+    }
+    uint4 q[kChunks], qn[kChunks];   // this tile's query chunks, the next active tile's (in flight)
+    bool have_qn = false;
+    int my_h = 0;
+    auto load_q = [&](int n, uint4 (&dst)[kChunks]) {
+      const uint4* qp = reinterpret_cast<const uint4*>(
+          qsrc + (static_cast<int64_t>(n) * Hq + my_h) * kRowBytes);
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) dst[c] = __ldg(qp + c);
+    };
+    int job = 0;   // active tiles seen so far in this round (selects the best-match buffer)
+    BoxTile t{};
+    advance(ck, cb);
+    for (int i = 0; i < nact; ++i) {
+      const unsigned sq = seq_base + static_cast<unsigned>(i);
+      if (cb == 0) {
+        const int4* src = reinterpret_cast<const int4*>(tinfo + ck);
+        const int4 w0 = src[0], w1 = src[1], w2 = src[2];
+        t.n = w0.x; t.tile = w0.y; t.P = w0.z; t.cbeg = w0.w;
+        t.cend = w1.x; t.s_begin = w1.y; t.nrows = w1.z; t.tail = w1.w;
+        t.off_lo = w2.x; t.off_hi = w2.y; t.nbox = w2.z; t.row0 = w2.w;
+        if (fixed_head) {
+          my_h = tid % Hq;
+          if (have_qn) {
+#pragma unroll
+            for (int c = 0; c < kChunks; ++c) q[c] = qn[c];
+          } else {
+            load_q(t.n, q);
+          }
+          int nk = ck + 1;   // the next tile's query is fetched a whole tile ahead
+          while (nk < rt && tinfo[nk].nbox == 0) ++nk;
+          have_qn = nk < rt;
+          if (have_qn) load_q(tinfo[nk].n, qn);
+        }
+      }
+      const int r_local = cb * kTmaBoxRows + tid;
+      bool cand = false;
+      int pos = 0, slot = 0;
+      if (r_local < t.nrows) {
+        const int so = r_local / Hq;
+        slot = t.s_begin + so;
+        if (!fixed_head) my_h = r_local - so * Hq;
+        pos = slot + (slot < t.tail ? t.off_lo : t.off_hi);
+        cand = pos >= t.cbeg && pos < t.cend;
+      }
+      if (!fixed_head && cand) load_q(t.n, q);
+      const bool ok = mbar_wait_bounded(bars_u32 + (sq % kStagesB) * 8, (sq / kStagesB) & 1u,
+                                        kCopyWaitLimitNs);
+      if (ok && cand) {
+        const uint8_t* rowp = my_row + (sq % kStagesB) * kBoxBytes;
+        float probe = 0.0f;
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c)
+          probe += scan_probe8(q[c], *reinterpret_cast<const uint4*>(rowp + ((c ^ swz) << 4)));
+        if (__builtin_expect(probe < thr_probe, 0)) {   // NaN probes drop out here as well
+          scan_exact_row(ring + static_cast<int64_t>(t.row0 + r_local) * kRowBytes,
+                         qsrc + (static_cast<int64_t>(t.n) * Hq + my_h) * kRowBytes, pos,
+                         best + (job & 1) * kMaxHq + my_h);
+        }
+      }
+      const bool last_box = cb == t.nbox - 1;
+      if (__syncthreads_or(ok ? 0 : 1)) {   // some thread's wait ran out: give up as one CTA
+        failed = true;
+        if (tid == 0) {
+          atomicOr(&g_status, MAC_B200_STATUS_COPY_TIMEOUT);
+          for (unsigned j = static_cast<unsigned>(i) + 1; j < issued; ++j)   // copies still in flight
+            mbar_wait_bounded(bars_u32 + ((seq_base + j) % kStagesB) * 8,
+                              ((seq_base + j) / kStagesB) & 1u, kCopyDrainLimitNs);
+        }
+        __syncthreads();
+        break;
+      }
+      if (tid == 0 && issued < static_cast<unsigned>(nact)) {   // the stage just read is free again
+        issue(issued);
+        ++issued;
+        advance(pk, pb);
+      }
+      if (last_box) {
+        if (tid < Hq) {
+          unsigned long long* slotp = best + (job & 1) * kMaxHq + tid;
+          const unsigned long long key = *slotp;
+          *slotp = kNoMatchKey;
+          const int64_t off = (static_cast<int64_t>(t.n) * Hq + tid) * Tm + t.tile;
+          const int bpos = static_cast<int>(key & 0xffffffffull);
+          a.match_dist[off] = __uint_as_float(static_cast<unsigned>(key >> 32));
+          a.match_pos[off] = bpos;
+          a.match_slot[off] = key == kNoMatchKey ? -1 : pos_to_ring_slot(t.P, M, bpos);
+        }
+        ++job;
+      }
+      advance(ck, cb);
+    }
+    seq_base += static_cast<unsigned>(nact);
+    __syncthreads();   // everyone is done with this round's tile descriptors
+  }
+  return !failed;
+}
+
+
+// ------------------------------------------------ phase A, register variant
+// The same match scan with no staging at all: a thread owns one ring row of a
+// 256-row box (the same row-per-thread split as the bulk-copy variant), fetches
+// the probe columns of its row with 32-byte global loads straight into
+// registers, and keeps kDirectDepth boxes in flight by rotating that many
+// register sets (the loop over boxes is unrolled by the depth, so a set is a
+// fixed group of registers).  Threads never wait for one another inside a
+// round: there is no shared-memory stage, no mbarrier and no barrier per box;
+// the per-(tile, head) minima of a whole round sit in shared memory
+// (64-bit atomicMin, as in the bulk-copy variant) and are written out once at
+// the end of the round.  Probe, exact evaluation of survivors and ordering are
+// those of the bulk-copy variant.
+constexpr int kDirectDepth = 4;
+
+__device__ __forceinline__ void ld_stream32(const void* p, uint4& lo, uint4& hi) {
+  asm volatile(
+      "ld.global.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+      : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z),
+        "=r"(hi.w)
+      : "l"(p));
+}
+
+template <int kChunks>
+__device__ void phase_match_scan_direct(const DecodeParams& p, uint8_t* smem) {
+  static_assert(kChunks % 2 == 0, "32-byte loads");
+  static_assert(2048 + kScanRoundTiles * kMaxHq * 8 <= kRingBytes, "round minima must fit");
+  const MacB200DecodeArgs& a = p.a;
+  const int tid = threadIdx.x;
+  if (blockIdx.x == 0) {
+    if (tid < 9) a.task_counts[tid] = 0;
+    if (tid == 9) *p.ar.ticket = 0u;
+  }
+  for (int g = blockIdx.x * kThreads + tid; g < p.NG; g += gridDim.x * kThreads)
+    p.ar.garrive[g] = 0;
+
+  const int Hq = a.Hq, M = a.M, Tm = a.max_match_tiles;
+  const int total_tiles = a.N * Tm;
+  const int my_tiles = static_cast<int>(blockIdx.x) < total_tiles
+                           ? (total_tiles - static_cast<int>(blockIdx.x) +
+                              static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x)
+                           : 0;
+  BoxTile* tinfo = reinterpret_cast<BoxTile*>(smem);                                  // [round tiles]
+  unsigned long long* best = reinterpret_cast<unsigned long long*>(smem + 2048);      // [round tiles][Hq]
+  const float thr_probe = p.thr_dist * 1.0625f;   // see the probe's error bound in scan_probe8's user
+  const char* ring = static_cast<const char*>(a.query_cache);
+  const char* qsrc = static_cast<const char*>(a.q_pre);
+
+  for (int r0 = 0; r0 < my_tiles; r0 += kScanRoundTiles) {
+    const int rt = min(kScanRoundTiles, my_tiles - r0);
+    if (tid < rt) {
+      ScanCursor c;
+      scan_load_tile(a, blockIdx.x + (r0 + tid) * gridDim.x, c);
+      BoxTile t;
+      t.n = c.n; t.tile = c.tile; t.P = c.P; t.cbeg = c.cbeg; t.cend = c.cend;
+      t.s_begin = c.s_begin; t.nrows = (c.s_end - c.s_begin) * Hq;
+      t.tail = c.tail; t.off_lo = c.off_lo; t.off_hi = c.off_hi;
+      t.row0 = (c.req * M + c.s_begin) * Hq;
+      bool any = false;
+      if (c.elig)
+        for (int s = c.s_begin; s < c.s_end; ++s) {
+          const int pos = scan_slot_pos(c, s);
+          any = any || (pos >= c.cbeg && pos < c.cend);
+        }
+      t.nbox = any ? (t.nrows + kTmaBoxRows - 1) / kTmaBoxRows : 0;
+      tinfo[tid] = t;
+    }
+    for (int e = tid; e < rt * Hq; e += kThreads) best[e] = kNoMatchKey;
+    __syncthreads();
+    int nact = 0;
+    for (int k = 0; k < rt; ++k) nact += tinfo[k].nbox;
+
+    int ik = 0, ib = -1, ck = 0, cb = -1;   // issue cursor, consume cursor over the active boxes
+    auto advance = [&](int& k, int& b) {
+      ++b;
+      while (k < rt && b >= tinfo[k].nbox) { ++k; b = 0; }
+    };
+    uint4 rowreg[kDirectDepth][kChunks], qreg[kDirectDepth][kChunks];
+    int posreg[kDirectDepth], headreg[kDirectDepth];
+    // loads of this thread's row of box (k, b) into register set `u`; posreg < 0: not a candidate
+    auto load_box = [&](int k, int b, int u) {
+      const int4* src = reinterpret_cast<const int4*>(tinfo + k);
+      const int4 w0 = src[0], w1 = src[1], w2 = src[2];   // n tile P cbeg | cend s_begin nrows tail | off_lo off_hi nbox row0
+      const int r_local = b * kTmaBoxRows + tid;
+      posreg[u] = -1;
+      if (r_local < w1.z) {
+        const int so = r_local / Hq;
+        const int h = r_local - so * Hq;
+        const int slot = w1.y + so;
+        const int pos = slot + (slot < w1.w ? w2.x : w2.y);
+        if (pos >= w0.w && pos < w1.x) {
+          posreg[u] = pos;
+          headreg[u] = h;
+          const char* rowp = ring + static_cast<int64_t>(w2.w + r_local) * kRowBytes;
+          const uint4* qp = reinterpret_cast<const uint4*>(
+              qsrc + (static_cast<int64_t>(w0.x) * Hq + h) * kRowBytes);
+#pragma unroll
+          for (int c = 0; c < kChunks; c += 2) ld_stream32(rowp + c * 16, rowreg[u][c], rowreg[u][c + 1]);
+#pragma unroll
+          for (int c = 0; c < kChunks; ++c) qreg[u][c] = __ldg(qp + c);
+        }
+      }
+    };
+    advance(ik, ib);
+    advance(ck, cb);
+#pragma unroll
+    for (int u = 0; u < kDirectDepth; ++u) {
+      if (u < nact) {
+        load_box(ik, ib, u);
+        advance(ik, ib);
+      }
+    }
+    for (int base = 0; base < nact; base += kDirectDepth) {
+#pragma unroll
+      for (int u = 0; u < kDirectDepth; ++u) {
+        const int i = base + u;
+        if (i < nact) {
+          if (posreg[u] >= 0) {
+            float probe = 0.0f;
+#pragma unroll
+            for (int c = 0; c < kChunks; ++c) probe += scan_probe8(qreg[u][c], rowreg[u][c]);
+            if (__builtin_expect(probe < thr_probe, 0)) {   // NaN probes drop out here as well
+              const BoxTile& t = tinfo[ck];
+              const int r_local = cb * kTmaBoxRows + tid;
+              scan_exact_row(ring + static_cast<int64_t>(t.row0 + r_local) * kRowBytes,
+                             qsrc + (static_cast<int64_t>(t.n) * Hq + headreg[u]) * kRowBytes,
+                             posreg[u], best + ck * Hq + headreg[u]);
+            }
+          }
+          advance(ck, cb);
+          if (i + kDirectDepth < nact) {   // refill this register set with the box kDirectDepth ahead
+            load_box(ik, ib, u);
+            advance(ik, ib);
+          }
+        }
+      }
+    }
+    __syncthreads();   // every thread's minima are in
+    for (int e = tid; e < rt * Hq; e += kThreads) {
+      const int k = e / Hq, h = e - k * Hq;
+      const unsigned long long key = best[e];
+      const int64_t off = (static_cast<int64_t>(tinfo[k].n) * Hq + h) * Tm + tinfo[k].tile;
+      const int bpos = static_cast<int>(key & 0xffffffffull);
+      a.match_dist[off] = __uint_as_float(static_cast<unsigned>(key >> 32));
+      a.match_pos[off] = bpos;
+      a.match_slot[off] = key == kNoMatchKey ? -1 : pos_to_ring_slot(tinfo[k].P, M, bpos);
+    }
+    __syncthreads();   // the next round overwrites the tile descriptors and the minima
   }
 }
 
@@ -1634,12 +2085,22 @@ __device__ __forceinline__ long long global_ns() {
   return t;
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
-mac_decode_persistent_kernel(const DecodeParams p) {
-  extern __shared__ __align__(128) uint8_t smem[];
+__device__ unsigned g_exit_count = 0;
+
+// The three phases; returns early when a bounded wait ran out.
+__device__ __forceinline__ void decode_phases(const DecodeParams& p, const CUtensorMap* ring_map,
+                                              uint8_t* smem) {
   const bool stamp = p.a.debug_enabled >= 2 && blockIdx.x == 0 && threadIdx.x == 0;
   if (stamp) p.a.phase_cycles[0] = global_ns();
-  phase_match_scan(p, smem);
+  if (p.scan_mode == 1) {
+    if (!phase_match_scan_bulk<4>(p, ring_map, smem)) return;
+  } else if (p.scan_mode == 2) {
+    if (!phase_match_scan_bulk<8>(p, ring_map, smem)) return;
+  } else if (p.scan_mode == 3) {
+    phase_match_scan_direct<4>(p, smem);
+  } else {
+    phase_match_scan(p, smem);
+  }
   if (!grid_barrier(gridDim.x)) return;
   if (stamp) p.a.phase_cycles[1] = global_ns();
   phase_classify(p);
@@ -1649,6 +2110,24 @@ mac_decode_persistent_kernel(const DecodeParams p) {
   if (stamp) {
     const long long t = global_ns();
     for (int i = 3; i < p.a.phase_cycles_count; ++i) p.a.phase_cycles[i] = t;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+mac_decode_persistent_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap ring_map) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  decode_phases(p, &ring_map, smem);
+  // The last CTA to leave puts the barrier counter back to zero.  After a normal
+  // step it already is; after a step that gave up at a barrier (bounded wait) it
+  // is not, and the next launch would otherwise pass its barriers early.
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(&g_exit_count, 1u) == gridDim.x - 1) {
+      g_exit_count = 0;
+      g_bar_count = 0;
+      __threadfence();
+    }
   }
 }
 
@@ -1775,6 +2254,7 @@ DecodeParams make_decode_params(const MacB200DecodeArgs& a, void* arena, int max
     p.thr_dist = t;
   }
   p.scale_log2 = a.sm_scale * kLog2e;
+  p.scan_mode = 0;   // set by launch_decode once the ring's tensor map exists
   const ArenaLayout L = arena_layout(p.NG, p.G, max_pieces);
   char* base = static_cast<char*>(arena);
   p.ar.ticket = reinterpret_cast<uint32_t*>(base + L.ticket);
@@ -1800,6 +2280,12 @@ int query_kernel_facts(int device, int* sm_count, int* ctas_per_sm, int* regs) {
   cudaFuncAttributes fa{};
   MAC_CUDA(cudaFuncGetAttributes(&fa, mac_decode_persistent_kernel));
   *regs = fa.numRegs;
+  // Experiment knob: the context's L2 fetch granularity hint (bytes: 32, 64 or 128).
+  if (const char* e = std::getenv("MAC_B200_L2_FETCH_GRANULARITY")) {
+    const int v = std::atoi(e);
+    if (v == 32 || v == 64 || v == 128)
+      MAC_CUDA(cudaDeviceSetLimit(cudaLimitMaxL2FetchGranularity, static_cast<size_t>(v)));
+  }
   return MAC_B200_OK;
 }
 
@@ -1815,6 +2301,66 @@ struct InFlight {
 };
 std::mutex g_inflight_mu;
 InFlight g_inflight[64];
+
+// Tensor map of the query ring for the bulk-copy scan: rows = (request, slot,
+// head), 128 bf16 each; one box = the probe columns of 256 consecutive rows,
+// swizzled so that 256 threads can each read their own row without bank
+// conflicts.  cuTensorMapEncodeTiled is a host-side computation; it is looked
+// up through the runtime so the library does not link against the driver.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q{};
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      ptr = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+// Scan variant.  MAC_B200_SCAN picks one for A/B runs:
+//   cpasync                per-thread cp.async staging, 128 B probe, eight lanes per row (0; default)
+//   bulk64 / bulk128       bulk tensor copies into shared memory, 64 B / 128 B probe (1 / 2)
+//   direct64               32-byte register loads, row per thread, 64 B probe (3)
+// Measured on B200 the four land within 25 % of each other and cpasync is never beaten.
+int scan_mode_wanted() {
+  const char* e = std::getenv("MAC_B200_SCAN");
+  if (!e) return 0;
+  if (!std::strcmp(e, "direct64")) return 3;
+  if (!std::strcmp(e, "bulk64")) return 1;
+  if (!std::strcmp(e, "bulk128")) return 2;
+  return 0;
+}
+
+// Returns the scan mode that can run and fills `map` for the bulk-copy modes.  The
+// row-per-thread variants need a 32-byte aligned ring and row indices that fit 31 bits; the
+// bulk-copy ones also need the driver's tensor-map encoder.  Otherwise: cp.async staging.
+int make_ring_map(const MacB200DecodeArgs& a, CUtensorMap* map) {
+  std::memset(map, 0, sizeof(*map));
+  const int mode = scan_mode_wanted();
+  if (mode == 0) return 0;
+  const unsigned long long rows = static_cast<unsigned long long>(a.R) * a.M * a.Hq;
+  if ((reinterpret_cast<uintptr_t>(a.query_cache) & 31u) != 0 ||
+      (reinterpret_cast<uintptr_t>(a.q_pre) & 15u) != 0 || rows >= (1ull << 31))
+    return 0;
+  if (mode >= 3) return mode;
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (enc == nullptr) return 0;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(kD), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(kRowBytes)};
+  const cuuint32_t box[2] = {mode == 1 ? 32u : 64u, static_cast<cuuint32_t>(kTmaBoxRows)};
+  const cuuint32_t estr[2] = {1u, 1u};
+  const CUresult rc = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.query_cache, dims, strides, box,
+                          estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          mode == 1 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS ? mode : 0;
+}
 
 int launch_decode(int device, const DecodeParams& p, int grid, cudaStream_t stream) {
   cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
@@ -1832,7 +2378,9 @@ int launch_decode(int device, const DecodeParams& p, int grid, cudaStream_t stre
     if (q != cudaSuccess) return cuda_fail(q, "cudaEventQuery");
   }
   DecodeParams params = p;
-  void* kargs[] = {&params};
+  alignas(64) CUtensorMap ring_map;
+  params.scan_mode = make_ring_map(p.a, &ring_map);
+  void* kargs[] = {&params, &ring_map};
   MAC_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(mac_decode_persistent_kernel),
                                        dim3(grid), dim3(kThreads), kargs, kSmemBytes, stream));
   g_kernel_launches.fetch_add(1, std::memory_order_relaxed);

@@ -83,6 +83,43 @@ def build_downdate(verbose: bool = False):
     return _load(DOWNDATE_NAME, CSRC / "mac_merge_downdate_cache.cu", flags, verbose)
 
 
+# --------------------------------------------------------------------------- the reference's own tests
+SUITE = OUT / "ref_suite"
+_SUITE_FILES = {
+    # reference file (relative to its project root) -> place in the staged suite
+    "attention/src/mac_attention/integrations/sglang/bridge.py":
+        "pkg/mac_attention/integrations/sglang/bridge.py",
+    "attention/tests/test_mac_persistent_decode.py": "tests/test_mac_persistent_decode.py",
+    "attention/tools/check_mac_persistent_decode.py": "tools/check_mac_persistent_decode.py",
+    "attention/tools/check_front_sink_recurrence.py": "tools/check_front_sink_recurrence.py",
+}
+
+
+def stage_reference_suite() -> Path | None:
+    """Stage the reference's own kernel tests, its checker tools and its loader
+    module -- unmodified, byte for byte -- under ``oracle/_ref/ref_suite`` (kept
+    out of the history like everything else in ``oracle/_ref``), so that
+    ``tests/test_reference_suite_gpu.py`` can run them against this library on a
+    box where the reference checkout is not mounted.  The package ``__init__``
+    files around the loader are empty files of our own (the reference's import
+    its SGLang hooks, which need SGLang)."""
+    import shutil
+
+    if not REF_ROOT.exists():
+        return SUITE if SUITE.exists() else None
+    for src, dst in _SUITE_FILES.items():
+        if not (REF_ROOT / src).exists():
+            continue
+        target = SUITE / dst
+        target.parent.mkdir(parents=True, exist_ok=True)
+        shutil.copyfile(REF_ROOT / src, target)
+    for pkg in ("pkg/mac_attention", "pkg/mac_attention/integrations",
+                "pkg/mac_attention/integrations/sglang"):
+        (SUITE / pkg).mkdir(parents=True, exist_ok=True)
+        (SUITE / pkg / "__init__.py").write_text("")
+    return SUITE
+
+
 def _import_prebuilt(name: str):
     """Import ``oracle/_ref/<name>/<name>.so`` without rebuilding."""
     import importlib.util
@@ -128,6 +165,7 @@ def main() -> int:
         build_downdate(verbose=True)
     if "decode" in which:
         build_decode(verbose=True)
+    stage_reference_suite()
     return 0
 
 

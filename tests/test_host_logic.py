@@ -41,6 +41,58 @@ def test_install_rebinds_bridge_and_imported_hooks(monkeypatch):
     assert fake_bridge.load_mac_merge_downdate_cache_extension is bridge.load_mac_merge_downdate_cache_extension
 
 
+def test_install_patches_the_reference_loader_module_itself():
+    """The reference's real ``bridge`` module (from the staged copy of its loader, or from
+    its checkout) is imported, ``install()`` is called on it, and all four loader names --
+    also in a module that had bound them at import, the way the reference's hook modules
+    do -- resolve to this library and return objects with the pybind operator names."""
+    import importlib
+    import os
+    from pathlib import Path
+
+    from oracle import build_ref
+
+    roots = [build_ref.SUITE / "pkg",
+             Path(os.environ.get("MAC_REFERENCE_ROOT", "/root/reference")) / "attention" / "src"]
+    root = next((r for r in roots
+                 if (r / "mac_attention" / "integrations" / "sglang" / "bridge.py").exists()), None)
+    if root is None:
+        pytest.skip("no copy of the reference's loader module on this machine")
+    staged = root == roots[0]
+    sys.path.insert(0, str(root))
+    try:
+        if not staged:   # the checkout's package __init__ imports the SGLang hooks
+            for name in ("mac_attention", "mac_attention.integrations",
+                         "mac_attention.integrations.sglang"):
+                m = types.ModuleType(name)
+                m.__path__ = [str(root / name.replace(".", "/"))]
+                sys.modules[name] = m
+        ref_bridge = importlib.import_module("mac_attention.integrations.sglang.bridge")
+        early = types.ModuleType("mac_attention.integrations.sglang.llama_hooks")
+        for name in bridge._PATCHED:          # bound before install(), as the hook modules do
+            setattr(early, name, getattr(ref_bridge, name))
+        sys.modules[early.__name__] = early
+        originals = {name: getattr(ref_bridge, name) for name in bridge._PATCHED}
+        patched = bridge.install()
+        assert patched[0] == "mac_attention.integrations.sglang.bridge" and early.__name__ in patched
+        for name in bridge._PATCHED:
+            assert getattr(ref_bridge, name) is getattr(bridge, name) is getattr(early, name)
+            assert getattr(ref_bridge, name) is not originals[name]
+        dec = ref_bridge.load_mac_persistent_decode_extension(False)
+        assert callable(dec.mac_persistent_decode_bf16)
+        pre = ref_bridge.load_mac_prefill_update_cache_extension(False)
+        for op in ("mac_prefill_update_cache", "mac_mark_persistent_ready",
+                   "mac_invalidate_persistent_ready", "mac_update_request_state"):
+            assert callable(getattr(pre, op))
+        assert callable(ref_bridge.load_mac_decode_rope_preserve_extension().mac_decode_rope_preserve_q_bf16)
+        assert callable(
+            ref_bridge.load_mac_merge_downdate_cache_extension().mac_update_then_downdate_bf16_inplace)
+    finally:
+        sys.path.remove(str(root))
+        for name in [m for m in sys.modules if m == "mac_attention" or m.startswith("mac_attention.")]:
+            del sys.modules[name]
+
+
 def test_decode_operator_rejects_cpu_tensors_like_the_reference():
     case = synth.make_decode_case(batch=1, ctx=20, hq=8, hkv=2, capacity=8, seed=0)
     cfg = O.DecodeConfig(max_context=32, semantic_pos_ahead=4)
