@@ -965,156 +965,6 @@ __device__ bool phase_match_scan_bulk(const DecodeParams& p, const CUtensorMap* 
 }
 
 
-// ------------------------------------------------ phase A, register variant
-// The same match scan with no staging at all: a thread owns one ring row of a
-// 256-row box (the same row-per-thread split as the bulk-copy variant), fetches
-// the probe columns of its row with 32-byte global loads straight into
-// registers, and keeps kDirectDepth boxes in flight by rotating that many
-// register sets (the loop over boxes is unrolled by the depth, so a set is a
-// fixed group of registers).  Threads never wait for one another inside a
-// round: there is no shared-memory stage, no mbarrier and no barrier per box;
-// the per-(tile, head) minima of a whole round sit in shared memory
-// (64-bit atomicMin, as in the bulk-copy variant) and are written out once at
-// the end of the round.  Probe, exact evaluation of survivors and ordering are
-// those of the bulk-copy variant.
-constexpr int kDirectDepth = 4;
-
-__device__ __forceinline__ void ld_stream32(const void* p, uint4& lo, uint4& hi) {
-  asm volatile(
-      "ld.global.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-      : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z),
-        "=r"(hi.w)
-      : "l"(p));
-}
-
-template <int kChunks>
-__device__ void phase_match_scan_direct(const DecodeParams& p, uint8_t* smem) {
-  static_assert(kChunks % 2 == 0, "32-byte loads");
-  static_assert(2048 + kScanRoundTiles * kMaxHq * 8 <= kRingBytes, "round minima must fit");
-  const MacB200DecodeArgs& a = p.a;
-  const int tid = threadIdx.x;
-  if (blockIdx.x == 0) {
-    if (tid < 9) a.task_counts[tid] = 0;
-    if (tid == 9) *p.ar.ticket = 0u;
-  }
-  for (int g = blockIdx.x * kThreads + tid; g < p.NG; g += gridDim.x * kThreads)
-    p.ar.garrive[g] = 0;
-
-  const int Hq = a.Hq, M = a.M, Tm = a.max_match_tiles;
-  const int total_tiles = a.N * Tm;
-  const int my_tiles = static_cast<int>(blockIdx.x) < total_tiles
-                           ? (total_tiles - static_cast<int>(blockIdx.x) +
-                              static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x)
-                           : 0;
-  BoxTile* tinfo = reinterpret_cast<BoxTile*>(smem);                                  // [round tiles]
-  unsigned long long* best = reinterpret_cast<unsigned long long*>(smem + 2048);      // [round tiles][Hq]
-  const float thr_probe = p.thr_dist * 1.0625f;   // see the probe's error bound in scan_probe8's user
-  const char* ring = static_cast<const char*>(a.query_cache);
-  const char* qsrc = static_cast<const char*>(a.q_pre);
-
-  for (int r0 = 0; r0 < my_tiles; r0 += kScanRoundTiles) {
-    const int rt = min(kScanRoundTiles, my_tiles - r0);
-    if (tid < rt) {
-      ScanCursor c;
-      scan_load_tile(a, blockIdx.x + (r0 + tid) * gridDim.x, c);
-      BoxTile t;
-      t.n = c.n; t.tile = c.tile; t.P = c.P; t.cbeg = c.cbeg; t.cend = c.cend;
-      t.s_begin = c.s_begin; t.nrows = (c.s_end - c.s_begin) * Hq;
-      t.tail = c.tail; t.off_lo = c.off_lo; t.off_hi = c.off_hi;
-      t.row0 = (c.req * M + c.s_begin) * Hq;
-      bool any = false;
-      if (c.elig)
-        for (int s = c.s_begin; s < c.s_end; ++s) {
-          const int pos = scan_slot_pos(c, s);
-          any = any || (pos >= c.cbeg && pos < c.cend);
-        }
-      t.nbox = any ? (t.nrows + kTmaBoxRows - 1) / kTmaBoxRows : 0;
-      tinfo[tid] = t;
-    }
-    for (int e = tid; e < rt * Hq; e += kThreads) best[e] = kNoMatchKey;
-    __syncthreads();
-    int nact = 0;
-    for (int k = 0; k < rt; ++k) nact += tinfo[k].nbox;
-
-    int ik = 0, ib = -1, ck = 0, cb = -1;   // issue cursor, consume cursor over the active boxes
-    auto advance = [&](int& k, int& b) {
-      ++b;
-      while (k < rt && b >= tinfo[k].nbox) { ++k; b = 0; }
-    };
-    uint4 rowreg[kDirectDepth][kChunks], qreg[kDirectDepth][kChunks];
-    int posreg[kDirectDepth], headreg[kDirectDepth];
-    // loads of this thread's row of box (k, b) into register set `u`; posreg < 0: not a candidate
-    auto load_box = [&](int k, int b, int u) {
-      const int4* src = reinterpret_cast<const int4*>(tinfo + k);
-      const int4 w0 = src[0], w1 = src[1], w2 = src[2];   // n tile P cbeg | cend s_begin nrows tail | off_lo off_hi nbox row0
-      const int r_local = b * kTmaBoxRows + tid;
-      posreg[u] = -1;
-      if (r_local < w1.z) {
-        const int so = r_local / Hq;
-        const int h = r_local - so * Hq;
-        const int slot = w1.y + so;
-        const int pos = slot + (slot < w1.w ? w2.x : w2.y);
-        if (pos >= w0.w && pos < w1.x) {
-          posreg[u] = pos;
-          headreg[u] = h;
-          const char* rowp = ring + static_cast<int64_t>(w2.w + r_local) * kRowBytes;
-          const uint4* qp = reinterpret_cast<const uint4*>(
-              qsrc + (static_cast<int64_t>(w0.x) * Hq + h) * kRowBytes);
-#pragma unroll
-          for (int c = 0; c < kChunks; c += 2) ld_stream32(rowp + c * 16, rowreg[u][c], rowreg[u][c + 1]);
-#pragma unroll
-          for (int c = 0; c < kChunks; ++c) qreg[u][c] = __ldg(qp + c);
-        }
-      }
-    };
-    advance(ik, ib);
-    advance(ck, cb);
-#pragma unroll
-    for (int u = 0; u < kDirectDepth; ++u) {
-      if (u < nact) {
-        load_box(ik, ib, u);
-        advance(ik, ib);
-      }
-    }
-    for (int base = 0; base < nact; base += kDirectDepth) {
-#pragma unroll
-      for (int u = 0; u < kDirectDepth; ++u) {
-        const int i = base + u;
-        if (i < nact) {
-          if (posreg[u] >= 0) {
-            float probe = 0.0f;
-#pragma unroll
-            for (int c = 0; c < kChunks; ++c) probe += scan_probe8(qreg[u][c], rowreg[u][c]);
-            if (__builtin_expect(probe < thr_probe, 0)) {   // NaN probes drop out here as well
-              const BoxTile& t = tinfo[ck];
-              const int r_local = cb * kTmaBoxRows + tid;
-              scan_exact_row(ring + static_cast<int64_t>(t.row0 + r_local) * kRowBytes,
-                             qsrc + (static_cast<int64_t>(t.n) * Hq + headreg[u]) * kRowBytes,
-                             posreg[u], best + ck * Hq + headreg[u]);
-            }
-          }
-          advance(ck, cb);
-          if (i + kDirectDepth < nact) {   // refill this register set with the box kDirectDepth ahead
-            load_box(ik, ib, u);
-            advance(ik, ib);
-          }
-        }
-      }
-    }
-    __syncthreads();   // every thread's minima are in
-    for (int e = tid; e < rt * Hq; e += kThreads) {
-      const int k = e / Hq, h = e - k * Hq;
-      const unsigned long long key = best[e];
-      const int64_t off = (static_cast<int64_t>(tinfo[k].n) * Hq + h) * Tm + tinfo[k].tile;
-      const int bpos = static_cast<int>(key & 0xffffffffull);
-      a.match_dist[off] = __uint_as_float(static_cast<unsigned>(key >> 32));
-      a.match_pos[off] = bpos;
-      a.match_slot[off] = key == kNoMatchKey ? -1 : pos_to_ring_slot(tinfo[k].P, M, bpos);
-    }
-    __syncthreads();   // the next round overwrites the tile descriptors and the minima
-  }
-}
-
 // ---------------------------------------------------------------- phase B
 // One warp per KV group: cross-tile argmin per head, hit test, synthetic
 // override, front-sink demotion, group mode, reported arrays, and the group's
@@ -2096,8 +1946,6 @@ __device__ __forceinline__ void decode_phases(const DecodeParams& p, const CUten
     if (!phase_match_scan_bulk<4>(p, ring_map, smem)) return;
   } else if (p.scan_mode == 2) {
     if (!phase_match_scan_bulk<8>(p, ring_map, smem)) return;
-  } else if (p.scan_mode == 3) {
-    phase_match_scan_direct<4>(p, smem);
   } else {
     phase_match_scan(p, smem);
   }
@@ -2280,12 +2128,6 @@ int query_kernel_facts(int device, int* sm_count, int* ctas_per_sm, int* regs) {
   cudaFuncAttributes fa{};
   MAC_CUDA(cudaFuncGetAttributes(&fa, mac_decode_persistent_kernel));
   *regs = fa.numRegs;
-  // Experiment knob: the context's L2 fetch granularity hint (bytes: 32, 64 or 128).
-  if (const char* e = std::getenv("MAC_B200_L2_FETCH_GRANULARITY")) {
-    const int v = std::atoi(e);
-    if (v == 32 || v == 64 || v == 128)
-      MAC_CUDA(cudaDeviceSetLimit(cudaLimitMaxL2FetchGranularity, static_cast<size_t>(v)));
-  }
   return MAC_B200_OK;
 }
 
@@ -2324,31 +2166,31 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 // Scan variant.  MAC_B200_SCAN picks one for A/B runs:
-//   cpasync                per-thread cp.async staging, 128 B probe, eight lanes per row (0; default)
-//   bulk64 / bulk128       bulk tensor copies into shared memory, 64 B / 128 B probe (1 / 2)
-//   direct64               32-byte register loads, row per thread, 64 B probe (3)
-// Measured on B200 the four land within 25 % of each other and cpasync is never beaten.
+//   cpasync            per-thread cp.async staging, 128 B probe, eight lanes per row (0; default)
+//   bulk64 / bulk128   bulk tensor copies into shared memory, 64 B / 128 B probe (1 / 2)
+// Measured on B200: DRAM delivers whole 128-byte lines whatever part of a ring row is asked
+// for (ncu: the same dram__bytes_read for the 64 B and the 128 B probe), so the narrower
+// probe saves no traffic; the variants land within a few percent of each other at batch 64
+// and cpasync wins at small batches (no mbarrier set-up, no barrier per box).
 int scan_mode_wanted() {
   const char* e = std::getenv("MAC_B200_SCAN");
   if (!e) return 0;
-  if (!std::strcmp(e, "direct64")) return 3;
   if (!std::strcmp(e, "bulk64")) return 1;
   if (!std::strcmp(e, "bulk128")) return 2;
   return 0;
 }
 
-// Returns the scan mode that can run and fills `map` for the bulk-copy modes.  The
-// row-per-thread variants need a 32-byte aligned ring and row indices that fit 31 bits; the
-// bulk-copy ones also need the driver's tensor-map encoder.  Otherwise: cp.async staging.
+// Returns the scan mode that can run and fills `map` for the bulk-copy modes: they need a
+// 16-byte aligned ring, row indices that fit 31 bits and the driver's tensor-map encoder.
+// Otherwise: cp.async staging.
 int make_ring_map(const MacB200DecodeArgs& a, CUtensorMap* map) {
   std::memset(map, 0, sizeof(*map));
   const int mode = scan_mode_wanted();
   if (mode == 0) return 0;
   const unsigned long long rows = static_cast<unsigned long long>(a.R) * a.M * a.Hq;
-  if ((reinterpret_cast<uintptr_t>(a.query_cache) & 31u) != 0 ||
+  if ((reinterpret_cast<uintptr_t>(a.query_cache) & 15u) != 0 ||
       (reinterpret_cast<uintptr_t>(a.q_pre) & 15u) != 0 || rows >= (1ull << 31))
     return 0;
-  if (mode >= 3) return mode;
   EncodeTiledFn enc = encode_tiled_fn();
   if (enc == nullptr) return 0;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(kD), static_cast<cuuint64_t>(rows)};

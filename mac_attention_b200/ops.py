@@ -5,12 +5,13 @@ reference operator (``csrc/mac_decode_persistent.cu:4962-5030`` in the reference
 project), ``mac_prefill_update_cache`` and the three gate/state operators take
 those of ``csrc/mac_prefill_update_cache.cu:324-337, 374-495``.  Each one checks
 what the reference launcher checks (same messages, ``RuntimeError``), fills the
-plain-C argument struct and calls the C ABI on torch's current stream.
+plain-C argument struct and calls the C ABI on torch's current stream.  The
+decode operators -- the per-step hot call -- do that in a compiled
+torch-extension shim (``csrc/mac_b200_torch.cpp``), the others through ctypes.
 """
 from __future__ import annotations
 
 import ctypes as C
-import os
 
 import torch
 
@@ -24,311 +25,50 @@ def _req(cond: bool, msg: str) -> None:
         raise RuntimeError(msg)
 
 
-def _check(t: torch.Tensor, name: str, dtype: torch.dtype, dim: int) -> None:
-    _req(t.is_cuda, f"{name} must be CUDA")
-    _req(t.is_contiguous(), f"{name} must be contiguous")
-    _req(t.dtype == dtype, f"{name} has wrong dtype")
-    _req(t.dim() == dim, f"{name} has wrong rank")
-
-
-def _check_partial_o(t: torch.Tensor, name: str) -> None:
-    _req(t.is_cuda, f"{name} must be CUDA")
-    _req(t.is_contiguous(), f"{name} must be contiguous")
-    _req(t.dtype in (_F32, _BF16), f"{name} must be float32 or bfloat16")
-    _req(t.dim() == 5, f"{name} has wrong rank")
-
-
-def _env_flag(name: str, default: int) -> int:
-    raw = os.environ.get(name)
-    if raw is None:
-        return default
-    try:
-        return 1 if int(raw) != 0 else 0
-    except ValueError:
-        return 0
-
-
-def _env_int(name: str, default: int) -> int:
-    raw = os.environ.get(name)
-    if raw is None:
-        return default
-    try:
-        v = int(raw)
-    except ValueError:
-        return default
-    return v if v > 0 else default
-
-
 def _stream_ptr(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
-def _decode_call(
-    entry_name,
-    q_post, q_pre, k_buffer, v_buffer, req_to_token, req_ids, past_lens, out_cache_loc,
-    query_cache, attn_cache, lse_cache, out, optional_lse,
-    match_dist, match_pos, match_slot,
-    head_hit, head_match_slot, head_match_pos, head_prefix_end, head_rect_start, head_new_end,
-    group_rect_begin, group_rect_end, group_rect_tiles,
-    group_tail_begin, group_tail_end, group_tail_tiles, group_mode,
-    complete_task_go, complete_task_tile, tail_task_go, tail_task_tile,
-    hit_tail_task_ho, hit_tail_task_tile, task_counts,
-    partial_rect_o, partial_rect_lse, partial_rect_reduced_o, partial_rect_reduced_lse,
-    partial_tail_o, partial_tail_lse, phase_cycles,
-    max_context, tile_tokens, match_tile_slots, semantic_pos_ahead, front_sink_tokens,
-    gen_min_limit, lookback_right, candidate_mode, threshold, sm_scale,
-    debug_enabled, bench_mode, bench_hit_rate, bench_hit_rate_std,
-    bench_skip_ratio, bench_skip_ratio_std, bench_match_lag_mean, bench_match_lag_std,
-    bench_seed, bench_miss_mask, bench_layer_id,
-    query_post_cache, mac_cache_ready, mac_cache_epoch, mac_request_epoch,
-) -> None:
-    """Checks and argument marshalling shared by the decode entry points; returns the
-    filled ``MacB200DecodeArgs``."""
-    _check(q_post, "q_post", _BF16, 3)
-    _check(q_pre, "q_pre", _BF16, 3)
-    _check(k_buffer, "k_buffer", _BF16, 3)
-    _check(v_buffer, "v_buffer", _BF16, 3)
-    _check(req_to_token, "req_to_token", _I32, 2)
-    _check(req_ids, "req_ids", _I32, 1)
-    _check(past_lens, "past_lens", _I32, 1)
-    _req(out_cache_loc.is_cuda, "out_cache_loc must be CUDA")
-    _req(out_cache_loc.is_contiguous(), "out_cache_loc must be contiguous")
-    _req(out_cache_loc.dim() == 1, "out_cache_loc has wrong rank")
-    _req(out_cache_loc.dtype in (_I32, _I64), "out_cache_loc must be int32 or int64")
-    _check(query_cache, "query_cache", _BF16, 4)
-    if query_post_cache is not None and query_post_cache.numel() > 0:
-        _check(query_post_cache, "query_post_cache", _BF16, 4)  # accepted, ignored
-    _check(attn_cache, "attn_cache", _BF16, 4)
-    _check(lse_cache, "lse_cache", _F32, 3)
-    _check(out, "out", _BF16, 3)
-    _req(optional_lse.is_cuda, "optional_lse must be CUDA")
-    _req(optional_lse.is_contiguous(), "optional_lse must be contiguous")
-    _req(optional_lse.numel() == 0 or optional_lse.dtype == _F32,
-         "optional_lse must be empty or float32")
-    _req(phase_cycles.is_cuda, "phase_cycles must be CUDA")
-    _req(phase_cycles.is_contiguous(), "phase_cycles must be contiguous")
-    _req(phase_cycles.dtype == _I64, "phase_cycles must be int64")
-    _req(phase_cycles.numel() >= 6, "phase_cycles must have at least 6 elements")
-    _check(match_dist, "match_dist", _F32, 3)
-    _check(match_pos, "match_pos", _I32, 3)
-    _check(match_slot, "match_slot", _I32, 3)
-    for name, t in (("head_hit", head_hit), ("head_match_slot", head_match_slot),
-                    ("head_match_pos", head_match_pos), ("head_prefix_end", head_prefix_end),
-                    ("head_rect_start", head_rect_start), ("head_new_end", head_new_end),
-                    ("group_rect_begin", group_rect_begin), ("group_rect_end", group_rect_end),
-                    ("group_rect_tiles", group_rect_tiles), ("group_tail_begin", group_tail_begin),
-                    ("group_tail_end", group_tail_end), ("group_tail_tiles", group_tail_tiles),
-                    ("group_mode", group_mode)):
-        _check(t, name, _I32, 2)
-    lean = partial_rect_o is None   # the lean operator passes no task lists / partial buffers
-    _check(task_counts, "task_counts", _I32, 1)
-    if not lean:
-        for name, t in (("complete_task_go", complete_task_go),
-                        ("complete_task_tile", complete_task_tile),
-                        ("tail_task_go", tail_task_go), ("tail_task_tile", tail_task_tile),
-                        ("hit_tail_task_ho", hit_tail_task_ho),
-                        ("hit_tail_task_tile", hit_tail_task_tile)):
-            _check(t, name, _I32, 1)
-        _check_partial_o(partial_rect_o, "partial_rect_o")
-        _check(partial_rect_lse, "partial_rect_lse", _F32, 4)
-        _check_partial_o(partial_rect_reduced_o, "partial_rect_reduced_o")
-        _check(partial_rect_reduced_lse, "partial_rect_reduced_lse", _F32, 4)
-        _check_partial_o(partial_tail_o, "partial_tail_o")
-        _check(partial_tail_lse, "partial_tail_lse", _F32, 4)
-        _req(partial_rect_reduced_o.dtype == partial_rect_o.dtype
-             and partial_tail_o.dtype == partial_rect_o.dtype,
-             "all partial output workspaces must use the same dtype")
-
-    N, Hq, D = q_post.shape
-    Hkv = k_buffer.shape[1]
-    _req(D == 128, "persistent decode v1 supports D=128 only")
-    _req(q_pre.shape == q_post.shape, "q_pre/q_post shape mismatch")
-    _req(v_buffer.shape == k_buffer.shape, "k/v shape mismatch")
-    _req(Hkv > 0 and Hq % Hkv == 0, "Hq must be divisible by Hkv")
-    G = Hq // Hkv
-    _req(0 < G <= 8, "unsupported GQA group size")
-    _req(req_ids.shape[0] >= N and past_lens.shape[0] >= N and out_cache_loc.shape[0] >= N,
-         "batch metadata too small")
-    _req(out.shape == q_post.shape, "out shape mismatch")
-    R, M = query_cache.shape[0], query_cache.shape[1]
-    _req(query_cache.shape[2] == Hq and query_cache.shape[3] == D, "query_cache shape mismatch")
-    _req(attn_cache.shape == query_cache.shape, "attn_cache shape mismatch")
-    _req(tuple(lse_cache.shape) == (R, M, Hq), "lse_cache shape mismatch")
-
-    tile_tokens = int(tile_tokens)
-    match_tile_slots = int(match_tile_slots)
-    max_context = int(max_context)
-    Tm = match_dist.shape[2]
-    _req(Tm >= (M + match_tile_slots - 1) // match_tile_slots, "match workspace too small")
-    _req(group_mode.shape[0] >= N and group_mode.shape[1] >= Hkv, "group_mode workspace too small")
-    _req(task_counts.numel() >= 9, "task_counts must have at least nine elements")
-    _req(int(bench_mode) in (0, 1, 2), "unsupported synthetic MAC bench mode")
-    if not lean:
-        Tc = partial_rect_lse.shape[2]
-        Tr = partial_rect_reduced_lse.shape[2]
-        Tt = partial_tail_lse.shape[2]
-        _req(Tm >= (M + match_tile_slots - 1) // match_tile_slots, "match workspace too small")
-        _req(Tc >= (max_context + tile_tokens - 1) // tile_tokens, "rect workspace too small")
-        _req(Tr >= (max_context + tile_tokens * 32 - 1) // (tile_tokens * 32),
-             "reduced rect workspace too small")
-        _req(Tt >= (int(semantic_pos_ahead) + tile_tokens - 1) // tile_tokens,
-             "tail workspace too small")
-        _req(partial_rect_o.shape[0] >= N and tuple(partial_rect_o.shape[1:]) == (Hkv, Tc, G, D),
-             "rect output workspace has wrong shape")
-        _req(partial_rect_lse.shape[0] >= N and tuple(partial_rect_lse.shape[1:]) == (Hkv, Tc, G),
-             "rect lse workspace has wrong shape")
-        _req(partial_rect_reduced_o.shape[0] >= N
-             and tuple(partial_rect_reduced_o.shape[1:]) == (Hkv, Tr, G, D),
-             "reduced rect output workspace has wrong shape")
-        _req(partial_rect_reduced_lse.shape[0] >= N
-             and tuple(partial_rect_reduced_lse.shape[1:]) == (Hkv, Tr, G),
-             "reduced rect lse workspace has wrong shape")
-        _req(partial_tail_o.shape[0] >= N and tuple(partial_tail_o.shape[1:]) == (Hkv, Tt, G, D),
-             "tail output workspace has wrong shape")
-        _req(partial_tail_lse.shape[0] >= N and tuple(partial_tail_lse.shape[1:]) == (Hkv, Tt, G),
-             "tail lse workspace has wrong shape")
-        _req(group_mode.shape[0] >= N and group_mode.shape[1] >= Hkv, "group_mode workspace too small")
-        _req(complete_task_tile.numel() == complete_task_go.numel(), "complete task shape mismatch")
-        _req(tail_task_tile.numel() == tail_task_go.numel(), "tail task shape mismatch")
-        _req(hit_tail_task_tile.numel() == hit_tail_task_ho.numel(), "hit tail task shape mismatch")
-        _req(task_counts.numel() >= 9, "task_counts must have at least nine elements")
-        _req(int(bench_mode) in (0, 1, 2), "unsupported synthetic MAC bench mode")
-        _req(complete_task_go.numel() >= N * Hq * Tc, "complete task workspace too small")
-        _req(tail_task_go.numel() >= N * Hkv * Tt, "tail task workspace too small")
-        _req(hit_tail_task_ho.numel() >= N * Hq * Tt, "hit tail task workspace too small")
-    ws_batch = match_dist.shape[0]
-    for name, t in (("match_dist", match_dist), ("match_pos", match_pos),
-                    ("match_slot", match_slot)):
-        _req(t.shape[0] >= N and t.shape[1] == Hq and t.shape[2] == Tm,
-             f"{name} workspace has wrong shape")
-    for name, t in (("head_hit", head_hit), ("head_match_slot", head_match_slot),
-                    ("head_match_pos", head_match_pos), ("head_prefix_end", head_prefix_end),
-                    ("head_rect_start", head_rect_start), ("head_new_end", head_new_end)):
-        _req(t.shape[0] >= N and t.shape[1] == Hq, f"{name} workspace has wrong shape")
-        ws_batch = min(ws_batch, t.shape[0])
-    for name, t in (("group_rect_begin", group_rect_begin), ("group_rect_end", group_rect_end),
-                    ("group_rect_tiles", group_rect_tiles), ("group_tail_begin", group_tail_begin),
-                    ("group_tail_end", group_tail_end), ("group_tail_tiles", group_tail_tiles),
-                    ("group_mode", group_mode)):
-        _req(t.shape[0] >= N and t.shape[1] == Hkv, f"{name} workspace has wrong shape")
-        ws_batch = min(ws_batch, t.shape[0])
-
-    ready_ptr = epoch_ptr = req_epoch_ptr = None
-    if mac_cache_ready is not None and mac_cache_ready.numel() > 0:
-        _req(mac_cache_ready.is_cuda, "mac_cache_ready must be CUDA")
-        _req(mac_cache_ready.is_contiguous(), "mac_cache_ready must be contiguous")
-        _req(mac_cache_ready.dtype in (torch.bool, torch.uint8),
-             "mac_cache_ready must be bool or uint8")
-        _req(mac_cache_ready.numel() >= R, "mac_cache_ready is smaller than the ring")
-        ready_ptr = mac_cache_ready.data_ptr()
-        if (mac_cache_epoch is not None and mac_cache_epoch.numel() > 0
-                and mac_request_epoch is not None and mac_request_epoch.numel() > 0):
-            _check(mac_cache_epoch, "mac_cache_epoch", _I64, 1)
-            _check(mac_request_epoch, "mac_request_epoch", _I64, 1)
-            _req(mac_cache_epoch.numel() >= R and mac_request_epoch.numel() >= R,
-                 "epoch tensors are smaller than the ring")
-            epoch_ptr = mac_cache_epoch.data_ptr()
-            req_epoch_ptr = mac_request_epoch.data_ptr()
-
-    a = _abi.MacB200DecodeArgs()
-    a.N, a.Hq, a.Hkv, a.D, a.M, a.R = N, Hq, Hkv, D, M, R
-    a.req_to_token_rows, a.req_to_token_stride = req_to_token.shape
-    a.kv_tokens = k_buffer.shape[0]
-    a.ws_batch, a.max_match_tiles = ws_batch, Tm
-    a.max_context, a.tile_tokens, a.match_tile_slots = max_context, tile_tokens, match_tile_slots
-    a.semantic_pos_ahead = int(semantic_pos_ahead)
-    a.front_sink_tokens = int(front_sink_tokens)
-    a.gen_min_limit = int(gen_min_limit)
-    a.lookback_right = int(lookback_right)
-    a.candidate_mode = int(candidate_mode)
-    a.threshold, a.sm_scale = float(threshold), float(sm_scale)
-    a.debug_enabled, a.bench_mode = int(debug_enabled), int(bench_mode)
-    a.bench_hit_rate, a.bench_hit_rate_std = float(bench_hit_rate), float(bench_hit_rate_std)
-    a.bench_skip_ratio = float(bench_skip_ratio)
-    a.bench_skip_ratio_std = float(bench_skip_ratio_std)
-    a.bench_match_lag_mean = float(bench_match_lag_mean)
-    a.bench_match_lag_std = float(bench_match_lag_std)
-    a.bench_seed = C.c_int32(int(bench_seed) & 0xFFFFFFFF).value
-    a.bench_miss_mask = int(bench_miss_mask)
-    a.bench_layer_id = C.c_int32(int(bench_layer_id) & 0xFFFFFFFF).value
-    # The reference reads these two from the environment on every launch.
-    a.mixed_group_fallback = _env_flag("MAC_PERSISTENT_MIXED_GROUP_FALLBACK", 1)
-    a.bench_exact_quota = _env_flag("MAC_BENCH_EXACT_QUOTA", 1)
-    a.out_cache_loc_is_i64 = 1 if out_cache_loc.dtype == _I64 else 0
-    a.phase_cycles_count = phase_cycles.numel()
-    a.grid_cap = _env_int("MAC_PERSISTENT_COOP_CTAS", 0)
-    a.q_post, a.q_pre = q_post.data_ptr(), q_pre.data_ptr()
-    a.k_buffer, a.v_buffer = k_buffer.data_ptr(), v_buffer.data_ptr()
-    a.req_to_token, a.req_ids = req_to_token.data_ptr(), req_ids.data_ptr()
-    a.past_lens, a.out_cache_loc = past_lens.data_ptr(), out_cache_loc.data_ptr()
-    a.query_cache, a.attn_cache = query_cache.data_ptr(), attn_cache.data_ptr()
-    a.lse_cache, a.out = lse_cache.data_ptr(), out.data_ptr()
-    a.optional_lse = optional_lse.data_ptr() if optional_lse.numel() > 0 else None
-    if optional_lse.numel() > 0:
-        _req(optional_lse.numel() >= N * Hq, "optional_lse is smaller than [N,Hq]")
-    a.match_dist, a.match_pos = match_dist.data_ptr(), match_pos.data_ptr()
-    a.match_slot = match_slot.data_ptr()
-    a.head_hit, a.head_match_slot = head_hit.data_ptr(), head_match_slot.data_ptr()
-    a.head_match_pos, a.head_prefix_end = head_match_pos.data_ptr(), head_prefix_end.data_ptr()
-    a.head_rect_start, a.head_new_end = head_rect_start.data_ptr(), head_new_end.data_ptr()
-    a.group_rect_begin, a.group_rect_end = group_rect_begin.data_ptr(), group_rect_end.data_ptr()
-    a.group_rect_tiles = group_rect_tiles.data_ptr()
-    a.group_tail_begin, a.group_tail_end = group_tail_begin.data_ptr(), group_tail_end.data_ptr()
-    a.group_tail_tiles, a.group_mode = group_tail_tiles.data_ptr(), group_mode.data_ptr()
-    a.task_counts, a.phase_cycles = task_counts.data_ptr(), phase_cycles.data_ptr()
-    a.cache_ready, a.cache_epoch, a.request_epoch = ready_ptr, epoch_ptr, req_epoch_ptr
-
-    return a
-
-
 _DECODE_ARG_COUNT = 68
-_TENSOR_ARGS = tuple(range(0, 43)) + (64, 65, 66, 67)
-_ARG_CACHE: dict = {}
-_ARG_CACHE_MAX = 64
-_ARG_CACHE_ON = os.environ.get("MAC_B200_NO_ARG_CACHE", "0") != "1"
+_shim = None
 
 
-def _decode_key(args):
-    """Identity of a call for the marshalling cache: address, shape, dtype and
-    contiguity of EVERY tensor argument plus all scalars.  A caching allocator
-    can hand the same address to a tensor of another shape or dtype, so the
-    address alone does not identify a buffer.  A repeat of the same call
-    (serving loops and graph warm-ups pass the same buffers every step) reuses
-    the checked argument struct instead of re-validating ~50 tensors."""
-    ident = tuple(None if t is None else (t.data_ptr(), t.shape, t.dtype, t.is_contiguous())
-                  for t in (args[i] for i in _TENSOR_ARGS))
-    return (ident, args[43:64], args[0].device)
+def _load_shim():
+    """The torch-extension shim of the decode operator (``csrc/mac_b200_torch.cpp``): it
+    takes the tensors, runs the reference launcher's checks in C++ and calls the C ABI on
+    torch's current stream.  Built in-tree next to ``libmac_b200.so``; there is no other
+    path to the decode kernel from Python."""
+    global _shim
+    if _shim is None:
+        import importlib.util
 
+        _abi.load_library()
+        from . import build as _build
 
-def _decode_entry(entry_name, args) -> None:
-    lib = _abi.load_library()
-    key = _decode_key(args) if _ARG_CACHE_ON else None
-    a = _ARG_CACHE.get(key) if key is not None else None
-    if a is None:
-        a = _decode_call(entry_name, *args)
-        if key is not None:
-            if len(_ARG_CACHE) >= _ARG_CACHE_MAX:
-                _ARG_CACHE.clear()
-            _ARG_CACHE[key] = a
-    else:
-        # the reference re-reads these environment knobs on every launch
-        a.mixed_group_fallback = _env_flag("MAC_PERSISTENT_MIXED_GROUP_FALLBACK", 1)
-        a.bench_exact_quota = _env_flag("MAC_BENCH_EXACT_QUOTA", 1)
-        a.grid_cap = _env_int("MAC_PERSISTENT_COOP_CTAS", 0)
-    device = args[0].device
-    with torch.cuda.device(device):
-        _abi.check(getattr(lib, entry_name)(C.byref(a), _stream_ptr(device)))
+        try:
+            if _build.shim_is_stale():
+                _build.build_shim()
+        except Exception as exc:  # noqa: BLE001
+            if not _build.SHIM.exists():
+                raise RuntimeError(f"mac_b200_torch.so is missing and could not be built: {exc}") from exc
+        spec = importlib.util.spec_from_file_location("mac_b200_torch", _build.SHIM)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        _shim = mod
+    return _shim
 
 
 def mac_persistent_decode_bf16(*args) -> None:
     """One fused MAC decode step; the reference operator's 68 positional arguments
-    (13 tensors, 30 workspace tensors, 21 scalars, ``query_post_cache`` and the
-    three readiness-gate tensors; see ``_decode_call`` for the names and
-    ``include/mac_b200.h`` for the meaning).  Returns ``None``."""
+    (``csrc/mac_decode_persistent.cu:4962-5030`` in the reference project): 13 tensors,
+    30 workspace tensors, 21 scalars, ``query_post_cache`` and the three readiness-gate
+    tensors; ``include/mac_b200.h`` has their meaning.  Checks are the reference
+    launcher's, with its messages, raised as ``RuntimeError`` before any launch.
+    Returns ``None``."""
     if len(args) != _DECODE_ARG_COUNT:
         raise TypeError(f"mac_persistent_decode_bf16() takes {_DECODE_ARG_COUNT} positional "
                         f"arguments ({len(args)} given)")
-    _decode_entry("mac_b200_persistent_decode_bf16", args)
+    _load_shim().decode(0, *args)
 
 
 def mac_persistent_decode_bf16_lean(q_post, q_pre, k_buffer, v_buffer, req_to_token, req_ids,
@@ -348,11 +88,11 @@ def mac_persistent_decode_bf16_lean(q_post, q_pre, k_buffer, v_buffer, req_to_to
         raise TypeError("decisions must hold the 18 tensors of make_decision_workspace()")
     if len(scalars_and_gate) != 25:
         raise TypeError("expected 21 scalars, query_post_cache and 3 readiness-gate tensors")
-    args = (q_post, q_pre, k_buffer, v_buffer, req_to_token, req_ids, past_lens, out_cache_loc,
-            query_cache, attn_cache, lse_cache, out, optional_lse,
-            *decisions[:16], None, None, None, None, None, None, decisions[16],
-            None, None, None, None, None, None, decisions[17], *scalars_and_gate)
-    _decode_entry("mac_b200_persistent_decode_bf16", args)
+    _load_shim().decode(
+        0, q_post, q_pre, k_buffer, v_buffer, req_to_token, req_ids, past_lens, out_cache_loc,
+        query_cache, attn_cache, lse_cache, out, optional_lse,
+        *decisions[:16], None, None, None, None, None, None, decisions[16],
+        None, None, None, None, None, None, decisions[17], *scalars_and_gate)
 
 
 def mac_persistent_decode_bf16_noalloc(*args) -> None:
@@ -365,7 +105,7 @@ def mac_persistent_decode_bf16_noalloc(*args) -> None:
     if len(args) != _DECODE_ARG_COUNT:
         raise TypeError(f"mac_persistent_decode_bf16_noalloc() takes {_DECODE_ARG_COUNT} "
                         f"positional arguments ({len(args)} given)")
-    _decode_entry("mac_b200_persistent_decode_bf16_noalloc", args)
+    _load_shim().decode(1, *args)
 
 
 def mac_prefill_update_cache(

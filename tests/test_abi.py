@@ -59,3 +59,25 @@ def test_argument_validation_needs_no_gpu(lib):
     assert lib.mac_b200_prefill_update_cache(ctypes.byref(p), None) == 0  # capacity 0: no-op
     p.M, p.B = 4, 1
     assert lib.mac_b200_prefill_update_cache(ctypes.byref(p), None) == -1
+
+
+def test_torch_shim_builds_loads_and_keeps_the_reference_messages(lib):
+    """The decode operator's torch-extension shim builds against this torch, links to the
+    C-ABI library next to it, and raises the reference launcher's messages (checked here on
+    CPU tensors, before anything touches a device)."""
+    import torch
+
+    from mac_attention_b200 import ops
+
+    build.build_shim()
+    shim = ops._load_shim()
+    assert callable(shim.decode)
+    t = torch.zeros(1, 8, 128, dtype=torch.bfloat16)
+    args = [t] * 43 + [0] * 8 + [0.45, 0.088] + [0, 0] + [0.0] * 6 + [1, -1, 0] + [t] * 4
+    assert len(args) == 68
+    with pytest.raises(RuntimeError, match="q_post must be CUDA"):
+        ops.mac_persistent_decode_bf16(*args)
+    with pytest.raises(TypeError, match="68 positional"):
+        ops.mac_persistent_decode_bf16(*args[:-1])
+    with pytest.raises(TypeError):
+        ops.mac_persistent_decode_bf16(*([None] + args[1:]))      # a required tensor is missing

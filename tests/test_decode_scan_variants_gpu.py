@@ -1,7 +1,7 @@
-"""The match-scan variants of the decode kernel must be indistinguishable: row-per-thread
-32-byte register loads with a 64-byte probe (the default), bulk tensor copies with a 64- or
-128-byte probe, and per-thread cp.async staging (``MAC_B200_SCAN`` = ``direct64`` /
-``bulk64`` / ``bulk128`` / ``cpasync``, read at every launch).  Each runs a seeded slice of the random parity
+"""The match-scan variants of the decode kernel must be indistinguishable: per-thread
+cp.async staging with a 128-byte probe (the default) and bulk tensor copies with a 64- or
+128-byte probe (``MAC_B200_SCAN`` = ``cpasync`` / ``bulk64`` / ``bulk128``, read at every
+launch).  Each runs a seeded slice of the random parity
 matrix against the CPU oracle -- including head counts that do not divide the
 256-row copy box (G = 3, 5, 7), 128 query heads, rings shorter than a box and
 contexts shorter than the ring -- and all of them must report bit-identical
@@ -19,7 +19,7 @@ from helpers import assert_decisions_equal, assert_outputs_close, run_cuda, run_
 
 pytestmark = pytest.mark.gpu
 
-MODES = ["direct64", "bulk64", "bulk128", "cpasync"]
+MODES = ["cpasync", "bulk64", "bulk128"]
 
 
 @pytest.fixture
