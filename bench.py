@@ -72,6 +72,11 @@ def parse_args():
     ap.add_argument("--no-gpu-baselines", action="store_true")
     ap.add_argument("--no-config3", action="store_true")
     ap.add_argument("--parity-requests", type=int, default=6)
+    ap.add_argument("--matched-prefix", default="",
+                    help="with --sweep: 'mean,std' of the matched prefix length as a fraction of "
+                         "the context (BASELINE config 1 draws it from [0.5, 0.95]: 0.725,0.13). "
+                         "Labelled extension: lifts the reference's rule that a reused entry lies "
+                         "within the last M positions, for synthetic decisions only")
     ap.add_argument("--shard", default="request", choices=["request", "kv_head"])
     ap.add_argument("--config4", action="store_true",
                     help="mixed serving step with readiness gating + prefill ring build timing")
@@ -230,8 +235,11 @@ def make_launch(ext, case, ws, scal, out, lse):
 def scalars(args, hit, debug=0, front_sink=None):
     """The operator's 21 scalars in positional order (reference benchmark defaults)."""
     F = args.front_sink if front_sink is None else front_sink
+    skip, skip_std = -1.0, 0.0
+    if getattr(args, "matched_prefix", ""):
+        skip, skip_std = (float(x) for x in args.matched_prefix.split(","))
     return (MAX_CONTEXT, TILE, MTS, SEM, F, 0, 0, 0, 0.45, 1.0 / math.sqrt(DIM),
-            debug, args.bench_mode, hit, 0.0, -1.0, 0.0, float(LAG), 0.0, 1, -1, 0)
+            debug, args.bench_mode, hit, 0.0, skip, skip_std, float(LAG), 0.0, 1, -1, 0)
 
 
 def time_graph(launch, steps, warmup, barrier=None):
@@ -937,6 +945,10 @@ def run_sweep(args):
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     ext = load_mac_persistent_decode_extension()
+    if args.matched_prefix:
+        # the operator reads this switch from the environment at every call, like the
+        # reference's own launcher knobs; the reference kernel ignores it and demotes
+        os.environ["MAC_B200_BENCH_LONG_BAND"] = "1"
     baselines = [b for b in args.baselines.split(",") if b]
     ref_ext = None
     if "refkernel" in baselines:
@@ -979,6 +991,7 @@ def run_sweep(args):
             torch.cuda.synchronize()
             ph = ws[29].cpu().tolist()
             row = dict(batch=batch, ctx=ctx, hit=hit, mac_us=ms * 1e3,
+                       matched_prefix=args.matched_prefix or None,
                        requested_gbs=ab["requested"] / (ms * 1e-3) / 1e9,
                        phase_us=dict(scan=(ph[1] - ph[0]) / 1e3, classify=(ph[2] - ph[1]) / 1e3,
                                      attend_cta0=(ph[3] - ph[2]) / 1e3),

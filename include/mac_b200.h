@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define MAC_B200_ABI_VERSION 1
+#define MAC_B200_ABI_VERSION 2
 
 /* Error codes (negative). */
 #define MAC_B200_OK 0
@@ -105,6 +105,12 @@ typedef struct MacB200DecodeArgs {
   int32_t out_cache_loc_is_i64; /* 0: int32, 1: int64                                       */
   int32_t phase_cycles_count;   /* elements of phase_cycles (>= 6)                          */
   int32_t grid_cap;             /* > 0 caps the persistent grid (MAC_PERSISTENT_COOP_CTAS)  */
+  /* Benchmark extension, no counterpart in the reference: with synthetic decisions
+   * (bench_mode != 0) a reused entry may lie further back than the ring is long, i.e.
+   * the rule "new_end - prefix_end <= M" (mac_decode_persistent.cu:1323-1328) is lifted,
+   * so that bench_skip_ratio can place the matched prefix anywhere in the context.
+   * 0 (default) keeps the reference's rule and its decisions. */
+  int32_t bench_long_band;
 
   /* ---- inputs ---- */
   const void* q_post;          /* [N,Hq,D] bf16, post-RoPE query (attention)                */

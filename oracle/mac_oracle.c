@@ -332,6 +332,9 @@ static void decide_head(const MacB200DecodeArgs* a, int n, int hq, HeadDecision*
         best_p = P - lag;
         if (best_p < 0) best_p = 0;
         best_s = pos_to_ring_slot(P, M, best_p);
+        /* benchmark extension: a synthetic match older than the ring's span stands in a
+         * slot of its own (position mod M) instead of an out-of-range one */
+        if (a->bench_long_band != 0 && best_p < P - M) best_s = best_p % M;
         best_d = 0.0f;
       }
     } else {
@@ -575,7 +578,10 @@ ORACLE_API int mac_oracle_decode_step_rows(const MacB200DecodeArgs* a, float* ou
         int clen = h->new_end - h->rect_start;
         if (v) {
           float pl = a->lse_cache[((int64_t)req * M + h->mslot) * Hq + hq];
-          v = isfinite(pl) && clen >= 0 && clen <= M;
+          /* bench_long_band: benchmark extension of the C ABI, lifts the "<= M" rule for
+           * synthetic decisions only (no counterpart in the reference) */
+          v = isfinite(pl) && clen >= 0 &&
+              (clen <= M || (a->bench_long_band != 0 && a->bench_mode != 0));
         }
         valid[l] = v;
         if (v) {

@@ -89,6 +89,7 @@ class DecodeConfig:
     bench_layer_id: int = 0
     mixed_group_fallback: int = 1
     bench_exact_quota: int = 1
+    bench_long_band: int = 0     # benchmark extension of the C ABI (see include/mac_b200.h)
 
     def scalar_args(self):
         """The 21 scalars in the operator's positional order."""
@@ -164,7 +165,7 @@ def decode_step(q_post, q_pre, k_buffer, v_buffer, req_to_token, req_ids, past_l
                  "threshold", "sm_scale", "debug_enabled", "bench_mode", "bench_hit_rate",
                  "bench_hit_rate_std", "bench_skip_ratio", "bench_skip_ratio_std",
                  "bench_match_lag_mean", "bench_match_lag_std", "bench_seed", "bench_miss_mask",
-                 "bench_layer_id", "mixed_group_fallback", "bench_exact_quota"):
+                 "bench_layer_id", "mixed_group_fallback", "bench_exact_quota", "bench_long_band"):
         setattr(a, name, getattr(cfg, name))
     a.out_cache_loc_is_i64 = 1 if out_cache_loc.dtype == torch.int64 else 0
     a.q_post, a.q_pre, a.k_buffer, a.v_buffer = _p(q_post), _p(q_pre), _p(k_buffer), _p(v_buffer)
@@ -212,7 +213,7 @@ def decide(q_pre, req_ids, past_lens, query_cache, lse_cache, cfg: DecodeConfig,
                  "threshold", "sm_scale", "debug_enabled", "bench_mode", "bench_hit_rate",
                  "bench_hit_rate_std", "bench_skip_ratio", "bench_skip_ratio_std",
                  "bench_match_lag_mean", "bench_match_lag_std", "bench_seed", "bench_miss_mask",
-                 "bench_layer_id", "mixed_group_fallback", "bench_exact_quota"):
+                 "bench_layer_id", "mixed_group_fallback", "bench_exact_quota", "bench_long_band"):
         setattr(a, name, getattr(cfg, name))
     a.q_pre, a.req_ids, a.past_lens = _p(q_pre), _p(req_ids), _p(past_lens)
     a.query_cache, a.lse_cache = _p(query_cache), _p(lse_cache)

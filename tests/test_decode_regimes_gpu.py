@@ -132,3 +132,31 @@ def test_headline_geometry_outputs(hit):
     cfg = O.DecodeConfig(max_context=131072, semantic_pos_ahead=256, bench_mode=1,
                          bench_hit_rate=hit, bench_match_lag_mean=64.0, bench_seed=1)
     _check(case, cfg, n, expect_hits=hit > 0, expect_misses=hit < 1)
+
+
+def test_matched_prefix_anywhere_in_the_context_extension(monkeypatch):
+    """The labelled benchmark extension (``MAC_B200_BENCH_LONG_BAND=1``): with synthetic
+    decisions a reused entry may lie anywhere in the context (BASELINE config 1 draws the
+    matched prefix from [50 %, 95 %] of it), i.e. the band a hit head recomputes is tens of
+    thousands of tokens long.  Decisions and outputs against the oracle with the same switch;
+    with the switch off (the default) the same step demotes those heads like the reference."""
+    n = 3
+    case = synth.make_decode_case(batch=n, ctx=60000, hq=32, hkv=8, capacity=2048, page_size=16,
+                                  seed=61, device="cuda")
+    cfg = O.DecodeConfig(max_context=131072, semantic_pos_ahead=256, bench_mode=1,
+                         bench_hit_rate=0.75, bench_skip_ratio=0.725, bench_skip_ratio_std=0.13,
+                         bench_seed=1, bench_long_band=1)
+    monkeypatch.setenv("MAC_B200_BENCH_LONG_BAND", "1")
+    cu, orc = _check(case, cfg, n)
+    hit = orc.head_hit.bool()
+    band = (orc.head_new_end - orc.head_rect_start)[hit]
+    assert int(band.max()) > 2048 * 4          # far beyond the ring's span
+    monkeypatch.delenv("MAC_B200_BENCH_LONG_BAND")
+    cfg.bench_long_band = 0
+    cu2 = run_cuda(case, cfg, partial_dtype=torch.bfloat16)
+    orc2, _ = run_oracle(case, cfg)
+    assert_decisions_equal(cu2, orc2, n)
+    hit2 = orc2.head_hit.bool()
+    band2 = (orc2.head_new_end - orc2.head_rect_start)[hit2]
+    assert band2.numel() == 0 or int(band2.max()) <= 2048
+    assert int(hit2.sum()) < int(hit.sum())
