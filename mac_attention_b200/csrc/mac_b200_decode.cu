@@ -1939,17 +1939,21 @@ __device__ __forceinline__ long long global_ns() {
   return t;
 }
 
-__device__ unsigned g_exit_count = 0;
-
-// The three phases; returns early when a bounded wait ran out.
+// The three phases; returns early when a bounded wait ran out.  kBulkScan selects the match
+// scan at compile time: the two variants are separate kernels, because merely carrying the
+// bulk-copy scan in the same kernel cost the cp.async variant 2-13 us per step on B200
+// (measured with interleaved runs of both builds; the code is never executed there).
+template <bool kBulkScan>
 __device__ __forceinline__ void decode_phases(const DecodeParams& p, const CUtensorMap* ring_map,
                                               uint8_t* smem) {
   const bool stamp = p.a.debug_enabled >= 2 && blockIdx.x == 0 && threadIdx.x == 0;
   if (stamp) p.a.phase_cycles[0] = global_ns();
-  if (p.scan_mode == 1) {
-    if (!phase_match_scan_bulk<4>(p, ring_map, smem)) return;
-  } else if (p.scan_mode == 2) {
-    if (!phase_match_scan_bulk<8>(p, ring_map, smem)) return;
+  if constexpr (kBulkScan) {
+    if (p.scan_mode == 1) {
+      if (!phase_match_scan_bulk<4>(p, ring_map, smem)) return;
+    } else {
+      if (!phase_match_scan_bulk<8>(p, ring_map, smem)) return;
+    }
   } else {
     phase_match_scan(p, smem);
   }
@@ -1966,21 +1970,17 @@ __device__ __forceinline__ void decode_phases(const DecodeParams& p, const CUten
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
-mac_decode_persistent_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap ring_map) {
+mac_decode_persistent_kernel(const DecodeParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  decode_phases(p, &ring_map, smem);
-  // The last CTA to leave puts the barrier counter back to zero.  After a normal
-  // step it already is; after a step that gave up at a barrier (bounded wait) it
-  // is not, and the next launch would otherwise pass its barriers early.
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    if (atomicAdd(&g_exit_count, 1u) == gridDim.x - 1) {
-      g_exit_count = 0;
-      g_bar_count = 0;
-      __threadfence();
-    }
-  }
+  decode_phases<false>(p, nullptr, smem);
+}
+
+// The same step with the bulk-copy match scan (MAC_B200_SCAN=bulk64 / bulk128).
+__global__ void __launch_bounds__(kThreads, 1)
+mac_decode_persistent_bulk_scan_kernel(const DecodeParams p,
+                                       const __grid_constant__ CUtensorMap ring_map) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  decode_phases<true>(p, &ring_map, smem);
 }
 
 // --------------------------------------------------------------- host state
@@ -2226,9 +2226,23 @@ int launch_decode(int device, const DecodeParams& p, int grid, cudaStream_t stre
   DecodeParams params = p;
   alignas(64) CUtensorMap ring_map;
   params.scan_mode = make_ring_map(p.a, &ring_map);
-  void* kargs[] = {&params, &ring_map};
-  MAC_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(mac_decode_persistent_kernel),
-                                       dim3(grid), dim3(kThreads), kargs, kSmemBytes, stream));
+  if (params.scan_mode != 0) {
+    static std::once_flag bulk_attr[64];
+    cudaError_t attr_rc = cudaSuccess;
+    std::call_once(bulk_attr[device], [&] {   // per device; this kernel shares the default one's shape
+      attr_rc = cudaFuncSetAttribute(mac_decode_persistent_bulk_scan_kernel,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    });
+    if (attr_rc != cudaSuccess) return cuda_fail(attr_rc, "cudaFuncSetAttribute");
+    void* kargs[] = {&params, &ring_map};
+    MAC_CUDA(cudaLaunchCooperativeKernel(
+        reinterpret_cast<void*>(mac_decode_persistent_bulk_scan_kernel), dim3(grid), dim3(kThreads),
+        kargs, kSmemBytes, stream));
+  } else {
+    void* kargs[] = {&params};
+    MAC_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(mac_decode_persistent_kernel),
+                                         dim3(grid), dim3(kThreads), kargs, kSmemBytes, stream));
+  }
   g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
   if (!capturing) {
     if (f.done == nullptr) MAC_CUDA(cudaEventCreateWithFlags(&f.done, cudaEventDisableTiming));

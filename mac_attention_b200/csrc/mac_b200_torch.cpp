@@ -3,16 +3,20 @@
 // 5526-5529 in the reference project), re-expressed over the C ABI.
 //
 // It takes torch.Tensors, checks what the reference launcher checks (same
-// messages, raised as the same c10::Error -> RuntimeError before any launch),
-// extracts pointers and sizes into MacB200DecodeArgs and calls the C-ABI entry
-// point on torch's current CUDA stream of the tensors' device.  Nothing else
-// happens here: no allocation, no kernel, no torch op.
+// messages, before any launch), extracts pointers and sizes into
+// MacB200DecodeArgs and calls the C-ABI entry point on torch's current CUDA
+// stream of the tensors' device.  Nothing else happens here: no allocation, no
+// kernel, no torch op.  Failures are reported by return code, not by C++
+// exceptions: kShimCheckFailed with the text at last_error() for a failed
+// check (the Python operator raises the RuntimeError the reference's
+// TORCH_CHECK would), else the C ABI's own status code.
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 #include <torch/extension.h>
 
 #include <cstdlib>
 #include <cstring>
+#include <string>
 
 #include "../../include/mac_b200.h"
 
@@ -21,19 +25,45 @@ namespace {
 using at::Tensor;
 using OptTensor = c10::optional<Tensor>;
 
-void check(const Tensor& t, const char* name, at::ScalarType dtype, int64_t dim) {
-  TORCH_CHECK(t.is_cuda(), name, " must be CUDA");
-  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
-  TORCH_CHECK(t.scalar_type() == dtype, name, " has wrong dtype");
-  TORCH_CHECK(t.dim() == dim, name, " has wrong rank");
+constexpr int kShimCheckFailed = -1000;
+
+std::string& shim_error() {
+  static thread_local std::string text;
+  return text;
 }
 
-void check_partial_o(const Tensor& t, const char* name) {
-  TORCH_CHECK(t.is_cuda(), name, " must be CUDA");
-  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
-  TORCH_CHECK(t.scalar_type() == at::kFloat || t.scalar_type() == at::kBFloat16, name,
-              " must be float32 or bfloat16");
-  TORCH_CHECK(t.dim() == 5, name, " has wrong rank");
+template <typename... Parts>
+int shim_fail(const Parts&... parts) {
+  shim_error() = c10::str(parts...);
+  return kShimCheckFailed;
+}
+
+// A failed requirement leaves its message at last_error() and makes the enclosing function
+// return kShimCheckFailed.
+#define REQUIRE(cond, ...)                         \
+  do {                                             \
+    if (!(cond)) return shim_fail(__VA_ARGS__);    \
+  } while (0)
+#define REQUIRE_OK(call)                           \
+  do {                                             \
+    if (const int rc_ = (call)) return rc_;        \
+  } while (0)
+
+int check(const Tensor& t, const char* name, at::ScalarType dtype, int64_t dim) {
+  REQUIRE(t.is_cuda(), name, " must be CUDA");
+  REQUIRE(t.is_contiguous(), name, " must be contiguous");
+  REQUIRE(t.scalar_type() == dtype, name, " has wrong dtype");
+  REQUIRE(t.dim() == dim, name, " has wrong rank");
+  return 0;
+}
+
+int check_partial_o(const Tensor& t, const char* name) {
+  REQUIRE(t.is_cuda(), name, " must be CUDA");
+  REQUIRE(t.is_contiguous(), name, " must be contiguous");
+  REQUIRE(t.scalar_type() == at::kFloat || t.scalar_type() == at::kBFloat16, name,
+          " must be float32 or bfloat16");
+  REQUIRE(t.dim() == 5, name, " has wrong rank");
+  return 0;
 }
 
 int env_flag(const char* name, int dflt) {
@@ -58,7 +88,9 @@ bool present(const OptTensor& t) { return t.has_value() && t->defined() && t->nu
 enum Entry { kDecode = 0, kDecodeNoAlloc = 1 };
 
 // `lean` callers pass no task lists and no partial buffers (None for those arguments).
-void decode(
+// Returns the C ABI's status code (0 = launched); the caller turns a non-zero code into a
+// RuntimeError carrying mac_b200_last_error() of this thread.
+int decode(
     int entry, const Tensor& q_post, const Tensor& q_pre, const Tensor& k_buffer,
     const Tensor& v_buffer, const Tensor& req_to_token, const Tensor& req_ids,
     const Tensor& past_lens, const Tensor& out_cache_loc, const Tensor& query_cache,
@@ -82,34 +114,34 @@ void decode(
     int64_t bench_seed, int64_t bench_miss_mask, int64_t bench_layer_id,
     const OptTensor& query_post_cache, const OptTensor& mac_cache_ready,
     const OptTensor& mac_cache_epoch, const OptTensor& mac_request_epoch) {
-  check(q_post, "q_post", at::kBFloat16, 3);
-  check(q_pre, "q_pre", at::kBFloat16, 3);
-  check(k_buffer, "k_buffer", at::kBFloat16, 3);
-  check(v_buffer, "v_buffer", at::kBFloat16, 3);
-  check(req_to_token, "req_to_token", at::kInt, 2);
-  check(req_ids, "req_ids", at::kInt, 1);
-  check(past_lens, "past_lens", at::kInt, 1);
-  TORCH_CHECK(out_cache_loc.is_cuda(), "out_cache_loc must be CUDA");
-  TORCH_CHECK(out_cache_loc.is_contiguous(), "out_cache_loc must be contiguous");
-  TORCH_CHECK(out_cache_loc.dim() == 1, "out_cache_loc has wrong rank");
-  TORCH_CHECK(out_cache_loc.scalar_type() == at::kInt || out_cache_loc.scalar_type() == at::kLong,
+  REQUIRE_OK(check(q_post, "q_post", at::kBFloat16, 3));
+  REQUIRE_OK(check(q_pre, "q_pre", at::kBFloat16, 3));
+  REQUIRE_OK(check(k_buffer, "k_buffer", at::kBFloat16, 3));
+  REQUIRE_OK(check(v_buffer, "v_buffer", at::kBFloat16, 3));
+  REQUIRE_OK(check(req_to_token, "req_to_token", at::kInt, 2));
+  REQUIRE_OK(check(req_ids, "req_ids", at::kInt, 1));
+  REQUIRE_OK(check(past_lens, "past_lens", at::kInt, 1));
+  REQUIRE(out_cache_loc.is_cuda(), "out_cache_loc must be CUDA");
+  REQUIRE(out_cache_loc.is_contiguous(), "out_cache_loc must be contiguous");
+  REQUIRE(out_cache_loc.dim() == 1, "out_cache_loc has wrong rank");
+  REQUIRE(out_cache_loc.scalar_type() == at::kInt || out_cache_loc.scalar_type() == at::kLong,
               "out_cache_loc must be int32 or int64");
-  check(query_cache, "query_cache", at::kBFloat16, 4);
-  if (present(query_post_cache)) check(*query_post_cache, "query_post_cache", at::kBFloat16, 4);
-  check(attn_cache, "attn_cache", at::kBFloat16, 4);
-  check(lse_cache, "lse_cache", at::kFloat, 3);
-  check(out, "out", at::kBFloat16, 3);
-  TORCH_CHECK(optional_lse.is_cuda(), "optional_lse must be CUDA");
-  TORCH_CHECK(optional_lse.is_contiguous(), "optional_lse must be contiguous");
-  TORCH_CHECK(optional_lse.numel() == 0 || optional_lse.scalar_type() == at::kFloat,
+  REQUIRE_OK(check(query_cache, "query_cache", at::kBFloat16, 4));
+  if (present(query_post_cache)) REQUIRE_OK(check(*query_post_cache, "query_post_cache", at::kBFloat16, 4));
+  REQUIRE_OK(check(attn_cache, "attn_cache", at::kBFloat16, 4));
+  REQUIRE_OK(check(lse_cache, "lse_cache", at::kFloat, 3));
+  REQUIRE_OK(check(out, "out", at::kBFloat16, 3));
+  REQUIRE(optional_lse.is_cuda(), "optional_lse must be CUDA");
+  REQUIRE(optional_lse.is_contiguous(), "optional_lse must be contiguous");
+  REQUIRE(optional_lse.numel() == 0 || optional_lse.scalar_type() == at::kFloat,
               "optional_lse must be empty or float32");
-  TORCH_CHECK(phase_cycles.is_cuda(), "phase_cycles must be CUDA");
-  TORCH_CHECK(phase_cycles.is_contiguous(), "phase_cycles must be contiguous");
-  TORCH_CHECK(phase_cycles.scalar_type() == at::kLong, "phase_cycles must be int64");
-  TORCH_CHECK(phase_cycles.numel() >= 6, "phase_cycles must have at least 6 elements");
-  check(match_dist, "match_dist", at::kFloat, 3);
-  check(match_pos, "match_pos", at::kInt, 3);
-  check(match_slot, "match_slot", at::kInt, 3);
+  REQUIRE(phase_cycles.is_cuda(), "phase_cycles must be CUDA");
+  REQUIRE(phase_cycles.is_contiguous(), "phase_cycles must be contiguous");
+  REQUIRE(phase_cycles.scalar_type() == at::kLong, "phase_cycles must be int64");
+  REQUIRE(phase_cycles.numel() >= 6, "phase_cycles must have at least 6 elements");
+  REQUIRE_OK(check(match_dist, "match_dist", at::kFloat, 3));
+  REQUIRE_OK(check(match_pos, "match_pos", at::kInt, 3));
+  REQUIRE_OK(check(match_slot, "match_slot", at::kInt, 3));
   const Tensor* head_ws[6] = {&head_hit,        &head_match_slot, &head_match_pos,
                               &head_prefix_end, &head_rect_start, &head_new_end};
   const char* head_names[6] = {"head_hit",        "head_match_slot", "head_match_pos",
@@ -119,62 +151,62 @@ void decode(
   const char* group_names[7] = {"group_rect_begin", "group_rect_end", "group_rect_tiles",
                                 "group_tail_begin", "group_tail_end", "group_tail_tiles",
                                 "group_mode"};
-  for (int i = 0; i < 6; ++i) check(*head_ws[i], head_names[i], at::kInt, 2);
-  for (int i = 0; i < 7; ++i) check(*group_ws[i], group_names[i], at::kInt, 2);
-  check(task_counts, "task_counts", at::kInt, 1);
+  for (int i = 0; i < 6; ++i) REQUIRE_OK(check(*head_ws[i], head_names[i], at::kInt, 2));
+  for (int i = 0; i < 7; ++i) REQUIRE_OK(check(*group_ws[i], group_names[i], at::kInt, 2));
+  REQUIRE_OK(check(task_counts, "task_counts", at::kInt, 1));
   const bool lean = !partial_rect_o.has_value();
   if (!lean) {
-    TORCH_CHECK(complete_task_go && complete_task_tile && tail_task_go && tail_task_tile &&
+    REQUIRE(complete_task_go && complete_task_tile && tail_task_go && tail_task_tile &&
                     hit_tail_task_ho && hit_tail_task_tile && partial_rect_lse &&
                     partial_rect_reduced_o && partial_rect_reduced_lse && partial_tail_o &&
                     partial_tail_lse,
                 "task lists and partial workspaces go together");
-    check(*complete_task_go, "complete_task_go", at::kInt, 1);
-    check(*complete_task_tile, "complete_task_tile", at::kInt, 1);
-    check(*tail_task_go, "tail_task_go", at::kInt, 1);
-    check(*tail_task_tile, "tail_task_tile", at::kInt, 1);
-    check(*hit_tail_task_ho, "hit_tail_task_ho", at::kInt, 1);
-    check(*hit_tail_task_tile, "hit_tail_task_tile", at::kInt, 1);
-    check_partial_o(*partial_rect_o, "partial_rect_o");
-    check(*partial_rect_lse, "partial_rect_lse", at::kFloat, 4);
-    check_partial_o(*partial_rect_reduced_o, "partial_rect_reduced_o");
-    check(*partial_rect_reduced_lse, "partial_rect_reduced_lse", at::kFloat, 4);
-    check_partial_o(*partial_tail_o, "partial_tail_o");
-    check(*partial_tail_lse, "partial_tail_lse", at::kFloat, 4);
-    TORCH_CHECK(partial_rect_reduced_o->scalar_type() == partial_rect_o->scalar_type() &&
+    REQUIRE_OK(check(*complete_task_go, "complete_task_go", at::kInt, 1));
+    REQUIRE_OK(check(*complete_task_tile, "complete_task_tile", at::kInt, 1));
+    REQUIRE_OK(check(*tail_task_go, "tail_task_go", at::kInt, 1));
+    REQUIRE_OK(check(*tail_task_tile, "tail_task_tile", at::kInt, 1));
+    REQUIRE_OK(check(*hit_tail_task_ho, "hit_tail_task_ho", at::kInt, 1));
+    REQUIRE_OK(check(*hit_tail_task_tile, "hit_tail_task_tile", at::kInt, 1));
+    REQUIRE_OK(check_partial_o(*partial_rect_o, "partial_rect_o"));
+    REQUIRE_OK(check(*partial_rect_lse, "partial_rect_lse", at::kFloat, 4));
+    REQUIRE_OK(check_partial_o(*partial_rect_reduced_o, "partial_rect_reduced_o"));
+    REQUIRE_OK(check(*partial_rect_reduced_lse, "partial_rect_reduced_lse", at::kFloat, 4));
+    REQUIRE_OK(check_partial_o(*partial_tail_o, "partial_tail_o"));
+    REQUIRE_OK(check(*partial_tail_lse, "partial_tail_lse", at::kFloat, 4));
+    REQUIRE(partial_rect_reduced_o->scalar_type() == partial_rect_o->scalar_type() &&
                     partial_tail_o->scalar_type() == partial_rect_o->scalar_type(),
                 "all partial output workspaces must use the same dtype");
   }
 
   const int64_t N = q_post.size(0), Hq = q_post.size(1), D = q_post.size(2);
   const int64_t Hkv = k_buffer.size(1);
-  TORCH_CHECK(D == 128, "persistent decode v1 supports D=128 only");
-  TORCH_CHECK(q_pre.sizes() == q_post.sizes(), "q_pre/q_post shape mismatch");
-  TORCH_CHECK(v_buffer.sizes() == k_buffer.sizes(), "k/v shape mismatch");
-  TORCH_CHECK(Hkv > 0 && Hq % Hkv == 0, "Hq must be divisible by Hkv");
+  REQUIRE(D == 128, "persistent decode v1 supports D=128 only");
+  REQUIRE(q_pre.sizes() == q_post.sizes(), "q_pre/q_post shape mismatch");
+  REQUIRE(v_buffer.sizes() == k_buffer.sizes(), "k/v shape mismatch");
+  REQUIRE(Hkv > 0 && Hq % Hkv == 0, "Hq must be divisible by Hkv");
   const int64_t G = Hq / Hkv;
-  TORCH_CHECK(G > 0 && G <= 8, "unsupported GQA group size");
-  TORCH_CHECK(req_ids.size(0) >= N && past_lens.size(0) >= N && out_cache_loc.size(0) >= N,
+  REQUIRE(G > 0 && G <= 8, "unsupported GQA group size");
+  REQUIRE(req_ids.size(0) >= N && past_lens.size(0) >= N && out_cache_loc.size(0) >= N,
               "batch metadata too small");
-  TORCH_CHECK(out.sizes() == q_post.sizes(), "out shape mismatch");
+  REQUIRE(out.sizes() == q_post.sizes(), "out shape mismatch");
   const int64_t R = query_cache.size(0), M = query_cache.size(1);
-  TORCH_CHECK(query_cache.size(2) == Hq && query_cache.size(3) == D, "query_cache shape mismatch");
-  TORCH_CHECK(attn_cache.sizes() == query_cache.sizes(), "attn_cache shape mismatch");
-  TORCH_CHECK(lse_cache.size(0) == R && lse_cache.size(1) == M && lse_cache.size(2) == Hq,
+  REQUIRE(query_cache.size(2) == Hq && query_cache.size(3) == D, "query_cache shape mismatch");
+  REQUIRE(attn_cache.sizes() == query_cache.sizes(), "attn_cache shape mismatch");
+  REQUIRE(lse_cache.size(0) == R && lse_cache.size(1) == M && lse_cache.size(2) == Hq,
               "lse_cache shape mismatch");
-  TORCH_CHECK(tile_tokens > 0 && match_tile_slots > 0, "tile sizes must be positive");
+  REQUIRE(tile_tokens > 0 && match_tile_slots > 0, "tile sizes must be positive");
   const int64_t Tm = match_dist.size(2);
-  TORCH_CHECK(Tm >= (M + match_tile_slots - 1) / match_tile_slots, "match workspace too small");
-  TORCH_CHECK(group_mode.size(0) >= N && group_mode.size(1) >= Hkv, "group_mode workspace too small");
-  TORCH_CHECK(task_counts.numel() >= 9, "task_counts must have at least nine elements");
-  TORCH_CHECK(bench_mode >= 0 && bench_mode <= 2, "unsupported synthetic MAC bench mode");
+  REQUIRE(Tm >= (M + match_tile_slots - 1) / match_tile_slots, "match workspace too small");
+  REQUIRE(group_mode.size(0) >= N && group_mode.size(1) >= Hkv, "group_mode workspace too small");
+  REQUIRE(task_counts.numel() >= 9, "task_counts must have at least nine elements");
+  REQUIRE(bench_mode >= 0 && bench_mode <= 2, "unsupported synthetic MAC bench mode");
   if (!lean) {
     const int64_t Tc = partial_rect_lse->size(2), Tr = partial_rect_reduced_lse->size(2),
                   Tt = partial_tail_lse->size(2);
-    TORCH_CHECK(Tc >= (max_context + tile_tokens - 1) / tile_tokens, "rect workspace too small");
-    TORCH_CHECK(Tr >= (max_context + tile_tokens * 32 - 1) / (tile_tokens * 32),
+    REQUIRE(Tc >= (max_context + tile_tokens - 1) / tile_tokens, "rect workspace too small");
+    REQUIRE(Tr >= (max_context + tile_tokens * 32 - 1) / (tile_tokens * 32),
                 "reduced rect workspace too small");
-    TORCH_CHECK(Tt >= (semantic_pos_ahead + tile_tokens - 1) / tile_tokens,
+    REQUIRE(Tt >= (semantic_pos_ahead + tile_tokens - 1) / tile_tokens,
                 "tail workspace too small");
     auto shape5 = [&](const Tensor& t, int64_t tiles) {
       return t.size(0) >= N && t.size(1) == Hkv && t.size(2) == tiles && t.size(3) == G &&
@@ -183,32 +215,32 @@ void decode(
     auto shape4 = [&](const Tensor& t, int64_t tiles) {
       return t.size(0) >= N && t.size(1) == Hkv && t.size(2) == tiles && t.size(3) == G;
     };
-    TORCH_CHECK(shape5(*partial_rect_o, Tc), "rect output workspace has wrong shape");
-    TORCH_CHECK(shape4(*partial_rect_lse, Tc), "rect lse workspace has wrong shape");
-    TORCH_CHECK(shape5(*partial_rect_reduced_o, Tr), "reduced rect output workspace has wrong shape");
-    TORCH_CHECK(shape4(*partial_rect_reduced_lse, Tr), "reduced rect lse workspace has wrong shape");
-    TORCH_CHECK(shape5(*partial_tail_o, Tt), "tail output workspace has wrong shape");
-    TORCH_CHECK(shape4(*partial_tail_lse, Tt), "tail lse workspace has wrong shape");
-    TORCH_CHECK(complete_task_tile->numel() == complete_task_go->numel(), "complete task shape mismatch");
-    TORCH_CHECK(tail_task_tile->numel() == tail_task_go->numel(), "tail task shape mismatch");
-    TORCH_CHECK(hit_tail_task_tile->numel() == hit_tail_task_ho->numel(), "hit tail task shape mismatch");
-    TORCH_CHECK(complete_task_go->numel() >= N * Hq * Tc, "complete task workspace too small");
-    TORCH_CHECK(tail_task_go->numel() >= N * Hkv * Tt, "tail task workspace too small");
-    TORCH_CHECK(hit_tail_task_ho->numel() >= N * Hq * Tt, "hit tail task workspace too small");
+    REQUIRE(shape5(*partial_rect_o, Tc), "rect output workspace has wrong shape");
+    REQUIRE(shape4(*partial_rect_lse, Tc), "rect lse workspace has wrong shape");
+    REQUIRE(shape5(*partial_rect_reduced_o, Tr), "reduced rect output workspace has wrong shape");
+    REQUIRE(shape4(*partial_rect_reduced_lse, Tr), "reduced rect lse workspace has wrong shape");
+    REQUIRE(shape5(*partial_tail_o, Tt), "tail output workspace has wrong shape");
+    REQUIRE(shape4(*partial_tail_lse, Tt), "tail lse workspace has wrong shape");
+    REQUIRE(complete_task_tile->numel() == complete_task_go->numel(), "complete task shape mismatch");
+    REQUIRE(tail_task_tile->numel() == tail_task_go->numel(), "tail task shape mismatch");
+    REQUIRE(hit_tail_task_tile->numel() == hit_tail_task_ho->numel(), "hit tail task shape mismatch");
+    REQUIRE(complete_task_go->numel() >= N * Hq * Tc, "complete task workspace too small");
+    REQUIRE(tail_task_go->numel() >= N * Hkv * Tt, "tail task workspace too small");
+    REQUIRE(hit_tail_task_ho->numel() >= N * Hq * Tt, "hit tail task workspace too small");
   }
   int64_t ws_batch = match_dist.size(0);
   const Tensor* match_ws[3] = {&match_dist, &match_pos, &match_slot};
   const char* match_names[3] = {"match_dist", "match_pos", "match_slot"};
   for (int i = 0; i < 3; ++i)
-    TORCH_CHECK(match_ws[i]->size(0) >= N && match_ws[i]->size(1) == Hq && match_ws[i]->size(2) == Tm,
+    REQUIRE(match_ws[i]->size(0) >= N && match_ws[i]->size(1) == Hq && match_ws[i]->size(2) == Tm,
                 match_names[i], " workspace has wrong shape");
   for (int i = 0; i < 6; ++i) {
-    TORCH_CHECK(head_ws[i]->size(0) >= N && head_ws[i]->size(1) == Hq, head_names[i],
+    REQUIRE(head_ws[i]->size(0) >= N && head_ws[i]->size(1) == Hq, head_names[i],
                 " workspace has wrong shape");
     ws_batch = std::min(ws_batch, head_ws[i]->size(0));
   }
   for (int i = 0; i < 7; ++i) {
-    TORCH_CHECK(group_ws[i]->size(0) >= N && group_ws[i]->size(1) == Hkv, group_names[i],
+    REQUIRE(group_ws[i]->size(0) >= N && group_ws[i]->size(1) == Hkv, group_names[i],
                 " workspace has wrong shape");
     ws_batch = std::min(ws_batch, group_ws[i]->size(0));
   }
@@ -217,23 +249,23 @@ void decode(
   std::memset(&a, 0, sizeof(a));
   if (present(mac_cache_ready)) {
     const Tensor& ready = *mac_cache_ready;
-    TORCH_CHECK(ready.is_cuda(), "mac_cache_ready must be CUDA");
-    TORCH_CHECK(ready.is_contiguous(), "mac_cache_ready must be contiguous");
-    TORCH_CHECK(ready.scalar_type() == at::kBool || ready.scalar_type() == at::kByte,
+    REQUIRE(ready.is_cuda(), "mac_cache_ready must be CUDA");
+    REQUIRE(ready.is_contiguous(), "mac_cache_ready must be contiguous");
+    REQUIRE(ready.scalar_type() == at::kBool || ready.scalar_type() == at::kByte,
                 "mac_cache_ready must be bool or uint8");
-    TORCH_CHECK(ready.numel() >= R, "mac_cache_ready is smaller than the ring");
+    REQUIRE(ready.numel() >= R, "mac_cache_ready is smaller than the ring");
     a.cache_ready = static_cast<const uint8_t*>(ready.data_ptr());
     if (present(mac_cache_epoch) && present(mac_request_epoch)) {
-      check(*mac_cache_epoch, "mac_cache_epoch", at::kLong, 1);
-      check(*mac_request_epoch, "mac_request_epoch", at::kLong, 1);
-      TORCH_CHECK(mac_cache_epoch->numel() >= R && mac_request_epoch->numel() >= R,
+      REQUIRE_OK(check(*mac_cache_epoch, "mac_cache_epoch", at::kLong, 1));
+      REQUIRE_OK(check(*mac_request_epoch, "mac_request_epoch", at::kLong, 1));
+      REQUIRE(mac_cache_epoch->numel() >= R && mac_request_epoch->numel() >= R,
                   "epoch tensors are smaller than the ring");
       a.cache_epoch = mac_cache_epoch->data_ptr<int64_t>();
       a.request_epoch = mac_request_epoch->data_ptr<int64_t>();
     }
   }
   if (optional_lse.numel() > 0) {
-    TORCH_CHECK(optional_lse.numel() >= N * Hq, "optional_lse is smaller than [N,Hq]");
+    REQUIRE(optional_lse.numel() >= N * Hq, "optional_lse is smaller than [N,Hq]");
     a.optional_lse = optional_lse.data_ptr<float>();
   }
   a.N = static_cast<int32_t>(N);
@@ -309,16 +341,19 @@ void decode(
 
   const c10::cuda::CUDAGuard guard(q_post.device());
   void* stream = static_cast<void*>(c10::cuda::getCurrentCUDAStream(q_post.device().index()).stream());
-  const int rc = entry == kDecodeNoAlloc ? mac_b200_persistent_decode_bf16_noalloc(&a, stream)
-                                         : mac_b200_persistent_decode_bf16(&a, stream);
-  TORCH_CHECK(rc == 0, "mac_b200: ", mac_b200_last_error(), " (code ", rc, ")");
+  return entry == kDecodeNoAlloc ? mac_b200_persistent_decode_bf16_noalloc(&a, stream)
+                                 : mac_b200_persistent_decode_bf16(&a, stream);
 }
 
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "torch.Tensor front end of the B200 MAC decode step (pointer/shape extraction only)";
+  m.def("last_error", [] { return shim_error(); },
+        "text of the last failed check on the calling thread");
+  m.attr("CHECK_FAILED") = kShimCheckFailed;
   m.def("decode", &decode,
         "entry (0: allocating, 1: fixed scratch block) followed by the reference operator's 68 "
-        "positional arguments; task lists and partial buffers may be None (lean call)");
+        "positional arguments; task lists and partial buffers may be None (lean call); returns "
+        "the C ABI's status code");
 }

@@ -58,6 +58,16 @@ def _load_shim():
     return _shim
 
 
+def _raise_on_failure(rc: int) -> None:
+    """0 = launched.  A failed check of the shim carries its own text (the message the
+    reference's TORCH_CHECK would raise); anything else is a C-ABI status code."""
+    if rc == 0:
+        return
+    if rc == _shim.CHECK_FAILED:
+        raise RuntimeError(_shim.last_error())
+    _abi.check(rc)
+
+
 def mac_persistent_decode_bf16(*args) -> None:
     """One fused MAC decode step; the reference operator's 68 positional arguments
     (``csrc/mac_decode_persistent.cu:4962-5030`` in the reference project): 13 tensors,
@@ -68,7 +78,7 @@ def mac_persistent_decode_bf16(*args) -> None:
     if len(args) != _DECODE_ARG_COUNT:
         raise TypeError(f"mac_persistent_decode_bf16() takes {_DECODE_ARG_COUNT} positional "
                         f"arguments ({len(args)} given)")
-    _load_shim().decode(0, *args)
+    _raise_on_failure(_load_shim().decode(0, *args))
 
 
 def mac_persistent_decode_bf16_lean(q_post, q_pre, k_buffer, v_buffer, req_to_token, req_ids,
@@ -88,11 +98,11 @@ def mac_persistent_decode_bf16_lean(q_post, q_pre, k_buffer, v_buffer, req_to_to
         raise TypeError("decisions must hold the 18 tensors of make_decision_workspace()")
     if len(scalars_and_gate) != 25:
         raise TypeError("expected 21 scalars, query_post_cache and 3 readiness-gate tensors")
-    _load_shim().decode(
+    _raise_on_failure(_load_shim().decode(
         0, q_post, q_pre, k_buffer, v_buffer, req_to_token, req_ids, past_lens, out_cache_loc,
         query_cache, attn_cache, lse_cache, out, optional_lse,
         *decisions[:16], None, None, None, None, None, None, decisions[16],
-        None, None, None, None, None, None, decisions[17], *scalars_and_gate)
+        None, None, None, None, None, None, decisions[17], *scalars_and_gate))
 
 
 def mac_persistent_decode_bf16_noalloc(*args) -> None:
@@ -105,7 +115,7 @@ def mac_persistent_decode_bf16_noalloc(*args) -> None:
     if len(args) != _DECODE_ARG_COUNT:
         raise TypeError(f"mac_persistent_decode_bf16_noalloc() takes {_DECODE_ARG_COUNT} "
                         f"positional arguments ({len(args)} given)")
-    _load_shim().decode(1, *args)
+    _raise_on_failure(_load_shim().decode(1, *args))
 
 
 def mac_prefill_update_cache(

@@ -534,3 +534,42 @@ def test_long_context_few_groups_outputs_match_oracle(hq, hkv):
     assert int(cu.ws[22][0]) >= 40          # pieces: far more than groups
     assert 0 < int(orc.head_hit.sum()) < orc.head_hit.numel()
     _status_clean()
+
+
+def test_overlapping_launch_on_another_stream_is_refused():
+    """Decode launches of one device share scratch and barrier words.  A second launch on
+    another stream while the first is still running must be refused with a clear error, not
+    left to race; after the first has finished the same call goes through."""
+    case = synth.make_decode_case(batch=8, ctx=60000, hq=32, hkv=8, capacity=256, page_size=16,
+                                  seed=3, device="cuda")
+    cfg = O.DecodeConfig(max_context=65536, gen_min_limit=10 ** 6)      # every group: full attention
+    ext = load_mac_persistent_decode_extension()
+    ws = make_decode_workspace(8, 32, 8, 256, cfg.max_context, cfg.tile_tokens,
+                               cfg.match_tile_slots, cfg.semantic_pos_ahead, 0,
+                               partial_dtype=torch.bfloat16)
+    out = torch.empty_like(case.q_post)
+    lse = torch.empty(8, 32, device="cuda")
+    e = torch.empty(0)
+
+    def call():
+        ext.mac_persistent_decode_bf16(case.q_post, case.q_pre, case.k, case.v, case.req_to_token,
+                                       case.req_ids, case.past_lens, case.out_cache_loc,
+                                       case.query_cache, case.attn_cache, case.lse_cache, out, lse,
+                                       *ws, *cfg.scalar_args(), case.query_cache, e, e, e)
+
+    call()
+    torch.cuda.synchronize()
+    want = out.clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    for _ in range(4):          # a few steps queued back to back keep the device busy
+        call()
+    with torch.cuda.stream(side):
+        with pytest.raises(RuntimeError, match="another stream"):
+            call()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        call()                  # nothing in flight any more: accepted
+    torch.cuda.synchronize()
+    assert torch.equal(out, want)
+    _status_clean()
