@@ -327,7 +327,21 @@ def time_e2e(ext, case, ws, scal, out, lse, dev, n_steps, barrier, count_launche
         step()
     ms = (time.perf_counter() - w0) * 1e3 / n_steps
     launches = (count_launches() - before) if count_launches else None
-    return ms, hs.h2d_bytes, out_host.numel() * out_host.element_size(), launches
+
+    def copy_us(fn):   # one copy alone, CUDA events on the same stream
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        fn()
+        stream.synchronize()
+        t0.record()
+        for _ in range(10):
+            fn()
+        t1.record()
+        stream.synchronize()
+        return t0.elapsed_time(t1) * 100.0
+
+    parts = {"h2d_copy_us": copy_us(hs.upload),
+             "d2h_copy_us": copy_us(lambda: out_host.copy_(out, non_blocking=True))}
+    return ms, hs.h2d_bytes, out_host.numel() * out_host.element_size(), launches, parts
 
 
 def time_real_scan(args, ext, case, ws, out, lse, dev):
@@ -730,7 +744,7 @@ def run_ours(args):
             real_scan = {"error": f"{type(exc).__name__}: {exc}"[:200]}
 
     n_e2e = max(5, min(args.steps, 50))
-    e2e_ms, h2d, d2h, launches_e2e = time_e2e(
+    e2e_ms, h2d, d2h, launches_e2e, e2e_parts = time_e2e(
         ext, case, ws, scal, out, lse, dev, n_e2e, barrier,
         count_launches=lambda: ops.launch_info(dev)["kernel_launches"])
     te = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
@@ -775,7 +789,10 @@ def run_ours(args):
         "hbm_gbs_full_row_convention": float(bytes_all[1]) / (ms_max * 1e-3) / 1e9,
         "request_steps_per_s": world * batch / (ms_max * 1e-3),
         "e2e": {"value": e2e_ms * 1e3, "unit": "us", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "h2d_copies_per_step": 1},
+                "d2h_bytes_per_step": d2h, "h2d_copies_per_step": 1,
+                # the two copies timed alone (back to back, CUDA events): what of the
+                # end-to-end overhead over the device time is PCIe transfer
+                **e2e_parts},
         "gpu_launches": args.steps,
         "gpu_launches_e2e_region": int(launches_e2e),
         "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"],
@@ -866,8 +883,8 @@ def run_reference_arm(args):
                                args.warmup, barrier)
     clocks = clk.summary()
     ab = alg_bytes(ws, batch, hq, hkv, args.front_sink, args.capacity, case.past_lens.cpu().tolist())
-    e2e_ms, h2d, d2h, _ = time_e2e(ref_ext, case, ws, scal, out, lse, dev,
-                                   max(5, min(args.steps, 50)), barrier)
+    e2e_ms, h2d, d2h, _, _ = time_e2e(ref_ext, case, ws, scal, out, lse, dev,
+                                      max(5, min(args.steps, 50)), barrier)
     t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
