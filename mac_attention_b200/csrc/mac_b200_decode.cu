@@ -80,7 +80,7 @@ struct GroupPlan {
   int32_t cls;       // 0 demoted queue, 1 miss queue, 2 hit queue
   int32_t cost;      // token equivalents, sum over non-empty rows of (len + kOvhTok)
   int32_t mode;
-  int32_t bad;
+  int32_t req;       // ring / page-table row of the request (-1 for a malformed row)
 };
 
 struct Arena {
@@ -472,7 +472,7 @@ __device__ void phase_match_scan(const DecodeParams& p, uint8_t* smem) {
   // control words used after the barriers
   if (blockIdx.x == 0) {
     if (tid < 9) a.task_counts[tid] = 0;
-    if (tid == 9) *p.ar.ticket = 0u;
+    if (tid == 9) *p.ar.ticket = gridDim.x;   // pieces 0 .. grid-1 go to their CTA without a ticket
   }
   for (int g = blockIdx.x * kThreads + tid; g < p.NG; g += gridDim.x * kThreads)
     p.ar.garrive[g] = 0;
@@ -780,7 +780,7 @@ __device__ bool phase_match_scan_bulk(const DecodeParams& p, const CUtensorMap* 
   const int tid = threadIdx.x;
   if (blockIdx.x == 0) {
     if (tid < 9) a.task_counts[tid] = 0;
-    if (tid == 9) *p.ar.ticket = 0u;
+    if (tid == 9) *p.ar.ticket = gridDim.x;   // pieces 0 .. grid-1 go to their CTA without a ticket
   }
   for (int g = blockIdx.x * kThreads + tid; g < p.NG; g += gridDim.x * kThreads)
     p.ar.garrive[g] = 0;
@@ -1001,7 +1001,7 @@ __device__ void phase_classify(const DecodeParams& p) {
         a.group_tail_begin[go] = 0; a.group_tail_end[go] = 0; a.group_tail_tiles[go] = 0;
         a.group_mode[go] = 1;
         plan.sink_hi = 0; plan.band_lo = 0; plan.new_end = 0; plan.kv_len = 0;
-        plan.cls = 0; plan.cost = 0; plan.mode = 1; plan.bad = 1;
+        plan.cls = 0; plan.cost = 0; plan.mode = 1; plan.req = -1;
         p.ar.plan[g] = plan;
       }
       continue;
@@ -1166,7 +1166,7 @@ __device__ void phase_classify(const DecodeParams& p) {
       plan.new_end = new_end;
       plan.kv_len = kv_len;
       plan.mode = mode;
-      plan.bad = 0;
+      plan.req = req;
       plan.cls = (mode == 0) ? 2 : (eligible ? 1 : 0);
       int cost = 0;
       if (my_sink > 0) cost += my_sink + p.ovh_tok;
@@ -1215,29 +1215,37 @@ __device__ __forceinline__ unsigned long long block_scan_excl(unsigned long long
 
 // Every CTA derives the same schedule from the group plans: order groups by
 // queue (demoted, miss, hit), prefix-sum their cost, cut into pieces.
-__device__ void build_schedule(const DecodeParams& p, Schedule& sc, unsigned long long* scan_sm) {
+__device__ void build_schedule(const DecodeParams& p, Schedule& sc, unsigned long long* scan_sm,
+                               uint32_t* tmp) {
   const int tid = threadIdx.x;
   const int NG = p.NG;
-  // pass 1: class totals
-  unsigned long long carry = 0;
+  // pass 1: one load per group (queue class and cost, kept in shared memory for the two
+  // passes that follow) and the class totals
   unsigned long long totals = 0;
   for (int base = 0; base < NG; base += kThreads) {
     const int g = base + tid;
     unsigned long long v = 0;
-    if (g < NG) v = 1ull << (21 * __ldcg(&p.ar.plan[g].cls));
+    if (g < NG) {
+      const int2 cc = __ldcg(reinterpret_cast<const int2*>(&p.ar.plan[g].cls));   // cls, cost
+      tmp[g] = static_cast<uint32_t>(cc.y) | (static_cast<uint32_t>(cc.x) << 30);
+      v = 1ull << (21 * cc.x);
+    }
     unsigned long long t;
     block_scan_excl(v, scan_sm, t);
     totals += t;
   }
   const unsigned t0 = static_cast<unsigned>(totals & 0x1fffffull);
   const unsigned t1 = static_cast<unsigned>((totals >> 21) & 0x1fffffull);
-  // pass 2: rank inside class -> permutation
+  // pass 2: rank inside class -> permutation; costs move to cost-space order
+  unsigned long long carry = 0;
   for (int base = 0; base < NG; base += kThreads) {
     const int g = base + tid;
     int cls = 0;
+    uint32_t cost = 0;
     unsigned long long v = 0;
     if (g < NG) {
-      cls = __ldcg(&p.ar.plan[g].cls);
+      cls = static_cast<int>(tmp[g] >> 30);
+      cost = tmp[g] & 0x3fffffffu;
       v = 1ull << (21 * cls);
     }
     unsigned long long t;
@@ -1247,16 +1255,17 @@ __device__ void build_schedule(const DecodeParams& p, Schedule& sc, unsigned lon
       const unsigned r = static_cast<unsigned>((ex >> (21 * cls)) & 0x1fffffull);
       const unsigned v_idx = (cls == 0) ? r : (cls == 1 ? t0 + r : t0 + t1 + r);
       sc.gperm[v_idx] = static_cast<uint16_t>(g);
+      sc.cpre[v_idx] = cost;
     }
   }
   __syncthreads();
-  // pass 3: cost prefix in cost-space order
+  // pass 3: cost prefix in cost-space order (in place)
   unsigned long long ccarry = 0;
   for (int base = 0; base < NG; base += kThreads) {
     const int v_idx = base + tid;
     unsigned long long c = 0;
     if (v_idx < NG) {
-      c = static_cast<unsigned long long>(__ldcg(&p.ar.plan[sc.gperm[v_idx]].cost));
+      c = static_cast<unsigned long long>(sc.cpre[v_idx]);
       // bits 40.. count the groups small enough to be finished in one fused pass
       if (c > 0 && c <= static_cast<unsigned long long>(p.fuse_max)) c |= 1ull << 40;
     }
@@ -1356,12 +1365,11 @@ struct WarpWork {
 // softmax.  Leaves the warp's un-normalised accumulators (rows = heads), running
 // max (log2 domain) and denominator (already summed over the quad).
 __device__ __forceinline__ void warp_stream(const DecodeParams& p, uint8_t* smem, int n, int hkv,
-                                            const WarpWork& w, float (&oacc)[16][4], float& m_run,
-                                            float& l_run) {
+                                            int req, int P, const WarpWork& w,
+                                            float (&oacc)[16][4], float& m_run, float& l_run) {
   const MacB200DecodeArgs& a = p.a;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int G = p.G;
-  const int req = a.req_ids[n], P = a.past_lens[n];
   const int hrow = lane >> 2, quad = lane & 3;
   const bool has_head = hrow < G;
   const int hq = hkv * G + (has_head ? hrow : 0);
@@ -1573,13 +1581,13 @@ __device__ __forceinline__ void combine_reduce(uint8_t* smem, int h, int w_lo, i
 
 // One segment by the whole CTA: warp w takes blocks w, w+8, ...; the normalised
 // partial (o, natural-log LSE) of every head goes to arena slot `slot`.
-__device__ void attend_segment(const DecodeParams& p, uint8_t* smem, int n, int hkv, int t0,
-                               int t1, int row_kind, int slot) {
+__device__ void attend_segment(const DecodeParams& p, uint8_t* smem, int n, int hkv, int req, int P,
+                               int t0, int t1, int row_kind, int slot) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float oacc[16][4];
   float m_run, l_run;
   const WarpWork w{t0, t1, row_kind, warp, kWarps};
-  warp_stream(p, smem, n, hkv, w, oacc, m_run, l_run);
+  warp_stream(p, smem, n, hkv, req, P, w, oacc, m_run, l_run);
   combine_publish(smem, oacc, m_run, l_run);
   if (warp < p.G) {
     float4 acc;
@@ -1612,7 +1620,7 @@ __device__ __forceinline__ void merge_state(float4& o, float& lse, const float4&
 // Reused prefix state of head hq (warp-wide; lane owns 4 dims): the matched
 // ring row if the head is a hit with a finite LSE, else empty (DEC.cu:4346-4365).
 __device__ __forceinline__ void load_prefix_state(const MacB200DecodeArgs& a, int n, int hq,
-                                                  float4& o, float& lse) {
+                                                  int req, float4& o, float& lse) {
   const int lane = threadIdx.x & 31;
   const int64_t ho = static_cast<int64_t>(n) * a.Hq + hq;
   o = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -1620,7 +1628,7 @@ __device__ __forceinline__ void load_prefix_state(const MacB200DecodeArgs& a, in
   const int hit = __ldcg(a.head_hit + ho);
   const int mslot = __ldcg(a.head_match_slot + ho);
   if (hit != 0 && mslot >= 0) {
-    const int64_t row = (static_cast<int64_t>(a.req_ids[n]) * a.M + mslot) * a.Hq + hq;
+    const int64_t row = (static_cast<int64_t>(req) * a.M + mslot) * a.Hq + hq;
     const float pl_lse = a.lse_cache[row];
     if (isfinite(pl_lse)) {
       const uint2 raw = *reinterpret_cast<const uint2*>(
@@ -1633,13 +1641,12 @@ __device__ __forceinline__ void load_prefix_state(const MacB200DecodeArgs& a, in
 
 // Ring row P mod M of this step (query, state, LSE); only for requests whose
 // cache passes the readiness gate (DEC.cu:4485-4497).
-__device__ __forceinline__ void write_ring_row(const MacB200DecodeArgs& a, int n, int hq,
-                                               const float4& o, float lse) {
+__device__ __forceinline__ void write_ring_row(const MacB200DecodeArgs& a, int n, int hq, int req,
+                                               int P, const float4& o, float lse) {
   const int lane = threadIdx.x & 31;
-  const int req = a.req_ids[n];
   if (!request_ready(a, req)) return;
   const int64_t ho = static_cast<int64_t>(n) * a.Hq + hq;
-  const int dest = a.past_lens[n] % a.M;
+  const int dest = P % a.M;
   const int64_t row = (static_cast<int64_t>(req) * a.M + dest) * a.Hq + hq;
   const bool ok = isfinite(lse);
   const uint2 qv = *reinterpret_cast<const uint2*>(static_cast<const char*>(a.q_pre) +
@@ -1698,7 +1705,7 @@ __device__ void merge_group(const DecodeParams& p, uint8_t* smem, const Schedule
 
   float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
   float lse = -INFINITY;
-  if (active) load_prefix_state(a, n, hq, o, lse);
+  if (active) load_prefix_state(a, n, hq, pl.req, o, lse);
   const uint32_t stage_u32 = smem_u32(smem);
   auto merge_row = [&](int r) {     // control flow is uniform over the CTA
     if (rows[r].c == 0) return;
@@ -1778,7 +1785,7 @@ __device__ void merge_group(const DecodeParams& p, uint8_t* smem, const Schedule
     }
   };
   merge_row(1);
-  if (active) write_ring_row(a, n, hq, o, lse);
+  if (active) write_ring_row(a, n, hq, pl.req, pl.kv_len - 1, o, lse);
   merge_row(0);
   merge_row(2);
   if (active) write_output(a, n, hq, o, lse);
@@ -1827,17 +1834,17 @@ __device__ void attend_group_fused(const DecodeParams& p, uint8_t* smem, int n, 
   float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
   float lse = -INFINITY;
   const int hq = hkv * G + (warp < G ? warp : 0);
-  if (warp < G) load_prefix_state(a, n, hq, o, lse);
+  if (warp < G) load_prefix_state(a, n, hq, pl.req, o, lse);
 
   float oacc[16][4];
   float m_run, l_run;
-  warp_stream(p, smem, n, hkv, w, oacc, m_run, l_run);
+  warp_stream(p, smem, n, hkv, pl.req, pl.kv_len - 1, w, oacc, m_run, l_run);
   combine_publish(smem, oacc, m_run, l_run);
   if (warp < G) {
     float4 o2;
     float l2;
     if (nw[1] > 0) { combine_reduce(smem, warp, base[1], base[1] + nw[1], o2, l2); merge_state(o, lse, o2, l2); }
-    write_ring_row(a, n, hq, o, lse);
+    write_ring_row(a, n, hq, pl.req, pl.kv_len - 1, o, lse);
     if (nw[0] > 0) { combine_reduce(smem, warp, base[0], base[0] + nw[0], o2, l2); merge_state(o, lse, o2, l2); }
     if (nw[2] > 0) { combine_reduce(smem, warp, base[2], base[2] + nw[2], o2, l2); merge_state(o, lse, o2, l2); }
     write_output(a, n, hq, o, lse);
@@ -1852,7 +1859,7 @@ __device__ void phase_attend(const DecodeParams& p, uint8_t* smem) {
   Schedule sc;
   sc.gperm = reinterpret_cast<uint16_t*>(smem + kRingBytes);
   sc.cpre = reinterpret_cast<uint32_t*>(smem + kRingBytes + kSmemPerm);
-  build_schedule(p, sc, scan_sm);
+  build_schedule(p, sc, scan_sm, reinterpret_cast<uint32_t*>(smem));   // the idle K/V ring is the scratch
   const int tid = threadIdx.x;
   const int NG = p.NG;
   if (blockIdx.x == 0 && tid == 0) {
@@ -1861,11 +1868,15 @@ __device__ void phase_attend(const DecodeParams& p, uint8_t* smem) {
   }
   if (sc.W == 0) return;
 
-  for (;;) {
-    __syncthreads();
-    if (tid == 0) sh_piece = static_cast<int>(atomicAdd(p.ar.ticket, 1u));
-    __syncthreads();
-    const int piece = sh_piece;
+  // CTA b takes piece b; further pieces (only with more than one wave of pieces) by ticket.
+  for (bool first = true;; first = false) {
+    int piece = static_cast<int>(blockIdx.x);
+    if (!first) {
+      __syncthreads();
+      if (tid == 0) sh_piece = static_cast<int>(atomicAdd(p.ar.ticket, 1u));
+      __syncthreads();
+      piece = sh_piece;
+    }
     if (piece >= static_cast<int>(sc.pieces)) break;
     const uint32_t x0 = static_cast<uint32_t>(piece) * sc.ps;
     uint32_t x1 = x0 + sc.ps;
@@ -1885,7 +1896,7 @@ __device__ void phase_attend(const DecodeParams& p, uint8_t* smem) {
         const int4* src = reinterpret_cast<const int4*>(&p.ar.plan[g]);
         const int4 w0 = __ldcg(src), w1 = __ldcg(src + 1);
         pl.sink_hi = w0.x; pl.band_lo = w0.y; pl.new_end = w0.z; pl.kv_len = w0.w;
-        pl.cls = w1.x; pl.cost = w1.y; pl.mode = w1.z; pl.bad = w1.w;
+        pl.cls = w1.x; pl.cost = w1.y; pl.mode = w1.z; pl.req = w1.w;
       }
       const int n = g / p.a.Hkv, hkv = g - n * p.a.Hkv;
       // A small group is never split: it belongs to the piece that holds its
@@ -1909,7 +1920,7 @@ __device__ void phase_attend(const DecodeParams& p, uint8_t* smem) {
         segment_tokens(rows[r], p.ovh_tok, x0, x1, t0, t1);
         const int slot = piece + 3 * v + r;
         if (slot < p.ar.slots) {
-          attend_segment(p, smem, n, hkv, t0, t1, r, slot);
+          attend_segment(p, smem, n, hkv, pl.req, pl.kv_len - 1, t0, t1, r, slot);
         } else if (tid == 0) {
           atomicOr(&g_status, MAC_B200_STATUS_SCHED_OVERFLOW);
         }

@@ -123,3 +123,32 @@ def test_rows_whose_distance_hides_in_the_unprobed_dims(mode, scan_mode):
     assert_outputs_close(cu, orc, orc_case)
     assert 0 < int(orc.head_hit.sum()) < orc.head_hit.numel()
     assert ops.query_status() == 0
+
+
+@pytest.mark.parametrize("knobs", [
+    {"MAC_B200_PIECE_WAVES": "2"}, {"MAC_B200_PIECE_WAVES": "4"},
+    {"MAC_PERSISTENT_COOP_CTAS": "37"}, {"MAC_PERSISTENT_COOP_CTAS": "5", "MAC_B200_PIECE_WAVES": "4"},
+    {"MAC_B200_MIN_PIECE": "64", "MAC_B200_FUSE_MAX": "0"}, {"MAC_B200_OVH_TOK": "64"},
+], ids=lambda k: "_".join(f"{a[9:]}{b}" for a, b in k.items()))
+def test_schedule_knobs_do_not_change_results(knobs, monkeypatch):
+    """The attention schedule's tuning knobs (pieces per CTA, a capped grid, the smallest piece,
+    no fused groups, the row-opening cost) only move work between CTAs: with several pieces per
+    CTA the later ones are pulled through the ticket, with a capped grid one CTA walks many
+    groups.  Decisions and outputs stay those of the oracle."""
+    for name, value in knobs.items():
+        monkeypatch.setenv(name, value)
+    rng = random.Random(77)
+    for i in range(6):
+        spec = _draw(rng)
+        spec["ctxs"] = [rng.choice([rng.randint(2000, 9000), rng.randint(300, 900)]) for _ in spec["ctxs"]]
+        case, cfg = _case(spec)
+        cfg.max_context = 16384
+        orc, orc_case = run_oracle(case, cfg)
+        cu = run_cuda(case, cfg)
+        tag = f"{knobs} case {i}: {spec}"
+        try:
+            assert_decisions_equal(cu, orc, spec["batch"])
+            assert_outputs_close(cu, orc, orc_case)
+        except AssertionError as exc:
+            raise AssertionError(f"{tag}\n{exc}") from exc
+        assert ops.query_status() == 0, tag
