@@ -1420,32 +1420,52 @@ __device__ __forceinline__ void warp_stream(const DecodeParams& p, uint8_t* smem
   // pool row of the lane's token (lanes 0..15) of this warp's j-th block; -1 = past the end
   // (Page-table entries are followed as they are, like in the reference: a bounds check here
   // was measured at 0.6-1.2 % of the whole step, a check inside issue_block at 16 %.)
-  auto load_token = [&](int j) -> int64_t {
+  // (pool rows travel as 32-bit values -- the launcher refuses pools of 2^31 rows or more --
+  // so that handing a row to the other lanes is one shuffle; every instruction of the
+  // copy-issue loop below is worth 0.2-0.5 % of a full-attention step)
+  auto load_token = [&](int j) -> int {
     const int pos = t0 + (w.first + j * w.stride) * kBlkTok + (lane & 15);
-    if (pos >= t1) return -1;
+    if (pos >= t1) return 0;   // never copied (see issue_block); any valid row will do
     if (pos == P) {
       return a.out_cache_loc_is_i64
-                 ? static_cast<int64_t>(static_cast<const int64_t*>(a.out_cache_loc)[n])
-                 : static_cast<int64_t>(static_cast<const int32_t*>(a.out_cache_loc)[n]);
+                 ? static_cast<int>(static_cast<const int64_t*>(a.out_cache_loc)[n])
+                 : static_cast<const int32_t*>(a.out_cache_loc)[n];
     }
-    return static_cast<int64_t>(__ldg(table + pos));
+    return __ldg(table + pos);
   };
-  auto issue_block = [&](int j, int64_t tok_reg) {
+  const char* kb_lane = kbase + (lane & 15) * 16;
+  const char* vb_lane = vbase + (lane & 15) * 16;
+  const uint32_t stride32 = static_cast<uint32_t>(tok_stride);
+  auto issue_block = [&](int j, int tok_reg) {
     const uint32_t st = ring_u32 + (j % kStages) * kStageBytes;
     const int chunk = lane & 15;
+    // rows of this block that lie inside [t0, t1): all 16 except in the last block of a row
+    const int nvalid = t1 - (t0 + (w.first + j * w.stride) * kBlkTok);
+    if (nvalid >= kBlkTok) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int r = (lane >> 4) + 2 * i;
-      const int64_t tok = __shfl_sync(0xffffffffu, tok_reg, r);
-      const bool ok = tok >= 0;
-      const int64_t off = (ok ? tok : 0) * tok_stride + chunk * 16;
-      const uint32_t dst = st + r * kRowBytes + ((chunk ^ (r & 7)) << 4);
-      cp_async16(dst, kbase + off, ok ? 16 : 0);
-      cp_async16(dst + kBlkTok * kRowBytes, vbase + off, ok ? 16 : 0);
+      for (int i = 0; i < 8; ++i) {
+        const int r = (lane >> 4) + 2 * i;
+        const uint32_t tok = static_cast<uint32_t>(__shfl_sync(0xffffffffu, tok_reg, r));
+        const uint64_t off = static_cast<uint64_t>(tok) * stride32;
+        const uint32_t dst = st + r * kRowBytes + ((chunk ^ (r & 7)) << 4);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(kb_lane + off) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + kBlkTok * kRowBytes), "l"(vb_lane + off) : "memory");
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int r = (lane >> 4) + 2 * i;
+        const uint32_t tok = static_cast<uint32_t>(__shfl_sync(0xffffffffu, tok_reg, r));
+        const int bytes = r < nvalid ? 16 : 0;   // rows past the end are zero-filled
+        const uint64_t off = static_cast<uint64_t>(tok) * stride32;
+        const uint32_t dst = st + r * kRowBytes + ((chunk ^ (r & 7)) << 4);
+        cp_async16(dst, kb_lane + off, bytes);
+        cp_async16(dst + kBlkTok * kRowBytes, vb_lane + off, bytes);
+      }
     }
   };
 
-  int64_t tok_next = -1;
+  int tok_next = -1;
 #pragma unroll
   for (int j = 0; j < kStages - 1; ++j) {
     if (j < mine) issue_block(j, load_token(j));
@@ -2095,6 +2115,9 @@ int validate_decode_args(const MacB200DecodeArgs& a, bool* empty) {
   if (NGll > kMaxGroups)
     return fail(MAC_B200_EUNSUPPORTED, "N*Hkv=%lld exceeds this build's limit of %d", NGll,
                 kMaxGroups);
+  if (a.kv_tokens >= (int64_t(1) << 31))
+    return fail(MAC_B200_EUNSUPPORTED, "KV pool of %lld rows exceeds this build's limit of 2^31 - 1",
+                static_cast<long long>(a.kv_tokens));
   return MAC_B200_OK;
 }
 
