@@ -112,7 +112,11 @@ typedef struct MacB200DecodeArgs {
    * 0 (default) keeps the reference's rule and its decisions. */
   int32_t bench_long_band;
 
-  /* ---- inputs ---- */
+  /* ---- inputs ----
+   * Every pointer is an address the device can access.  q_post, q_pre and out may also be
+   * page-locked host memory mapped into the device's address space: out is written once per
+   * row, which saves the copy of the result back to the host; q_pre is read once per scanned
+   * ring tile, so a step that scans should keep it in device memory. */
   const void* q_post;          /* [N,Hq,D] bf16, post-RoPE query (attention)                */
   const void* q_pre;           /* [N,Hq,D] bf16, pre-RoPE query (matching, ring write)      */
   const void* k_buffer;        /* [kv_tokens,Hkv,D] bf16                                    */

@@ -57,6 +57,19 @@ int check(const Tensor& t, const char* name, at::ScalarType dtype, int64_t dim) 
   return 0;
 }
 
+// The step's own inputs and its output (q_post, q_pre, out) may also lie in pinned host memory
+// (torch's pin_memory(): page-locked by the CUDA runtime, one address on host and device): the
+// kernel then reads the queries and writes the output over the bus itself, and a caller whose
+// queries are produced on the host, or who wants the output there, needs no staging copy.
+int check_step_io(const Tensor& t, const char* name, at::ScalarType dtype, int64_t dim) {
+  REQUIRE(t.is_cuda() || (t.device().is_cpu() && t.is_pinned()), name,
+          " must be CUDA or pinned host memory");
+  REQUIRE(t.is_contiguous(), name, " must be contiguous");
+  REQUIRE(t.scalar_type() == dtype, name, " has wrong dtype");
+  REQUIRE(t.dim() == dim, name, " has wrong rank");
+  return 0;
+}
+
 int check_partial_o(const Tensor& t, const char* name) {
   REQUIRE(t.is_cuda(), name, " must be CUDA");
   REQUIRE(t.is_contiguous(), name, " must be contiguous");
@@ -114,8 +127,8 @@ int decode(
     int64_t bench_seed, int64_t bench_miss_mask, int64_t bench_layer_id,
     const OptTensor& query_post_cache, const OptTensor& mac_cache_ready,
     const OptTensor& mac_cache_epoch, const OptTensor& mac_request_epoch) {
-  REQUIRE_OK(check(q_post, "q_post", at::kBFloat16, 3));
-  REQUIRE_OK(check(q_pre, "q_pre", at::kBFloat16, 3));
+  REQUIRE_OK(check_step_io(q_post, "q_post", at::kBFloat16, 3));
+  REQUIRE_OK(check_step_io(q_pre, "q_pre", at::kBFloat16, 3));
   REQUIRE_OK(check(k_buffer, "k_buffer", at::kBFloat16, 3));
   REQUIRE_OK(check(v_buffer, "v_buffer", at::kBFloat16, 3));
   REQUIRE_OK(check(req_to_token, "req_to_token", at::kInt, 2));
@@ -130,7 +143,7 @@ int decode(
   if (present(query_post_cache)) REQUIRE_OK(check(*query_post_cache, "query_post_cache", at::kBFloat16, 4));
   REQUIRE_OK(check(attn_cache, "attn_cache", at::kBFloat16, 4));
   REQUIRE_OK(check(lse_cache, "lse_cache", at::kFloat, 3));
-  REQUIRE_OK(check(out, "out", at::kBFloat16, 3));
+  REQUIRE_OK(check_step_io(out, "out", at::kBFloat16, 3));
   REQUIRE(optional_lse.is_cuda(), "optional_lse must be CUDA");
   REQUIRE(optional_lse.is_contiguous(), "optional_lse must be contiguous");
   REQUIRE(optional_lse.numel() == 0 || optional_lse.scalar_type() == at::kFloat,
@@ -308,8 +321,9 @@ int decode(
   a.bench_long_band = env_flag("MAC_B200_BENCH_LONG_BAND", 0);   // benchmark extension, default off
   a.out_cache_loc_is_i64 = out_cache_loc.scalar_type() == at::kLong ? 1 : 0;
   a.phase_cycles_count = static_cast<int32_t>(phase_cycles.numel());
-  a.q_post = q_post.data_ptr();
+  a.q_post = q_post.data_ptr();   // pinned host memory has the same address on the device
   a.q_pre = q_pre.data_ptr();
+  a.out = out.data_ptr();
   a.k_buffer = k_buffer.data_ptr();
   a.v_buffer = v_buffer.data_ptr();
   a.req_to_token = req_to_token.data_ptr<int32_t>();
@@ -319,7 +333,6 @@ int decode(
   a.query_cache = query_cache.data_ptr();
   a.attn_cache = attn_cache.data_ptr();
   a.lse_cache = lse_cache.data_ptr<float>();
-  a.out = out.data_ptr();
   a.match_dist = match_dist.data_ptr<float>();
   a.match_pos = match_pos.data_ptr<int32_t>();
   a.match_slot = match_slot.data_ptr<int32_t>();
@@ -339,8 +352,8 @@ int decode(
   a.task_counts = task_counts.data_ptr<int32_t>();
   a.phase_cycles = phase_cycles.data_ptr<int64_t>();
 
-  const c10::cuda::CUDAGuard guard(q_post.device());
-  void* stream = static_cast<void*>(c10::cuda::getCurrentCUDAStream(q_post.device().index()).stream());
+  const c10::cuda::CUDAGuard guard(k_buffer.device());   // q_post may be host memory
+  void* stream = static_cast<void*>(c10::cuda::getCurrentCUDAStream(k_buffer.device().index()).stream());
   return entry == kDecodeNoAlloc ? mac_b200_persistent_decode_bf16_noalloc(&a, stream)
                                  : mac_b200_persistent_decode_bf16(&a, stream);
 }

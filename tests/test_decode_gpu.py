@@ -309,6 +309,39 @@ def test_run_twice_is_bit_identical_and_graph_replay_matches():
     _status_clean()
 
 
+def test_step_tensors_in_pinned_host_memory_give_the_same_step():
+    """q_post, q_pre and out may lie in pinned host memory (the kernel reads and writes them
+    over the bus); a pageable host tensor is refused."""
+    ext = load_mac_persistent_decode_extension()
+    case = synth.make_decode_case(batch=3, ctx=0, ctx_list=[3000, 700, 1900], hq=32, hkv=8,
+                                  capacity=256, seed=33)
+    synth.plant_matches(case, hit_fraction=0.5, seed=4)
+    cfg = O.DecodeConfig(max_context=4096, semantic_pos_ahead=128, front_sink_tokens=16)
+    want = run_cuda(case, cfg)
+    c = case.to("cuda").clone()
+    ws = make_decode_workspace(3, 32, 8, 256, 4096, 32, 32, 128, 16)
+    lse = torch.empty(3, 32, device="cuda")
+    e = torch.empty(0)
+    q_post = case.q_post.cpu().pin_memory()
+    q_pre = case.q_pre.cpu().pin_memory()
+    out = torch.zeros(case.q_post.shape, dtype=torch.bfloat16).pin_memory()
+
+    def call(q_post_t, q_pre_t, out_t):
+        ext.mac_persistent_decode_bf16(q_post_t, q_pre_t, c.k, c.v, c.req_to_token, c.req_ids,
+                                       c.past_lens, c.out_cache_loc, c.query_cache, c.attn_cache,
+                                       c.lse_cache, out_t, lse, *ws, *cfg.scalar_args(),
+                                       c.query_cache, e, e, e)
+
+    call(q_post, q_pre, out)
+    torch.cuda.synchronize()
+    assert torch.equal(out, want.out.cpu()) and torch.equal(lse, want.lse)
+    assert torch.equal(c.attn_cache, want.case.attn_cache)
+    assert torch.equal(c.query_cache, want.case.query_cache)
+    with pytest.raises(RuntimeError, match="pinned host memory"):
+        call(q_post, q_pre, torch.zeros(case.q_post.shape, dtype=torch.bfloat16))
+    _status_clean()
+
+
 def test_hit_path_equals_full_attention_at_long_context():
     """Size-independent property at a full-size context: a step that reuses the
     prefix state written by the previous step gives the same output as exact
