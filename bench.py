@@ -270,6 +270,25 @@ def time_graph(launch, steps, warmup, barrier=None):
     return t0.elapsed_time(t1) / steps, graph
 
 
+def replay_blocks(graph, steps, blocks=5):
+    """Further blocks of `steps` replays of an already-timed graph, each between
+    its own CUDA events: the spread of the headline number inside one process."""
+    import torch
+
+    out = []
+    for _ in range(blocks):
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(steps):
+            graph.replay()
+        t1.record()
+        torch.cuda.synchronize()
+        out.append(t0.elapsed_time(t1) * 1e3 / steps)
+    out.sort()
+    return {"blocks": blocks, "steps_per_block": steps, "us_min": out[0],
+            "us_median": out[len(out) // 2], "us_max": out[-1]}
+
+
 class HostStep:
     """One step's host-side inputs the way a serving engine would send them: the
     two query tensors and the three per-row integer vectors packed into ONE
@@ -732,6 +751,7 @@ def run_ours(args):
     if profiler_range:   # the side legs below are not part of the launch list
         torch.cuda.synchronize()
         torch.cuda.profiler.stop()
+    stability = replay_blocks(graph, args.steps)
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -811,6 +831,8 @@ def run_ours(args):
         "hbm_gbs": float(bytes_all[0]) / (ms_max * 1e-3) / 1e9,
         "hbm_gbs_full_row_convention": float(bytes_all[1]) / (ms_max * 1e-3) / 1e9,
         "request_steps_per_s": world * batch / (ms_max * 1e-3),
+        # five more blocks of `steps` replays of the same graph on this rank, after the timed one
+        "stability": stability,
         "e2e": {"value": e2e_ms * 1e3, "unit": "us", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "h2d_copies_per_step": 1, "d2h_copies_per_step": 0,
                 # the output is written by the kernel into the caller's pinned host buffer;
