@@ -647,7 +647,7 @@ __device__ void phase_match_scan(const DecodeParams& p, uint8_t* smem) {
       cp_async_commit();
     }
     cp_async_wait<0>();
-    __syncthreads();   // everyone is done with this round's tile descriptors
+    __syncthreads();   // everyone is done with the tile descriptors of this pass
     if (spar > 1) {
       for (int t = tid; t < rt * Hq; t += kThreads) {
         const int k = t / Hq, h = t - k * Hq;
@@ -876,7 +876,7 @@ __device__ bool phase_match_scan_bulk(const DecodeParams& p, const CUtensorMap* 
 #pragma unroll
       for (int c = 0; c < kChunks; ++c) dst[c] = __ldg(qp + c);
     };
-    int job = 0;   // active tiles seen so far in this round (selects the best-match buffer)
+    int job = 0;   // active tiles seen so far in this pass (selects the best-match buffer)
     BoxTile t{};
     advance(ck, cb);
     for (int i = 0; i < nact; ++i) {
@@ -959,7 +959,7 @@ __device__ bool phase_match_scan_bulk(const DecodeParams& p, const CUtensorMap* 
       advance(ck, cb);
     }
     seq_base += static_cast<unsigned>(nact);
-    __syncthreads();   // everyone is done with this round's tile descriptors
+    __syncthreads();   // everyone is done with the tile descriptors of this pass
   }
   return !failed;
 }
