@@ -218,13 +218,16 @@ prefill_downdate_ring_kernel(const MacB200PrefillBuildArgs a) {
 // CTA = (slice of a request's ring rows, one KV head); 8 independent warps.  A
 // warp tile is 16 MMA rows = 16/G consecutive tokens x the G query heads of the
 // KV head.  Per tile the warp
-//   1. cp.asyncs its q_post, q_pre, full and band rows into its own staging
-//      and fetches the rows' LSEs (lane r < 16 owns MMA row r),
-//   2. S = Q K^T over the sink keys, softmax (log2 domain), O = P V,
+//   1. cp.asyncs its full and band rows into its own staging and fetches the
+//      rows' LSEs (lane r < 16 owns MMA row r); the q_post and q_pre rows were
+//      requested while the previous tile was still being worked on,
+//   2. S = Q K^T over the sink keys; as soon as the staged q rows are dead the
+//      NEXT tile's q rows are requested into the same staging, so that a tile
+//      never starts by waiting for DRAM; softmax (log2 domain), O = P V,
 //   3. folds both downdates into three factors per row, one row per lane:
 //      state = full*A - band*B - sink_unnormalised*C,
-//   4. parks the sink state in shared memory (over the dead q staging) and
-//      streams the rows to the ring in 16-byte chunks.
+//   4. applies them in the accumulators' own layout, in place over the staged
+//      full rows, and streams the rows to the ring in 16-byte chunks.
 // With 246 registers per thread (64 score + 64 output accumulators) only eight
 // warps fit an SM, so the kernel is bound by issue latency rather than by HBM
 // or the tensor pipe; anything the warp does on a few lanes only (the row
@@ -234,13 +237,11 @@ constexpr int kSxRowBytes = kSxD * 2;
 constexpr int kSxMaxF = 128;
 constexpr int kSxWarps = 8;
 constexpr int kSxThreads = kSxWarps * 32;
-constexpr int kSxSinkStride = 136;                     // floats per parked sink row
-constexpr int kSxRegionA = 16 * kSxSinkStride * 4;     // q_post + q_pre staging, then the sink state
 constexpr int kSxRegionRows = 16 * kSxRowBytes;        // one staged 16-row tensor
+constexpr int kSxRegionA = 2 * kSxRegionRows;          // q_post + q_pre staging of one tile
 constexpr int kSxWarpBytes = kSxRegionA + 2 * kSxRegionRows + 16 * 16;
 constexpr int kSxKvBytes = 2 * kSxMaxF * kSxRowBytes;
 constexpr int kSxSmemBytes = kSxKvBytes + kSxWarps * kSxWarpBytes;
-static_assert(kSxRegionA >= 2 * kSxRegionRows, "q_post and q_pre staging must fit region A");
 
 __device__ __forceinline__ uint32_t sx_smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -374,29 +375,39 @@ prefill_sink_exclusive_ring_kernel(const MacB200PrefillBuildArgs a) {
   const size_t head_base = static_cast<size_t>(kh * G) * kSxRowBytes + c * 16;
   const int mi = lane >> 3, l7 = lane & 7;
 
-  for (int tile = blockIdx.x * kSxWarps + warp; tile < ntiles; tile += gridDim.x * kSxWarps) {
+  // q_post (swizzled, an MMA operand) and q_pre (linear, copied through) rows of a tile
+  auto stage_q_rows = [&](int tile_q) {
+    const int iq = tile_q * TG;
+    const size_t tsrc = src_base + static_cast<size_t>(iq) * row_bf16;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int r = 2 * j + r_half;
+      const bool ok = tile_q < ntiles && iq + r / G < sp.keep;
+      const size_t so = ok ? tsrc + static_cast<size_t>(r / G) * row_bf16 + (r % G) * kSxRowBytes : 0;
+      sx_cp_async16(regA_u32 + r * kSxRowBytes + ((c ^ (r & 7)) << 4), qpost + so, ok ? 16 : 0);
+      sx_cp_async16(regA_u32 + kSxRegionRows + r * kSxRowBytes + c * 16, qpre + so, ok ? 16 : 0);
+    }
+    sx_commit();
+  };
+  const int tile_step = gridDim.x * kSxWarps;
+  if (static_cast<int>(blockIdx.x) * kSxWarps + warp < ntiles)
+    stage_q_rows(blockIdx.x * kSxWarps + warp);
+
+  for (int tile = blockIdx.x * kSxWarps + warp; tile < ntiles; tile += tile_step) {
     const int i0 = tile * TG;
     const size_t tile_src = src_base + static_cast<size_t>(i0) * row_bf16;
     int dbase = sp.base_dest + i0;                  // ring row of the tile's first token
     if (dbase >= p.M) dbase -= p.M;
 
-    // ---- 1. stage the tile
+    // ---- 1. stage the tile: full and band rows now; the q rows are already on their way
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int r = 2 * j + r_half;
       const bool ok = i0 + r / G < sp.keep;
       const size_t so = ok ? tile_src + static_cast<size_t>(r / G) * row_bf16 + (r % G) * kSxRowBytes : 0;
-      sx_cp_async16(regA_u32 + r * kSxRowBytes + ((c ^ (r & 7)) << 4), qpost + so, ok ? 16 : 0);
-      sx_cp_async16(regA_u32 + kSxRegionRows + r * kSxRowBytes + c * 16, qpre + so, ok ? 16 : 0);
-    }
-    sx_commit();
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int r = 2 * j + r_half;
-      const bool ok = i0 + r / G < sp.keep;
-      const size_t so = ok ? tile_src + static_cast<size_t>(r / G) * row_bf16 + (r % G) * kSxRowBytes : 0;
-      sx_cp_async16(full_u32 + r * kSxRowBytes + c * 16, fsrc + so, ok ? 16 : 0);
-      sx_cp_async16(band_u32 + r * kSxRowBytes + c * 16, bsrc + so, ok ? 16 : 0);
+      const uint32_t dst = r * kSxRowBytes + ((c ^ (r & 7)) << 4);
+      sx_cp_async16(full_u32 + dst, fsrc + so, ok ? 16 : 0);
+      sx_cp_async16(band_u32 + dst, bsrc + so, ok ? 16 : 0);
     }
     sx_commit();
     // LSEs of the row whose factors this lane works out later (lane r < 16 owns MMA row r):
@@ -452,6 +463,11 @@ prefill_sink_exclusive_ring_kernel(const MacB200PrefillBuildArgs a) {
         }
       }
     }
+    // The staged q rows are dead (q_pre went to the ring above, q_post into S): request the next
+    // tile's into the same staging now, a tile's worth of work ahead of their use.
+    __syncwarp();
+    if (tile + tile_step < ntiles) stage_q_rows(tile + tile_step); else sx_commit();
+
     // softmax over the F sink keys, log2 domain; keys >= F only exist in the last block
     if (F & 15) {
 #pragma unroll
@@ -527,7 +543,6 @@ prefill_sink_exclusive_ring_kernel(const MacB200PrefillBuildArgs a) {
 
     // ---- 3. both downdates folded into three factors per row, lane r < 16 for MMA row r:
     //   state = full * A - band * B - sink_unnormalised * C
-    __syncwarp();   // every lane is done with the staged q rows: region A is free
     {
       // row r's scaled maximum and denominator live in the quad 4 * (r & 7): rows 0..7 in
       // the "lo" values, rows 8..15 in the "hi" values
@@ -561,42 +576,41 @@ prefill_sink_exclusive_ring_kernel(const MacB200PrefillBuildArgs a) {
         lc[static_cast<size_t>(d) * H + h] = ret2;
       }
     }
-    // ---- 4. park the sink state, then stream the rows to the ring
+    // ---- 4. apply the factors where the sink state lies (the accumulators' layout: rows rlo
+    // and rhi, columns jj * 8 + quad * 2 + {0, 1}), in place over the staged full rows, then
+    // stream the rows to the ring
+    sx_wait<1>();   // full and band rows have landed; the next tile's q rows may still be in flight
+    __syncwarp();   // and every lane sees them and the row factors
     {
-      float* plo = reinterpret_cast<float*>(regA) + rlo * kSxSinkStride + quad * 2;
-      float* phi = reinterpret_cast<float*>(regA) + rhi * kSxSinkStride + quad * 2;
+      const float4 klo = scal[rlo], khi = scal[rhi];
+      uint8_t* f_lo = fullS + rlo * kSxRowBytes + quad * 4;
+      const uint8_t* b_lo = bandS + rlo * kSxRowBytes + quad * 4;
+      constexpr int kHi = 8 * kSxRowBytes;   // row rhi = rlo + 8 has the same swizzle (rhi & 7 == rlo)
 #pragma unroll
       for (int jj = 0; jj < 16; ++jj) {
-        *reinterpret_cast<float2*>(plo + jj * 8) = make_float2(o[jj][0], o[jj][1]);
-        *reinterpret_cast<float2*>(phi + jj * 8) = make_float2(o[jj][2], o[jj][3]);
+        const int ch = (jj ^ rlo) << 4;
+        uint32_t* fl = reinterpret_cast<uint32_t*>(f_lo + ch);
+        uint32_t* fh = reinterpret_cast<uint32_t*>(f_lo + kHi + ch);
+        const uint32_t xl = *fl, xh = *fh;
+        const uint32_t yl = *reinterpret_cast<const uint32_t*>(b_lo + ch);
+        const uint32_t yh = *reinterpret_cast<const uint32_t*>(b_lo + kHi + ch);
+        const float l0 = fmaf(lo_f(xl), klo.x, fmaf(-lo_f(yl), klo.y, -(o[jj][0] * klo.z)));
+        const float l1 = fmaf(hi_f(xl), klo.x, fmaf(-hi_f(yl), klo.y, -(o[jj][1] * klo.z)));
+        const float h0 = fmaf(lo_f(xh), khi.x, fmaf(-lo_f(yh), khi.y, -(o[jj][2] * khi.z)));
+        const float h1 = fmaf(hi_f(xh), khi.x, fmaf(-hi_f(yh), khi.y, -(o[jj][3] * khi.z)));
+        *fl = klo.w != 0.f ? 0u : pack2(l0, l1);
+        *fh = khi.w != 0.f ? 0u : pack2(h0, h1);
       }
     }
-    sx_wait<0>();
     __syncwarp();
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int r = 2 * j + r_half;
       if (i0 + r / G >= sp.keep) continue;
-      const uint4 f4 = *reinterpret_cast<const uint4*>(fullS + r * kSxRowBytes + c * 16);
-      const uint4 b4 = *reinterpret_cast<const uint4*>(bandS + r * kSxRowBytes + c * 16);
-      const float4 k4 = scal[r];
-      const float* sk = reinterpret_cast<const float*>(regA) + r * kSxSinkStride + c * 8;
-      const float4 k0 = *reinterpret_cast<const float4*>(sk);
-      const float4 k1 = *reinterpret_cast<const float4*>(sk + 4);
-      const float sink[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
-      const uint32_t x[4] = {f4.x, f4.y, f4.z, f4.w};
-      const uint32_t y[4] = {b4.x, b4.y, b4.z, b4.w};
-      uint32_t w[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float r0 = fmaf(lo_f(x[i]), k4.x, fmaf(-lo_f(y[i]), k4.y, -(sink[2 * i] * k4.z)));
-        const float r1 = fmaf(hi_f(x[i]), k4.x, fmaf(-hi_f(y[i]), k4.y, -(sink[2 * i + 1] * k4.z)));
-        w[i] = k4.w != 0.f ? 0u : pack2(r0, r1);
-      }
+      const uint4 w4 = *reinterpret_cast<const uint4*>(fullS + r * kSxRowBytes + ((c ^ (r & 7)) << 4));
       int d = dbase + r / G;
       if (d >= p.M) d -= p.M;
-      st_stream16(ac + static_cast<size_t>(d) * row_bf16 + head_base + (r % G) * kSxRowBytes,
-                  make_uint4(w[0], w[1], w[2], w[3]));
+      st_stream16(ac + static_cast<size_t>(d) * row_bf16 + head_base + (r % G) * kSxRowBytes, w4);
     }
     __syncwarp();   // the next tile's staging overwrites what other lanes just read
   }
