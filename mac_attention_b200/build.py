@@ -17,7 +17,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libmac_b200.so"
 SOURCES = ["mac_b200_api.cu", "mac_b200_prefill.cu", "mac_b200_decode.cu", "mac_b200_rope.cu",
-           "mac_b200_downdate.cu", "mac_b200_prefill_build.cu"]
+           "mac_b200_downdate.cu", "mac_b200_prefill_build.cu", "mac_b200_prefill_sink_tc.cu"]
 HEADERS = [CSRC / "mac_b200_common.h", CSRC / "mac_b200_state_math.cuh",
            PKG.parent / "include" / "mac_b200.h"]
 

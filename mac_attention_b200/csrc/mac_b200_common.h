@@ -28,6 +28,14 @@ inline int cuda_fail(cudaError_t err, const char* what) {
 // the current device (the caller has synchronised the device).
 int take_prefill_build_status(unsigned* bits);
 
+// The same for the tensor-memory variant of the sink-exclusive build.
+int take_prefill_sink_tc_status(unsigned* bits);
+
+// Sink-exclusive prefill build on tcgen05 / tensor memory (validated arguments); sets
+// *launched when it ran, leaves it false when this step has to take the mma.sync kernel.
+int launch_prefill_sink_exclusive_tc(const ::MacB200PrefillBuildArgs& a, int sms, cudaStream_t stream,
+                                     bool* launched);
+
 // Multiprocessor count of a device, looked up once per device.
 int device_sm_count(int device);
 

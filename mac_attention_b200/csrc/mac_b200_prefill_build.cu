@@ -647,7 +647,9 @@ int take_prefill_build_status(unsigned* bits) {
     const unsigned zero = 0;
     MAC_CUDA(cudaMemcpyToSymbol(g_build_status, &zero, sizeof(zero)));
   }
-  *bits = v;
+  unsigned tc = 0;
+  if (const int rc = take_prefill_sink_tc_status(&tc)) return rc;
+  *bits = v | tc;
   return MAC_B200_OK;
 }
 
@@ -711,6 +713,21 @@ extern "C" int mac_b200_prefill_downdate_update_cache(const MacB200PrefillBuildA
     MAC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   kSxSmemBytes));
     const int sms = device_sm_count(device);
+    // MAC_B200_SINK_KERNEL=tcgen05 takes the tensor-memory kernel (mac_b200_prefill_sink_tc.cu)
+    if (const char* k = std::getenv("MAC_B200_SINK_KERNEL")) {
+      if (k[0] == 't') {
+        bool launched = false;
+        if (const int rc = launch_prefill_sink_exclusive_tc(a, sms, stream, &launched)) return rc;
+        if (launched) {
+          if (!p.request_length_by_batch || a.ready) {
+            prefill_build_finish_kernel<<<(p.B + 127) / 128, 128, 0, stream>>>(a);
+            MAC_CUDA(cudaGetLastError());
+            g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+          }
+          return MAC_B200_OK;
+        }
+      }
+    }
     const int TG = 16 / G;
     const int max_tiles = ((p.M < 1 ? 1 : p.M) + TG - 1) / TG;
     const int pairs = p.B * a.Hkv;

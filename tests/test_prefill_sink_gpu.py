@@ -23,6 +23,14 @@ from prefill_cases import SPECS, make_prompts as _prompts, run_build as _build
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True, params=["mma", "tcgen05"])
+def sink_kernel(request, monkeypatch):
+    """Every test of this file runs on both implementations of the sink-exclusive build: the
+    mma.sync kernel (default) and the tcgen05 / tensor-memory kernel."""
+    monkeypatch.setenv("MAC_B200_SINK_KERNEL", request.param)
+    return request.param
+
+
 @pytest.mark.parametrize("spec", SPECS, ids=["gqa4_chunked", "gqa8_wrap", "mha_odd_sink", "gqa16"])
 def test_sink_exclusive_build_matches_oracle_and_direct_attention(spec):
     ext = load_mac_prefill_update_cache_extension()
