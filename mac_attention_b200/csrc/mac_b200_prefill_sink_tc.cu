@@ -104,10 +104,10 @@ __device__ __forceinline__ bool tc_mbar_try_wait(uint32_t bar, uint32_t parity) 
 __device__ __forceinline__ bool tc_mbar_wait(uint32_t bar, uint32_t parity) {
   if (tc_mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = tc_now_ns();
-  while (!tc_mbar_try_wait(bar, parity)) {
-    if (tc_now_ns() - t0 > kTcWaitLimitNs) return false;
+  for (unsigned spins = 1;; ++spins) {
+    if (tc_mbar_try_wait(bar, parity)) return true;   // each try may itself block for a while
+    if ((spins & 63u) == 0u && tc_now_ns() - t0 > kTcWaitLimitNs) return false;
   }
-  return true;
 }
 // named barrier of one group (ids 1 and 2; 0 is __syncthreads)
 __device__ __forceinline__ void tc_group_sync(int g) {
@@ -264,7 +264,9 @@ prefill_sink_exclusive_tc_kernel(const MacB200PrefillBuildArgs a,
     const char* vb = static_cast<const char*>(a.v_buffer) + static_cast<int64_t>(kh) * kTcRowBytes;
     const int64_t tok_stride = static_cast<int64_t>(Hkv) * kTcRowBytes;
     for (int task = tid; task < kTcMaxF * 16; task += kTcThreads) {
-      const int j = task >> 4, c = task & 15;   // key, 16-byte chunk of its row (8 dims)
+      const int c = task >> 7, j = task & 127;  // 16-byte chunk (8 dims) of the row of key j: keys
+                                                // vary across the lanes, so the transposing
+                                                // 2-byte stores of a warp land in a few words
       int64_t tok = -1;
       if (j < F && j < a.req_to_token_stride) tok = table[j];
       const bool ok = tok >= 0 && tok < a.kv_tokens;
@@ -341,9 +343,27 @@ prefill_sink_exclusive_tc_kernel(const MacB200PrefillBuildArgs a,
     tc_tma_load_3d(opnd_u32, &q_map, 0, kh * G, src_tok, bar_q);
     tc_tma_load_3d(opnd_u32 + kTcAtomBytes, &q_map, 64, kh * G, src_tok, bar_q);
   };
+  // The q_pre, full and band rows of a tile go through registers (there is no shared memory left
+  // to stage them in); asked for in one burst they stall at issue behind DRAM.  So they are
+  // pulled into L2 a tile ahead by the copy engine: one prefetch per (tensor, token) of the G
+  // heads' contiguous rows, no registers, no shared memory.
+  auto prefetch_rows = [&](int tile_p) {
+    if (tile_p >= ntiles) return;
+    const int ip = tile_p * TG;
+    for (int t = r; t < 3 * TG; t += kTcGroupThreads) {
+      const int which = t / TG, tk = t - which * TG;
+      if (ip + tk >= sp.keep) continue;
+      const char* base = which == 0 ? qpre : which == 1 ? fsrc : bsrc;
+      const char* src = base + static_cast<size_t>(sp.base_off + sp.start + ip + tk) * row_bf16 +
+                        static_cast<size_t>(kh * G) * kTcRowBytes;
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(G * kTcRowBytes)
+                   : "memory");
+    }
+  };
   const int tile_step = gridDim.x * kTcGroups;
   const int tile0 = blockIdx.x * kTcGroups + g;
   if (tile0 < ntiles && r == 0) request_q_rows(tile0);
+  prefetch_rows(tile0);
 
   for (int tile = tile0; tile < ntiles; tile += tile_step) {
     if (*reinterpret_cast<volatile uint32_t*>(abort_word) != 0u) break;
@@ -351,6 +371,7 @@ prefill_sink_exclusive_tc_kernel(const MacB200PrefillBuildArgs a,
     const int src_tok0 = sp.base_off + sp.start + i0;      // source row of the tile's first token
     const int nrows_tok = sp.keep - i0;                    // tokens of the tile that exist (may exceed TG)
     bool good = true;
+    prefetch_rows(tile + tile_step);
 
     // q_pre rows go to the ring as they are (the NaN stamp of q_post_cache too): rows
     // blk*64 + u*8 + r/16, loaded before a wait on a product and stored after it
@@ -533,7 +554,9 @@ prefill_sink_exclusive_tc_kernel(const MacB200PrefillBuildArgs a,
           for (int c = 0; c < 8; ++c) {           // 16-byte chunks of 4 floats, swizzled with the row
             uint4 v = make_uint4(ou[c * 4], ou[c * 4 + 1], ou[c * 4 + 2], ou[c * 4 + 3]);
             if (nk2 == 0) v = make_uint4(0u, 0u, 0u, 0u);   // no sink key: no second product
-            *reinterpret_cast<uint4*>(srow + (((q * 8 + c) ^ (r & 7)) << 4)) = v;
+            const int k = q * 8 + c;              // chunk k sits at position k/2 + 16 * (k odd): the
+                                                  // pass reads neighbouring positions per quarter-warp
+            *reinterpret_cast<uint4*>(srow + ((((k >> 1) + ((k & 1) << 4)) ^ (r & 7)) << 4)) = v;
           }
         }
       }
@@ -545,8 +568,8 @@ prefill_sink_exclusive_tc_kernel(const MacB200PrefillBuildArgs a,
         const int rr = half * 64 + lr;
         const float4 k4 = fac[rr];
         const uint8_t* srow = stage + lr * 512;
-        const float4 k0 = *reinterpret_cast<const float4*>(srow + (((2 * c16) ^ (lr & 7)) << 4));
-        const float4 k1 = *reinterpret_cast<const float4*>(srow + (((2 * c16 + 1) ^ (lr & 7)) << 4));
+        const float4 k0 = *reinterpret_cast<const float4*>(srow + ((c16 ^ (lr & 7)) << 4));
+        const float4 k1 = *reinterpret_cast<const float4*>(srow + (((16 + c16) ^ (lr & 7)) << 4));
         const float sink[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
         const uint32_t x[4] = {f4[half][it].x, f4[half][it].y, f4[half][it].z, f4[half][it].w};
         const uint32_t y[4] = {b4[half][it].x, b4[half][it].y, b4[half][it].z, b4[half][it].w};
