@@ -1215,7 +1215,7 @@ def run_config4(args):
     print(json.dumps(rows[-1]), flush=True)
     # sink-exclusive rows (F = 128): the same pass plus each row's attention over
     # the sink tokens, computed in the kernel from q_post and the paged K/V
-    Fs = 128
+    Fs = int(os.environ.get("MAC_BENCH_SINK_F", "128"))   # sink size of the sink-exclusive leg
     q_post_rows = torch.empty_like(src_q)
     for r0 in range(0, q_post_rows.shape[0], 1 << 16):
         q_post_rows[r0:r0 + (1 << 16)].normal_()
@@ -1234,7 +1234,7 @@ def run_config4(args):
     xms, _ = time_graph(build_sink_exclusive, args.steps, args.warmup)
     xbytes = bbytes + batch * keep * H * 256
     xflops = 4.0 * batch * keep * H * Fs * D
-    rows.append(dict(kind="prefill_downdate_update_cache (sink-exclusive, F=128)", batch=batch,
+    rows.append(dict(kind=f"prefill_downdate_update_cache (sink-exclusive, F={Fs})", batch=batch,
                      prompt_len=plen, capacity=M, us=xms * 1e3,
                      alg_gbs=xbytes / (xms * 1e-3) / 1e9, alg_bytes=xbytes,
                      sink_attention_tflops=xflops / (xms * 1e-3) / 1e12))

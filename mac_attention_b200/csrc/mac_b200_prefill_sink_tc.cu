@@ -10,36 +10,37 @@
 // which stamps such rows unmatchable instead
 // (attention/src/mac_attention/integrations/sglang/flashinfer_hooks.py:2205-2215).
 //
-// Why a second implementation: with mma.sync the kernel is bound by issue
-// slots (a 16-row tile costs a warp ~2400 instructions, two thirds of them
-// operand movement and tensor-core issue), not by HBM.  Here one thread issues
-// the two products of a 128-row tile, the copy engine stages the operand, and
-// the 128 threads of a group own one row each for the softmax, so the warps
-// issue only the arithmetic that is inherent to the rows.
+// Why a second implementation: the products of a tile leave the warps altogether (one thread
+// issues them, the copy engine stages every operand and every row), which takes a fifth of the
+// instruction stream away; what is left -- softmax, row factors, element-wise combine -- is
+// inherent to the rows.
 //
-// CTA = (slice of a request's ring rows, one KV head), 256 threads = two groups
-// of four warps.  The sink K (key-major) and V (transposed: dim-major) of the
-// (request, KV head) are staged once per CTA in the 128-byte-swizzled operand
-// layout.  A group works through 128-row tiles (128/G tokens x the G query
-// heads of the KV head) on its own, so the two groups overlap each other's
-// waits:
-//   1. one thread requests the tile's q_post rows: two bulk tensor copies
-//      (dims 0..63 and 64..127) into the operand layout, completion on an
-//      mbarrier;
-//   2. the same thread issues S = Q K^T (eight 128x128x16 products) into the
-//      group's tensor-memory columns and commits to an mbarrier;
-//   3. every thread reads its own row of S from tensor memory, takes the softmax
-//      over the F sink keys in the log2 domain, writes the bf16 weights over
-//      the dead q_post rows as the next operand;
-//   4. one thread issues O = P V; meanwhile every thread folds both downdates
-//      of its row into three factors (state = full*A - band*B - sink*C), and
-//      the group copies the tile's q_pre rows to the ring;
-//   5. every thread reads its row of O, parks it in shared memory, and the
-//      group streams the rows to the ring with coalesced 16-byte accesses
-//      (full and band rows straight from global memory).
-// Every wait on a copy or a product is bounded by wall time; on expiry the CTA
-// records MAC_B200_STATUS_COPY_TIMEOUT, leaves its tile loop at the next common
-// point, frees its tensor memory and returns.
+// CTA = (slice of a request's ring rows, one KV head), 256 threads, one CTA per SM.  The sink K
+// (key-major) and V (transposed: dim-major) of the (request, KV head) are staged once per CTA
+// in the 128-byte-swizzled operand layout.  The CTA works through 128-row tiles (128/G tokens x
+// the G query heads of the KV head); two threads share a row, each taking 64 of its columns
+// (both reach the row's tensor-memory lane: warps w and w + 4 address the same lanes):
+//   1. the tile's q_post, full and band rows arrive by bulk tensor copies (3-D boxes of 64 dims
+//      x G heads x 128/G tokens, 128-byte swizzle, completion on mbarriers): q_post two tiles
+//      ahead into a two-stage operand buffer, full / band one tile ahead; the rows that come
+//      through registers (q_pre) are pulled into L2 two tiles ahead;
+//   2. S = Q K^T was issued while the previous tile was being finished (eight
+//      tcgen05.mma 128x128x16 products into one of two score stages in tensor memory);
+//   3. every thread reads its 64 score columns with tcgen05.ld, the two halves of a row exchange
+//      their maxima through shared memory, and the bf16 weights go over the dead q_post rows as
+//      the next operand (64 keys = one operand atom per thread half);
+//   4. one thread issues O = P V and, right after, the next tile's S = Q K^T; meanwhile the
+//      q_pre rows are stored to the ring and one thread per row folds both downdates into three
+//      factors (state = full*A - band*B - sink*C);
+//   5. every thread reads its 64 columns of O and combines them with its half of the staged full
+//      and band rows IN PLACE (the staged rows lie in the operand layout: a thread's 16-byte
+//      chunks are swizzled with its row, so row-per-thread access is free of bank conflicts and
+//      no transposition through shared memory is needed);
+//   6. the finished rows go to the ring in whole 256-byte rows, and the next tile's full / band
+//      rows are requested.
+// Every wait on a copy or a product is bounded by wall time; on expiry the CTA records
+// MAC_B200_STATUS_COPY_TIMEOUT, leaves its tile loop at the next common point, frees its
+// tensor memory and returns.
 #include <cuda.h>
 
 #include <cstdlib>
@@ -53,20 +54,19 @@ namespace {
 constexpr int kTcRowBytes = 256;                 // D = 128 bf16
 constexpr int kTcTileRows = 128;                 // MMA M
 constexpr int kTcMaxF = 128;                     // MMA N of the first product
-constexpr int kTcGroups = 2;
-constexpr int kTcGroupThreads = 128;
-constexpr int kTcThreads = kTcGroups * kTcGroupThreads;
+constexpr int kTcThreads = 256;                  // two threads per row: each takes 64 columns
 constexpr int kTcAtomBytes = 128 * 128;          // 128 rows x 64 bf16, swizzled: one operand atom
 constexpr int kTcOperandBytes = 2 * kTcAtomBytes;
-constexpr int kTcStageBytes = kTcTileRows * 64 * 4;   // 64 fp32 columns of a tile's sink state
 constexpr int kTcSmemK = 0;
 constexpr int kTcSmemVt = kTcSmemK + kTcOperandBytes;
-constexpr int kTcSmemGroup = kTcSmemVt + kTcOperandBytes;           // per group: operand + staging
-constexpr int kTcGroupBytes = kTcOperandBytes + kTcStageBytes;
-constexpr int kTcSmemFac = kTcSmemGroup + kTcGroups * kTcGroupBytes;  // float4 per row and group
-constexpr int kTcSmemBars = kTcSmemFac + kTcGroups * kTcTileRows * 16;
+constexpr int kTcSmemQ = kTcSmemVt + kTcOperandBytes;               // two stages of q_post rows / weights
+constexpr int kTcSmemFull = kTcSmemQ + 2 * kTcOperandBytes;         // full rows, then the finished rows
+constexpr int kTcSmemBand = kTcSmemFull + kTcOperandBytes;
+constexpr int kTcSmemFac = kTcSmemBand + kTcOperandBytes;           // float4 per row
+constexpr int kTcSmemXch = kTcSmemFac + kTcTileRows * 16;           // float2 per row
+constexpr int kTcSmemBars = kTcSmemXch + kTcTileRows * 8;
 constexpr int kTcSmemBytes = kTcSmemBars + 128 + 1024;   // + room to align the base to 1024 bytes
-constexpr int kTcTmemCols = 512;                 // per group: 128 columns of S + 128 of O
+constexpr int kTcTmemCols = 512;                 // two stages of S (128 columns each) and O (128)
 constexpr unsigned long long kTcWaitLimitNs = 2000000000ull;
 
 // instruction descriptor of both products: bf16 x bf16 -> fp32, both operands K-major, M 128, N 128
@@ -108,10 +108,6 @@ __device__ __forceinline__ bool tc_mbar_wait(uint32_t bar, uint32_t parity) {
     if (tc_mbar_try_wait(bar, parity)) return true;   // each try may itself block for a while
     if ((spins & 63u) == 0u && tc_now_ns() - t0 > kTcWaitLimitNs) return false;
   }
-}
-// named barrier of one group (ids 1 and 2; 0 is __syncthreads)
-__device__ __forceinline__ void tc_group_sync(int g) {
-  asm volatile("bar.sync %0, %1;" ::"r"(g + 1), "n"(kTcGroupThreads) : "memory");
 }
 __device__ __forceinline__ void tc_fence_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -217,7 +213,9 @@ __device__ __forceinline__ TcRowSpan tc_row_span(const MacB200PrefillArgs& p, in
 template <int G>
 __global__ void __launch_bounds__(kTcThreads, 1)
 prefill_sink_exclusive_tc_kernel(const MacB200PrefillBuildArgs a,
-                                 const __grid_constant__ CUtensorMap q_map) {
+                                 const __grid_constant__ CUtensorMap q_map,
+                                 const __grid_constant__ CUtensorMap f_map,
+                                 const __grid_constant__ CUtensorMap b_map) {
   extern __shared__ __align__(1024) uint8_t tc_smem_raw[];
   // the swizzled operand layout repeats every 1024 bytes of the shared-memory ADDRESS
   uint8_t* tc_smem = tc_smem_raw + ((1024u - (tc_smem_u32(tc_smem_raw) & 1023u)) & 1023u);
@@ -233,12 +231,15 @@ prefill_sink_exclusive_tc_kernel(const MacB200PrefillBuildArgs a,
   const int kh = blockIdx.y;
   const int F = a.front_sink_tokens;
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int g = tid >> 7;                            // group
-  const int r = tid & (kTcGroupThreads - 1);         // row of the tile this thread owns
+  const int r = tid & 127;                           // row of the tile (= tensor-memory lane)
+  const int h = tid >> 7;                            // column half this thread works on
   const uint32_t smem0 = tc_smem_u32(tc_smem);
   uint32_t* tmem_word = reinterpret_cast<uint32_t*>(tc_smem + kTcSmemBars + 96);
-  uint32_t* abort_word = reinterpret_cast<uint32_t*>(tc_smem + kTcSmemBars + 100) + g;   // per group
-  const uint32_t bar_q = smem0 + kTcSmemBars + g * 32, bar_s = bar_q + 8, bar_o = bar_q + 16;
+  uint32_t* abort_word = reinterpret_cast<uint32_t*>(tc_smem + kTcSmemBars + 100);
+  const uint32_t bar_q0 = smem0 + kTcSmemBars;       // q_post rows of stage 0 / 1: +0, +8
+  const uint32_t bar_s0 = bar_q0 + 16;               // first product into S[0] / S[1]: +16, +24
+  const uint32_t bar_o = bar_q0 + 32;                // second product
+  const uint32_t bar_fb = bar_q0 + 40;               // full and band rows
 
   // ---- tensor memory, barriers
   if (warp == 0) {
@@ -249,10 +250,8 @@ prefill_sink_exclusive_tc_kernel(const MacB200PrefillBuildArgs a,
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   if (tid == 0) {
-    for (int i = 0; i < kTcGroups; ++i)
-      for (int k = 0; k < 3; ++k) tc_mbar_init(smem0 + kTcSmemBars + i * 32 + k * 8, 1);
-    reinterpret_cast<uint32_t*>(tc_smem + kTcSmemBars + 100)[0] = 0u;
-    reinterpret_cast<uint32_t*>(tc_smem + kTcSmemBars + 100)[1] = 0u;
+    for (int k = 0; k < 6; ++k) tc_mbar_init(bar_q0 + k * 8, 1);
+    *abort_word = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
 
@@ -296,14 +295,13 @@ prefill_sink_exclusive_tc_kernel(const MacB200PrefillBuildArgs a,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_word;
-  const uint32_t tmem_s = tmem_base + g * 256, tmem_o = tmem_s + 128;
   const uint32_t tmem_lane = static_cast<uint32_t>((warp & 3) * 32) << 16;
+  const uint32_t tmem_o = tmem_base + 256;           // S[0] at +0, S[1] at +128
 
-  uint8_t* opnd = tc_smem + kTcSmemGroup + g * kTcGroupBytes;   // q_post rows, then the weights
-  uint8_t* stage = opnd + kTcOperandBytes;                      // 64 fp32 columns of the sink state
-  float4* fac = reinterpret_cast<float4*>(tc_smem + kTcSmemFac) + g * kTcTileRows;
-  const uint32_t opnd_u32 = tc_smem_u32(opnd);
-  const uint64_t desc_q = tc_operand_desc(opnd_u32);
+  uint8_t* fullS = tc_smem + kTcSmemFull;
+  uint8_t* bandS = tc_smem + kTcSmemBand;
+  float4* fac = reinterpret_cast<float4*>(tc_smem + kTcSmemFac);
+  float2* xch = reinterpret_cast<float2*>(tc_smem + kTcSmemXch);   // per row: the halves' maxima, then sums
   const uint64_t desc_k = tc_operand_desc(smem0 + kTcSmemK);
   const uint64_t desc_vt = tc_operand_desc(smem0 + kTcSmemVt);
 
@@ -327,137 +325,148 @@ prefill_sink_exclusive_tc_kernel(const MacB200PrefillBuildArgs a,
   const uint4 nan4 = make_uint4(nanw, nanw, nanw, nanw);
   const int nk2 = (F + 15) >> 4;                     // k-steps of the second product
   const int tok_r = r / G, head_r = kh * G + (r % G);   // token of the tile and head of this thread's row
-  uint32_t phase = 0;
 
   // what this thread moves in the coalesced passes: 16-byte piece `c16` of the 256-byte rows
-  // it*8 + r/16
-  const int c16 = r & 15, row16 = r >> 4;
-  auto tok16 = [&](int rr) { return rr / G; };
+  // it*16 + tid/16
+  const int c16 = tid & 15, row16 = tid >> 4;
   auto head_off16 = [&](int rr) {
     return static_cast<size_t>(kh * G + rr % G) * kTcRowBytes + c16 * 16;
   };
-
-  auto request_q_rows = [&](int tile_q) {   // one thread: the tile's q_post rows -> operand layout
-    const int src_tok = sp.base_off + sp.start + tile_q * TG;
-    tc_mbar_expect_tx(bar_q, kTcOperandBytes);
-    tc_tma_load_3d(opnd_u32, &q_map, 0, kh * G, src_tok, bar_q);
-    tc_tma_load_3d(opnd_u32 + kTcAtomBytes, &q_map, 64, kh * G, src_tok, bar_q);
+  auto src_tok_of = [&](int tile_x) { return sp.base_off + sp.start + tile_x * TG; };
+  // The copy-engine requests and the products are issued by single threads; each costs its
+  // thread a few hundred cycles, and every other thread meets it at the next barrier.  So the
+  // duties are spread over threads of different warps: thread 0 arms the barriers and issues
+  // the second product, thread 128 issues the next tile's first product, and the boxes of a
+  // request are issued one per warp.
+  auto request_q_rows = [&](int tile_x, int stage) {   // threads 0 and 128: q_post rows -> operand layout
+    const uint32_t dst = smem0 + kTcSmemQ + stage * kTcOperandBytes, bar = bar_q0 + stage * 8;
+    if (tid == 0) {
+      tc_mbar_expect_tx(bar, kTcOperandBytes);
+      tc_tma_load_3d(dst, &q_map, 0, kh * G, src_tok_of(tile_x), bar);
+    } else if (tid == 128) {
+      tc_tma_load_3d(dst + kTcAtomBytes, &q_map, 64, kh * G, src_tok_of(tile_x), bar);
+    }
   };
-  // The q_pre, full and band rows of a tile go through registers (there is no shared memory left
-  // to stage them in); asked for in one burst they stall at issue behind DRAM.  So they are
-  // pulled into L2 a tile ahead by the copy engine: one prefetch per (tensor, token) of the G
-  // heads' contiguous rows, no registers, no shared memory.
-  auto prefetch_rows = [&](int tile_p) {
-    if (tile_p >= ntiles) return;
-    const int ip = tile_p * TG;
-    for (int t = r; t < 3 * TG; t += kTcGroupThreads) {
+  auto request_state_rows = [&](int tile_x) {          // threads 0, 32, 64, 96: full and band rows
+    if (tid == 0) {
+      tc_mbar_expect_tx(bar_fb, 2 * kTcOperandBytes);
+      tc_tma_load_3d(smem0 + kTcSmemFull, &f_map, 0, kh * G, src_tok_of(tile_x), bar_fb);
+    } else if (tid == 32) {
+      tc_tma_load_3d(smem0 + kTcSmemFull + kTcAtomBytes, &f_map, 64, kh * G, src_tok_of(tile_x), bar_fb);
+    } else if (tid == 64) {
+      tc_tma_load_3d(smem0 + kTcSmemBand, &b_map, 0, kh * G, src_tok_of(tile_x), bar_fb);
+    } else if (tid == 96) {
+      tc_tma_load_3d(smem0 + kTcSmemBand + kTcAtomBytes, &b_map, 64, kh * G, src_tok_of(tile_x), bar_fb);
+    }
+  };
+  auto issue_first_product = [&](int stage) {          // one thread: S[stage] = Q[stage] K^T
+    const uint64_t desc_q = tc_operand_desc(smem0 + kTcSmemQ + stage * kTcOperandBytes);
+    tc_fence_after_sync();
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const uint64_t off = static_cast<uint64_t>(((k >> 2) * kTcAtomBytes + (k & 3) * 32) >> 4);
+      tc_mma(tmem_base + stage * 128, desc_q + off, desc_k + off, k > 0 ? 1u : 0u);
+    }
+    tc_commit(bar_s0 + stage * 8);
+  };
+  // Rows that come through registers (q_pre) or the copy engine (q_post, full, band) are pulled
+  // into L2 two tiles ahead: one prefetch per (tensor, token) of the G heads' contiguous rows.
+  auto prefetch_rows = [&](int tile_x) {
+    if (tile_x >= ntiles) return;
+    const int ip = tile_x * TG;
+    for (int t = tid; t < 3 * TG; t += kTcThreads) {
       const int which = t / TG, tk = t - which * TG;
       if (ip + tk >= sp.keep) continue;
       const char* base = which == 0 ? qpre : which == 1 ? fsrc : bsrc;
-      const char* src = base + static_cast<size_t>(sp.base_off + sp.start + ip + tk) * row_bf16 +
+      const char* src = base + static_cast<size_t>(src_tok_of(tile_x) + tk) * row_bf16 +
                         static_cast<size_t>(kh * G) * kTcRowBytes;
       asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(G * kTcRowBytes)
                    : "memory");
     }
   };
-  const int tile_step = gridDim.x * kTcGroups;
-  const int tile0 = blockIdx.x * kTcGroups + g;
-  if (tile0 < ntiles && r == 0) request_q_rows(tile0);
-  prefetch_rows(tile0);
 
-  for (int tile = tile0; tile < ntiles; tile += tile_step) {
+  const int tile_step = gridDim.x;
+  const int tile0 = blockIdx.x;
+  bool good = true;
+  if (tile0 < ntiles) {
+    prefetch_rows(tile0);
+    prefetch_rows(tile0 + tile_step);
+    request_q_rows(tile0, 0);
+    if (tile0 + tile_step < ntiles) request_q_rows(tile0 + tile_step, 1);
+    request_state_rows(tile0);
+    if (tid == 0) {
+      good &= tc_mbar_wait(bar_q0, 0);
+      issue_first_product(0);
+    }
+    __syncwarp();
+  }
+
+  int k = 0;
+  for (int tile = tile0; tile < ntiles; tile += tile_step, ++k) {
     if (*reinterpret_cast<volatile uint32_t*>(abort_word) != 0u) break;
+    const int s = k & 1;                                   // stage of this tile's q_post rows and scores
+    const uint32_t ph2 = static_cast<uint32_t>(k >> 1) & 1u, ph1 = static_cast<uint32_t>(k) & 1u;
     const int i0 = tile * TG;
-    const int src_tok0 = sp.base_off + sp.start + i0;      // source row of the tile's first token
+    const int src_tok0 = src_tok_of(tile);                 // source row of the tile's first token
     const int nrows_tok = sp.keep - i0;                    // tokens of the tile that exist (may exceed TG)
-    bool good = true;
-    prefetch_rows(tile + tile_step);
+    const bool has_next = tile + tile_step < ntiles;
+    uint8_t* opnd = tc_smem + kTcSmemQ + s * kTcOperandBytes;   // q_post rows, then the weights
+    prefetch_rows(tile + 2 * tile_step);
 
-    // q_pre rows go to the ring as they are (the NaN stamp of q_post_cache too): rows
-    // blk*64 + u*8 + r/16, loaded before a wait on a product and stored after it
-    uint4 qv[8];
-    auto q_pre_load = [&](int blk) {
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int rr = blk * 64 + u * 8 + row16;
-        if (tok16(rr) < nrows_tok)
-          qv[u] = ld_stream16(qpre + static_cast<size_t>(src_tok0 + tok16(rr)) * row_bf16 + head_off16(rr));
-      }
-    };
-    auto q_pre_store = [&](int blk) {
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int rr = blk * 64 + u * 8 + row16;
-        if (tok16(rr) < nrows_tok) {
-          int d = sp.base_dest + i0 + tok16(rr);
-          if (d >= p.M) d -= p.M;
-          const size_t doff = static_cast<size_t>(d) * row_bf16 + head_off16(rr);
-          st_stream16(qc + doff, qv[u]);
-          if (pc) st_stream16(pc + doff, nan4);
-        }
-      }
-    };
-
-    // ---- 1. this row's LSEs (needed after the products); the q_post rows were requested while
-    // the previous tile was written out
+    // ---- 1. this row's LSEs; the q_pre rows on their way to the ring (stored after the softmax)
     const bool row_ok = tok_r < nrows_tok;
     float l_full = 0.f, l_band = 0.f;
-    if (row_ok) {
+    if (row_ok && h == 0) {
       const size_t li = static_cast<size_t>(src_tok0 + tok_r) * H + head_r;
       l_full = load_lse(p.src_lse, a.full_lse_dtype, li);
       l_band = load_lse(a.band_lse, a.band_lse_dtype, li);
     }
-    good &= tc_mbar_wait(bar_q, phase);
-
-    // ---- 2. S = Q K^T
-    if (r == 0) {
-      tc_fence_after_sync();
+    uint4 qv[8];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const uint64_t off = static_cast<uint64_t>(((k >> 2) * kTcAtomBytes + (k & 3) * 32) >> 4);
-        tc_mma(tmem_s, desc_q + off, desc_k + off, k > 0 ? 1u : 0u);
-      }
-      tc_commit(bar_s);
+    for (int u = 0; u < 8; ++u) {
+      const int rr = u * 16 + row16;
+      if (rr / G < nrows_tok)
+        qv[u] = ld_stream16(qpre + static_cast<size_t>(src_tok0 + rr / G) * row_bf16 + head_off16(rr));
     }
-    __syncwarp();
-    q_pre_load(0);
-    good &= tc_mbar_wait(bar_s, phase);
+
+    // ---- 2. softmax of this thread's half of its row (64 of the 128 score columns)
+    good &= tc_mbar_wait(bar_s0 + s * 8, ph2);
     tc_fence_after_sync();
-    q_pre_store(0);
-    // ---- 3. softmax of this thread's row over the F sink keys, weights -> operand layout
-    float ms = 0.f, sum = 0.f;
+    float ms, psum;
     {
-      float m = -INFINITY;
-      uint32_t su[4][32];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) tc_ld32_nowait(tmem_s + tmem_lane + q * 32, su[q]);
+      uint32_t su[2][32];
+      tc_ld32_nowait(tmem_base + s * 128 + tmem_lane + h * 64, su[0]);
+      tc_ld32_nowait(tmem_base + s * 128 + tmem_lane + h * 64 + 32, su[1]);
       tc_ld_wait();
-      float sv[4][32];
+      float sv[2][32];
 #pragma unroll
-      for (int q = 0; q < 4; ++q)
+      for (int q = 0; q < 2; ++q)
 #pragma unroll
         for (int i = 0; i < 32; ++i) sv[q][i] = __uint_as_float(su[q][i]);
       if (F < kTcMaxF) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
+        for (int q = 0; q < 2; ++q)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (q * 32 + i >= F) sv[q][i] = -INFINITY;
+            if (h * 64 + q * 32 + i >= F) sv[q][i] = -INFINITY;
       }
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      for (int q = 0; q < 2; ++q)
 #pragma unroll
         for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], sv[q][i]);
-        m = fmaxf(m, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
-      }
-      ms = m == -INFINITY ? 0.f : m * scale_log2;   // -inf only when there is no sink key at all
-      uint8_t* prow = opnd + r * 128;
+      const float m_half = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      reinterpret_cast<float*>(&xch[r])[h] = m_half;
+      __syncthreads();                                  // sync 1: both halves' maxima are there
+      const float2 mm = xch[r];
+      const float m = fmaxf(mm.x, mm.y);
+      ms = m == -INFINITY ? 0.f : m * scale_log2;       // -inf only when there is no sink key at all
+      uint8_t* prow = opnd + h * kTcAtomBytes + r * 128;   // keys 64h .. 64h+63 are operand atom h
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
+      for (int q = 0; q < 2; ++q) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {           // 8 keys = one 16-byte chunk of weights
+        for (int c = 0; c < 4; ++c) {                   // 8 keys = one 16-byte chunk of weights
           uint32_t w[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -466,51 +475,47 @@ prefill_sink_exclusive_tc_kernel(const MacB200PrefillBuildArgs a,
             sum4[e] += e0 + e1;
             w[e] = pack2(e0, e1);
           }
-          const int key_chunk = q * 4 + c;        // chunk of 8 keys: atom = chunk / 8
-          *reinterpret_cast<uint4*>(prow + (key_chunk >> 3) * kTcAtomBytes +
-                                    (((key_chunk & 7) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(prow + (((q * 4 + c) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
-      sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      psum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
     }
     tc_fence_async_smem();
     tc_fence_before_sync();
-    tc_group_sync(g);
+    __syncthreads();                                    // sync 2: weights written, maxima consumed
+    reinterpret_cast<float*>(&xch[r])[h] = psum;        // read after sync 3
 
-    // ---- 4. O = P V; meanwhile the full and band rows of the first 64 rows are requested, the
-    // other q_pre rows copied and the row factors worked out
-    if (r == 0) {
+    // ---- 3. O = P V, and at once the next tile's S = Q K^T; meanwhile the q_pre rows are
+    // stored and the row factors worked out
+    if (tid == 0) {
+      const uint64_t desc_p = tc_operand_desc(smem0 + kTcSmemQ + s * kTcOperandBytes);
       tc_fence_after_sync();
-      for (int k = 0; k < nk2; ++k) {
-        const uint64_t off = static_cast<uint64_t>(((k >> 2) * kTcAtomBytes + (k & 3) * 32) >> 4);
-        tc_mma(tmem_o, desc_q + off, desc_vt + off, k > 0 ? 1u : 0u);
+      for (int kk = 0; kk < nk2; ++kk) {
+        const uint64_t off = static_cast<uint64_t>(((kk >> 2) * kTcAtomBytes + (kk & 3) * 32) >> 4);
+        tc_mma(tmem_o, desc_p + off, desc_vt + off, kk > 0 ? 1u : 0u);
       }
       tc_commit(bar_o);
+    } else if (tid == 128 && has_next) {
+      good &= tc_mbar_wait(bar_q0 + (s ^ 1) * 8, static_cast<uint32_t>((k + 1) >> 1) & 1u);
+      issue_first_product(s ^ 1);
     }
     __syncwarp();
-    // state rows: piece c16 of rows half*64 + it*8 + r/16.  Both halves and the other 64 q_pre
-    // rows are requested at once, now that the score row's registers are free: their latency
-    // is paid once per tile, behind the second product and the row factors.  (Requesting the
-    // first half before the softmax instead spills registers there and was 8 % slower.)
-    uint4 f4[2][8], b4[2][8];
-    auto request_state_rows = [&](int half) {
 #pragma unroll
-      for (int it = 0; it < 8; ++it) {
-        const int rr = half * 64 + it * 8 + row16;
-        f4[half][it] = make_uint4(0u, 0u, 0u, 0u);
-        b4[half][it] = f4[half][it];
-        if (tok16(rr) < nrows_tok) {
-          const size_t so = static_cast<size_t>(src_tok0 + tok16(rr)) * row_bf16 + head_off16(rr);
-          f4[half][it] = ld_stream16(fsrc + so);
-          b4[half][it] = ld_stream16(bsrc + so);
-        }
+    for (int u = 0; u < 8; ++u) {
+      const int rr = u * 16 + row16;
+      if (rr / G < nrows_tok) {
+        int d = sp.base_dest + i0 + rr / G;
+        if (d >= p.M) d -= p.M;
+        const size_t doff = static_cast<size_t>(d) * row_bf16 + head_off16(rr);
+        st_stream16(qc + doff, qv[u]);
+        if (pc) st_stream16(pc + doff, nan4);
       }
-    };
-    request_state_rows(0);
-    request_state_rows(1);
-    q_pre_load(1);
-    if (row_ok) {
-      int dest_r = sp.base_dest + i0 + tok_r;             // ring row of this thread's row
+    }
+    __syncthreads();                                    // sync 3: both halves' sums are there
+    if (row_ok && h == 0) {
+      const float2 ss = xch[r];
+      const float sum = ss.x + ss.y;
+      int dest_r = sp.base_dest + i0 + tok_r;           // ring row of this thread's row
       if (dest_r >= p.M) dest_r -= p.M;
       float ret1, t1, s1;
       downdate_scalars(l_full, __fmul_rn(l_band, a.band_lse_scale), ret1, t1, s1);
@@ -529,68 +534,68 @@ prefill_sink_exclusive_tc_kernel(const MacB200PrefillBuildArgs a,
       fac[r] = make_float4(fa, fb, fc, empty);
       lc[static_cast<size_t>(dest_r) * H + head_r] = ret2;
     }
-    good &= tc_mbar_wait(bar_o, phase);
+    good &= tc_mbar_wait(bar_o, ph1);
+    good &= tc_mbar_wait(bar_fb, ph1);
     tc_fence_after_sync();
-    // the operand buffer is free: the next tile's q_post rows can come while this tile is written out
-    if (r == 0 && tile + tile_step < ntiles) request_q_rows(tile + tile_step);
+    __syncthreads();                                    // sync 4: the row factors are there
+    // the operand buffer of this stage is free: the q_post rows of the tile after the next
+    if (tile + 2 * tile_step < ntiles) request_q_rows(tile + 2 * tile_step, s);
     __syncwarp();
+
+    // ---- 4. this thread's half of its row: state = full*A - band*B - sink*C, written in place
+    // over the staged full row (both rows lie in the operand layout: a thread's 16-byte chunks
+    // are swizzled with its row, so the eight rows of a quarter-warp never share a bank)
+    {
+      const float4 k4 = fac[r];
+      uint8_t* frow = fullS + h * kTcAtomBytes + r * 128;
+      const uint8_t* brow = bandS + h * kTcAtomBytes + r * 128;
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        uint32_t ou[32];
+        tc_ld32_nowait(tmem_o + tmem_lane + h * 64 + q * 32, ou);
+        tc_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {                   // 8 columns = one 16-byte chunk of bf16
+          const int pos = ((q * 4 + c) ^ (r & 7)) << 4;
+          const uint4 f4 = *reinterpret_cast<const uint4*>(frow + pos);
+          const uint4 b4 = *reinterpret_cast<const uint4*>(brow + pos);
+          const uint32_t x[4] = {f4.x, f4.y, f4.z, f4.w};
+          const uint32_t y[4] = {b4.x, b4.y, b4.z, b4.w};
+          uint32_t w[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float s0 = nk2 == 0 ? 0.f : __uint_as_float(ou[c * 8 + 2 * i]);
+            const float s1 = nk2 == 0 ? 0.f : __uint_as_float(ou[c * 8 + 2 * i + 1]);
+            const float r0 = fmaf(lo_f(x[i]), k4.x, fmaf(-lo_f(y[i]), k4.y, -(s0 * k4.z)));
+            const float r1 = fmaf(hi_f(x[i]), k4.x, fmaf(-hi_f(y[i]), k4.y, -(s1 * k4.z)));
+            w[i] = k4.w != 0.f ? 0u : pack2(r0, r1);
+          }
+          *reinterpret_cast<uint4*>(frow + pos) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+    }
+    tc_fence_before_sync();
     if (!good) {
       atomicOr(&g_tc_status, MAC_B200_STATUS_COPY_TIMEOUT);
-      *reinterpret_cast<volatile uint32_t*>(abort_word) = 1u;   // read after the group syncs below
+      *reinterpret_cast<volatile uint32_t*>(abort_word) = 1u;   // read after the syncs below
     }
+    __syncthreads();                                    // sync 5: the finished rows are in place
 
-    // ---- 5. the sink state of 64 rows at a time (the two warps that own them park their whole
-    // rows, 512 bytes each), then the group streams those rows to the ring in whole 256-byte rows
+    // ---- 5. the rows go to the ring in whole 256-byte rows
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      if ((r >> 6) == half) {
-        uint8_t* srow = stage + (r & 63) * 512;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint32_t ou[32];
-          tc_ld32_nowait(tmem_o + tmem_lane + q * 32, ou);
-          tc_ld_wait();
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {           // 16-byte chunks of 4 floats, swizzled with the row
-            uint4 v = make_uint4(ou[c * 4], ou[c * 4 + 1], ou[c * 4 + 2], ou[c * 4 + 3]);
-            if (nk2 == 0) v = make_uint4(0u, 0u, 0u, 0u);   // no sink key: no second product
-            const int k = q * 8 + c;              // chunk k sits at position k/2 + 16 * (k odd): the
-                                                  // pass reads neighbouring positions per quarter-warp
-            *reinterpret_cast<uint4*>(srow + ((((k >> 1) + ((k & 1) << 4)) ^ (r & 7)) << 4)) = v;
-          }
-        }
-      }
-      tc_fence_before_sync();
-      tc_group_sync(g);
-#pragma unroll
-      for (int it = 0; it < 8; ++it) {
-        const int lr = it * 8 + row16;            // row inside the parked half
-        const int rr = half * 64 + lr;
-        const float4 k4 = fac[rr];
-        const uint8_t* srow = stage + lr * 512;
-        const float4 k0 = *reinterpret_cast<const float4*>(srow + ((c16 ^ (lr & 7)) << 4));
-        const float4 k1 = *reinterpret_cast<const float4*>(srow + (((16 + c16) ^ (lr & 7)) << 4));
-        const float sink[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
-        const uint32_t x[4] = {f4[half][it].x, f4[half][it].y, f4[half][it].z, f4[half][it].w};
-        const uint32_t y[4] = {b4[half][it].x, b4[half][it].y, b4[half][it].z, b4[half][it].w};
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float r0 = fmaf(lo_f(x[i]), k4.x, fmaf(-lo_f(y[i]), k4.y, -(sink[2 * i] * k4.z)));
-          const float r1 = fmaf(hi_f(x[i]), k4.x, fmaf(-hi_f(y[i]), k4.y, -(sink[2 * i + 1] * k4.z)));
-          w[i] = k4.w != 0.f ? 0u : pack2(r0, r1);
-        }
-        if (tok16(rr) < nrows_tok) {
-          int d = sp.base_dest + i0 + tok16(rr);
-          if (d >= p.M) d -= p.M;
-          st_stream16(ac + static_cast<size_t>(d) * row_bf16 + head_off16(rr),
-                      make_uint4(w[0], w[1], w[2], w[3]));
-        }
-      }
-      if (half == 0) q_pre_store(1);
-      tc_group_sync(g);   // the staging is free again; the abort word is the same for every thread
+    for (int u = 0; u < 8; ++u) {
+      const int rr = u * 16 + row16;
+      if (rr / G >= nrows_tok) continue;
+      const uint4 w4 = *reinterpret_cast<const uint4*>(fullS + (c16 >> 3) * kTcAtomBytes + rr * 128 +
+                                                       (((c16 & 7) ^ (rr & 7)) << 4));
+      int d = sp.base_dest + i0 + rr / G;
+      if (d >= p.M) d -= p.M;
+      st_stream16(ac + static_cast<size_t>(d) * row_bf16 + head_off16(rr), w4);
     }
-    phase ^= 1u;
+    tc_fence_async_smem();                              // the copy engine writes these rows next
+    __syncthreads();                                    // sync 6: the staged rows are free
+    if (has_next) request_state_rows(tile + tile_step);
+    __syncwarp();
   }
 
   tc_fence_before_sync();
@@ -644,7 +649,7 @@ int launch_prefill_sink_exclusive_tc(const MacB200PrefillBuildArgs& a, int sms, 
   // whole waves -- the count in 1..8 whose last wave is fullest.
   const int TG = kTcTileRows / G;
   const int max_tiles = ((p.M < 1 ? 1 : p.M) + TG - 1) / TG;
-  const int max_slices = (max_tiles + kTcGroups - 1) / kTcGroups;
+  const int max_slices = max_tiles;
   const int pairs = p.B * a.Hkv;
   int slices = 1;
   double best = -1.0;
@@ -660,17 +665,23 @@ int launch_prefill_sink_exclusive_tc(const MacB200PrefillBuildArgs& a, int sms, 
   }
   TcEncodeTiledFn enc = tc_encode_tiled_fn();
   if (enc == nullptr) return MAC_B200_OK;
-  alignas(64) CUtensorMap q_map;
+  // q_post, full and band rows share one geometry: [src_rows][H][128] bf16, box = 64 dims x the G
+  // heads of a KV head x 128/G tokens, 128-byte swizzle (a box lands as one operand atom)
+  alignas(64) CUtensorMap q_map, f_map, b_map;
   const cuuint64_t dims[3] = {128u, static_cast<cuuint64_t>(p.H), static_cast<cuuint64_t>(p.src_rows)};
   const cuuint64_t strides[2] = {static_cast<cuuint64_t>(kTcRowBytes),
                                  static_cast<cuuint64_t>(p.H) * kTcRowBytes};
   const cuuint32_t box[3] = {64u, static_cast<cuuint32_t>(G), static_cast<cuuint32_t>(kTcTileRows / G)};
   const cuuint32_t estr[3] = {1u, 1u, 1u};
-  if (enc(&q_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(a.q_post), dims, strides, box,
-          estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-          CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-    return MAC_B200_OK;
-  void (*kernel)(MacB200PrefillBuildArgs, CUtensorMap) =
+  const void* bases[3] = {a.q_post, p.src_attn, a.band_attn};
+  CUtensorMap* maps[3] = {&q_map, &f_map, &b_map};
+  for (int i = 0; i < 3; ++i) {
+    if (enc(maps[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(bases[i]), dims, strides,
+            box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return MAC_B200_OK;
+  }
+  void (*kernel)(MacB200PrefillBuildArgs, CUtensorMap, CUtensorMap, CUtensorMap) =
       G == 1 ? prefill_sink_exclusive_tc_kernel<1>
       : G == 2 ? prefill_sink_exclusive_tc_kernel<2>
       : G == 4 ? prefill_sink_exclusive_tc_kernel<4>
@@ -678,7 +689,7 @@ int launch_prefill_sink_exclusive_tc(const MacB200PrefillBuildArgs& a, int sms, 
                : prefill_sink_exclusive_tc_kernel<16>;
   MAC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes));
   dim3 grid(slices, a.Hkv, p.B);
-  kernel<<<grid, kTcThreads, kTcSmemBytes, stream>>>(a, q_map);
+  kernel<<<grid, kTcThreads, kTcSmemBytes, stream>>>(a, q_map, f_map, b_map);
   MAC_CUDA(cudaGetLastError());
   g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
   *launched = true;
