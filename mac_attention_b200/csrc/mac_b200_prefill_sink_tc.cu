@@ -186,6 +186,64 @@ __device__ __forceinline__ void tc_tma_load_3d(uint32_t dst, const CUtensorMap* 
       : "memory");
 }
 
+// Softmax of one thread's share of its score row: kQ * 32 columns starting at column
+// h * kQ * 32 of the row in tensor memory.  The two threads of a row exchange their maxima
+// through `xch` (one __syncthreads inside: every thread of the CTA calls this), then each writes
+// the bf16 weights of its columns into the operand layout (row r of `opnd`: 16-byte chunks of 8
+// keys, atom = chunk / 8, chunk swizzled with the row) and returns the scaled row maximum and
+// the sum of its own weights.
+template <int kQ>
+__device__ __forceinline__ void tc_softmax_share(uint32_t trow, int h, int r, int F, float scale_log2,
+                                                 float2* xch, uint8_t* opnd, float& ms, float& psum) {
+  const int col0 = h * kQ * 32;
+  uint32_t su[kQ][32];
+#pragma unroll
+  for (int q = 0; q < kQ; ++q) tc_ld32_nowait(trow + col0 + q * 32, su[q]);
+  tc_ld_wait();
+  float sv[kQ][32];
+#pragma unroll
+  for (int q = 0; q < kQ; ++q)
+#pragma unroll
+    for (int i = 0; i < 32; ++i) sv[q][i] = __uint_as_float(su[q][i]);
+  if (F < 2 * kQ * 32) {
+#pragma unroll
+    for (int q = 0; q < kQ; ++q)
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + q * 32 + i >= F) sv[q][i] = -INFINITY;
+  }
+  float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+  for (int q = 0; q < kQ; ++q)
+#pragma unroll
+    for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], sv[q][i]);
+  reinterpret_cast<float*>(&xch[r])[h] = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+  __syncthreads();                                      // both shares' maxima are there
+  const float2 mm = xch[r];
+  const float m = fmaxf(mm.x, mm.y);
+  ms = m == -INFINITY ? 0.f : m * scale_log2;           // -inf only when there is no sink key at all
+  uint8_t* prow = opnd + r * 128;
+  float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int q = 0; q < kQ; ++q) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {                       // 8 keys = one 16-byte chunk of weights
+      uint32_t w[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float e0 = tc_ex2(fmaf(sv[q][c * 8 + 2 * e], scale_log2, -ms));
+        const float e1 = tc_ex2(fmaf(sv[q][c * 8 + 2 * e + 1], scale_log2, -ms));
+        sum4[e] += e0 + e1;
+        w[e] = pack2(e0, e1);
+      }
+      const int key_chunk = (col0 >> 3) + q * 4 + c;
+      *reinterpret_cast<uint4*>(prow + (key_chunk >> 3) * kTcAtomBytes +
+                                (((key_chunk & 7) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  psum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+}
+
 struct TcRowSpan {
   int req, keep, start, base_off, base_dest;
   bool ok;
@@ -429,57 +487,16 @@ prefill_sink_exclusive_tc_kernel(const MacB200PrefillBuildArgs a,
         qv[u] = ld_stream16(qpre + static_cast<size_t>(src_tok0 + rr / G) * row_bf16 + head_off16(rr));
     }
 
-    // ---- 2. softmax of this thread's half of its row (64 of the 128 score columns)
+    // ---- 2. softmax of this thread's share of its row: 64 of the 128 score columns, or 32 of
+    // the first 64 when the sink has at most 64 keys (the columns beyond F hold no key; the
+    // second product only reads the k-steps that do)
     good &= tc_mbar_wait(bar_s0 + s * 8, ph2);
     tc_fence_after_sync();
     float ms, psum;
-    {
-      uint32_t su[2][32];
-      tc_ld32_nowait(tmem_base + s * 128 + tmem_lane + h * 64, su[0]);
-      tc_ld32_nowait(tmem_base + s * 128 + tmem_lane + h * 64 + 32, su[1]);
-      tc_ld_wait();
-      float sv[2][32];
-#pragma unroll
-      for (int q = 0; q < 2; ++q)
-#pragma unroll
-        for (int i = 0; i < 32; ++i) sv[q][i] = __uint_as_float(su[q][i]);
-      if (F < kTcMaxF) {
-#pragma unroll
-        for (int q = 0; q < 2; ++q)
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (h * 64 + q * 32 + i >= F) sv[q][i] = -INFINITY;
-      }
-      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int q = 0; q < 2; ++q)
-#pragma unroll
-        for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], sv[q][i]);
-      const float m_half = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-      reinterpret_cast<float*>(&xch[r])[h] = m_half;
-      __syncthreads();                                  // sync 1: both halves' maxima are there
-      const float2 mm = xch[r];
-      const float m = fmaxf(mm.x, mm.y);
-      ms = m == -INFINITY ? 0.f : m * scale_log2;       // -inf only when there is no sink key at all
-      uint8_t* prow = opnd + h * kTcAtomBytes + r * 128;   // keys 64h .. 64h+63 are operand atom h
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {                   // 8 keys = one 16-byte chunk of weights
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float e0 = tc_ex2(fmaf(sv[q][c * 8 + 2 * e], scale_log2, -ms));
-            const float e1 = tc_ex2(fmaf(sv[q][c * 8 + 2 * e + 1], scale_log2, -ms));
-            sum4[e] += e0 + e1;
-            w[e] = pack2(e0, e1);
-          }
-          *reinterpret_cast<uint4*>(prow + (((q * 4 + c) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-      }
-      psum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-    }
+    if (F > 64)
+      tc_softmax_share<2>(tmem_base + s * 128 + tmem_lane, h, r, F, scale_log2, xch, opnd, ms, psum);
+    else
+      tc_softmax_share<1>(tmem_base + s * 128 + tmem_lane, h, r, F, scale_log2, xch, opnd, ms, psum);
     tc_fence_async_smem();
     tc_fence_before_sync();
     __syncthreads();                                    // sync 2: weights written, maxima consumed
