@@ -62,8 +62,7 @@ constexpr int kTcSmemVt = kTcSmemK + kTcOperandBytes;
 constexpr int kTcSmemQ = kTcSmemVt + kTcOperandBytes;               // two stages of q_post rows / weights
 constexpr int kTcSmemFull = kTcSmemQ + 2 * kTcOperandBytes;         // full rows, then the finished rows
 constexpr int kTcSmemBand = kTcSmemFull + kTcOperandBytes;
-constexpr int kTcSmemFac = kTcSmemBand + kTcOperandBytes;           // float4 per row
-constexpr int kTcSmemXch = kTcSmemFac + kTcTileRows * 16;           // float2 per row
+constexpr int kTcSmemXch = kTcSmemBand + kTcOperandBytes;           // float2 per row
 constexpr int kTcSmemBars = kTcSmemXch + kTcTileRows * 8;
 constexpr int kTcSmemBytes = kTcSmemBars + 128 + 1024;   // + room to align the base to 1024 bytes
 constexpr int kTcTmemCols = 512;                 // two stages of S (128 columns each) and O (128)
@@ -358,7 +357,6 @@ prefill_sink_exclusive_tc_kernel(const MacB200PrefillBuildArgs a,
 
   uint8_t* fullS = tc_smem + kTcSmemFull;
   uint8_t* bandS = tc_smem + kTcSmemBand;
-  float4* fac = reinterpret_cast<float4*>(tc_smem + kTcSmemFac);
   float2* xch = reinterpret_cast<float2*>(tc_smem + kTcSmemXch);   // per row: the halves' maxima, then sums
   const uint64_t desc_k = tc_operand_desc(smem0 + kTcSmemK);
   const uint64_t desc_vt = tc_operand_desc(smem0 + kTcSmemVt);
@@ -474,7 +472,7 @@ prefill_sink_exclusive_tc_kernel(const MacB200PrefillBuildArgs a,
     // ---- 1. this row's LSEs; the q_pre rows on their way to the ring (stored after the softmax)
     const bool row_ok = tok_r < nrows_tok;
     float l_full = 0.f, l_band = 0.f;
-    if (row_ok && h == 0) {
+    if (row_ok) {
       const size_t li = static_cast<size_t>(src_tok0 + tok_r) * H + head_r;
       l_full = load_lse(p.src_lse, a.full_lse_dtype, li);
       l_band = load_lse(a.band_lse, a.band_lse_dtype, li);
@@ -529,33 +527,37 @@ prefill_sink_exclusive_tc_kernel(const MacB200PrefillBuildArgs a,
       }
     }
     __syncthreads();                                    // sync 3: both halves' sums are there
-    if (row_ok && h == 0) {
+    // both threads of a row work out its factors (the second one would only wait otherwise):
+    // no hand-over through shared memory, one barrier fewer
+    float4 k4 = make_float4(0.f, 0.f, 0.f, 1.f);
+    if (row_ok) {
       const float2 ss = xch[r];
       const float sum = ss.x + ss.y;
-      int dest_r = sp.base_dest + i0 + tok_r;           // ring row of this thread's row
-      if (dest_r >= p.M) dest_r -= p.M;
       float ret1, t1, s1;
       downdate_scalars(l_full, __fmul_rn(l_band, a.band_lse_scale), ret1, t1, s1);
       int64_t E = pos_base + i0 + tok_r + 1 - a.semantic_pos_ahead;
       if (E < 0) E = 0;
-      float ret2 = -INFINITY, fa = 0.f, fb = 0.f, fc = 0.f, empty = 1.f;
+      float ret2 = -INFINITY;
       if (E > F) {
         const float lse_sink = sum > 0.f ? (ms + log2f(sum)) * 0.6931471805599453f : -INFINITY;
         float t2, s2;
         downdate_scalars(ret1, lse_sink, ret2, t2, s2);
-        fa = s1 * s2;
-        fb = t1 * fa;
-        fc = sum > 0.f ? t2 * s2 / sum : 0.f;
-        empty = 0.f;
+        k4.x = s1 * s2;
+        k4.y = t1 * k4.x;
+        k4.z = sum > 0.f ? t2 * s2 / sum : 0.f;
+        k4.w = 0.f;
       }
-      fac[r] = make_float4(fa, fb, fc, empty);
-      lc[static_cast<size_t>(dest_r) * H + head_r] = ret2;
+      if (h == 0) {
+        int dest_r = sp.base_dest + i0 + tok_r;           // ring row of this thread's row
+        if (dest_r >= p.M) dest_r -= p.M;
+        lc[static_cast<size_t>(dest_r) * H + head_r] = ret2;
+      }
     }
     good &= tc_mbar_wait(bar_o, ph1);
     good &= tc_mbar_wait(bar_fb, ph1);
     tc_fence_after_sync();
-    __syncthreads();                                    // sync 4: the row factors are there
-    // the operand buffer of this stage is free: the q_post rows of the tile after the next
+    // the operand buffer of this stage is free (threads 0 and 128 have seen the second product
+    // finish themselves): the q_post rows of the tile after the next
     if (tile + 2 * tile_step < ntiles) request_q_rows(tile + 2 * tile_step, s);
     __syncwarp();
 
@@ -563,7 +565,6 @@ prefill_sink_exclusive_tc_kernel(const MacB200PrefillBuildArgs a,
     // over the staged full row (both rows lie in the operand layout: a thread's 16-byte chunks
     // are swizzled with its row, so the eight rows of a quarter-warp never share a bank)
     {
-      const float4 k4 = fac[r];
       uint8_t* frow = fullS + h * kTcAtomBytes + r * 128;
       const uint8_t* brow = bandS + h * kTcAtomBytes + r * 128;
 #pragma unroll
