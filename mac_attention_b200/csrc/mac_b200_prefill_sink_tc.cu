@@ -30,8 +30,9 @@
 //      their maxima through shared memory, and the bf16 weights go over the dead q_post rows as
 //      the next operand (64 keys = one operand atom per thread half);
 //   4. one thread issues O = P V and, right after, the next tile's S = Q K^T; meanwhile the
-//      q_pre rows are stored to the ring and one thread per row folds both downdates into three
-//      factors (state = full*A - band*B - sink*C);
+//      q_pre rows are stored to the ring and the two threads of a row exchange the sums of their
+//      weights and each fold both downdates into the row's three factors
+//      (state = full*A - band*B - sink*C);
 //   5. every thread reads its 64 columns of O and combines them with its half of the staged full
 //      and band rows IN PLACE (the staged rows lie in the operand layout: a thread's 16-byte
 //      chunks are swizzled with its row, so row-per-thread access is free of bank conflicts and
